@@ -1,0 +1,585 @@
+// KV-paged single-query decode for sm_100a: split-KV partial kernels + log-sum-exp combine.
+//
+// Semantics (paged_attention_kernel.cu:100-187 of the reference, with a correct softmax): for
+// sequence b with cached tokens t in [beg_b, end_b) living in rows slots[t] of the K/V pools, and
+// head h:  s_t = scale*<q, K[slots[t], h]>,  s_new = scale*<q, k_new>,  p = softmax(s_0..s_n, s_new),
+// out = sum p_t V[slots[t], h] + p_new v_new.
+//
+// Work decomposition.  The concatenated token stream is cut by a global grid of `chunk` tokens; a
+// work unit is the intersection of one grid cell with one sequence, numbered  u = cell + b.  That
+// numbering is strictly increasing in (b, cell), needs no host knowledge of the lengths (so no
+// device->host sync, unlike the reference launcher's per-sequence .item() loop) and has at most
+// n_tokens/chunk + B + 1 ids; ids that correspond to no unit exit at once.  A CTA resolves its
+// unit with a binary search over the offsets staged in shared memory.
+//
+// Fast kernel (16-bit q; 16-bit or e4m3 KV; D in {64,128,256}): one warp per (unit, head), the
+// warps of a CTA covering adjacent heads of the SAME tokens so that a CTA streams `warps*D`
+// contiguous elements per token.  Each 16-byte slice of a row is owned by one lane; a warp-wide
+// 128-bit load fetches 32/LPR rows, and U such loads for K plus U for V are issued back to back
+// before any arithmetic (2*U*512 B in flight per warp).  The slot table is read once per tile by
+// the warp (coalesced) and broadcast by shuffle; the next tile's slots are prefetched.  Scores are
+// reduced over the LPR lanes of a row by xor shuffles, the online-softmax state (m, l, o) is kept
+// in the log2 domain in registers.  Each warp writes one partial row [o[D], m, l].
+//
+// Generic kernel (any dtype / head_dim): one CTA per (unit, head); small-shape compatibility path.
+#include "common.cuh"
+
+namespace attn {
+
+constexpr int kMaxStagedB = 2048;
+
+struct DecodeParams {
+    const void* q;
+    const void* k_cache;
+    const void* v_cache;
+    const int32_t* slots;
+    const int32_t* offsets;
+    float* part;  // [n_units, H, D + 2]
+    double* S;
+    int64_t sp_stride;
+    int B, H, D;
+    int64_t n_tokens, n_slots;
+    int uniform_ctx;
+    int chunk;
+    float scale_log2;  // scale * log2(e)
+    const float* k_scale;
+    const float* v_scale;
+    int32_t* err_flag;
+    int head_groups;
+};
+
+struct Unit {
+    int b;
+    int64_t seq_beg, tbeg, tend;
+};
+
+// beg(b) for b in [0, B]: start of sequence b in the token stream (beg(B) = total).
+struct SeqBounds {
+    const int32_t* off;  // global or shared copy; nullptr => uniform
+    int64_t uniform_ctx;
+    int64_t n_tokens;
+    __device__ __forceinline__ int64_t beg(int b) const {
+        if (!off) return (int64_t)b * uniform_ctx;
+        if (b == 0) return 0;
+        int64_t v = off[b - 1];
+        return v < 0 ? 0 : (v > n_tokens ? n_tokens : v);
+    }
+};
+
+__device__ __forceinline__ bool resolve_unit(int64_t u, int B, int chunk, const SeqBounds& sb, Unit& out) {
+    int lo = 0, hi = B - 1;
+    while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (sb.beg(mid) / chunk + mid <= u) lo = mid; else hi = mid - 1;
+    }
+    const int64_t seq_beg = sb.beg(lo), seq_end = sb.beg(lo + 1);
+    const int64_t cell = u - lo;
+    const int64_t tb = cell * chunk, te = tb + chunk;
+    out.b = lo;
+    out.seq_beg = seq_beg;
+    out.tbeg = tb > seq_beg ? tb : seq_beg;
+    out.tend = te < seq_end ? te : seq_end;
+    return out.tbeg < out.tend;
+}
+
+__device__ __forceinline__ const int32_t* stage_offsets(const DecodeParams& p, int32_t* s_off) {
+    if (!p.offsets) return nullptr;
+    if (p.B > kMaxStagedB) return p.offsets;
+    for (int i = threadIdx.x; i < p.B; i += blockDim.x) s_off[i] = p.offsets[i];
+    __syncthreads();
+    return s_off;
+}
+
+// ---------------------------------------------------------------------------------------------
+// fast kernel
+// ---------------------------------------------------------------------------------------------
+template <typename KVT, int EPL> struct RowChunk;  // 16 bytes of a KV row -> EPL floats
+template <> struct RowChunk<__half, 8> {
+    static __device__ __forceinline__ void unpack(const uint4& r, float* f) {
+        unpack2(r.x, __half(), f[0], f[1]); unpack2(r.y, __half(), f[2], f[3]);
+        unpack2(r.z, __half(), f[4], f[5]); unpack2(r.w, __half(), f[6], f[7]);
+    }
+};
+template <> struct RowChunk<__nv_bfloat16, 8> {
+    static __device__ __forceinline__ void unpack(const uint4& r, float* f) {
+        unpack2(r.x, __nv_bfloat16(), f[0], f[1]); unpack2(r.y, __nv_bfloat16(), f[2], f[3]);
+        unpack2(r.z, __nv_bfloat16(), f[4], f[5]); unpack2(r.w, __nv_bfloat16(), f[6], f[7]);
+    }
+};
+template <> struct RowChunk<__nv_fp8_e4m3, 16> {
+    static __device__ __forceinline__ void unpack(const uint4& r, float* f) {
+        unpack4_e4m3(r.x, f[0], f[1], f[2], f[3]); unpack4_e4m3(r.y, f[4], f[5], f[6], f[7]);
+        unpack4_e4m3(r.z, f[8], f[9], f[10], f[11]); unpack4_e4m3(r.w, f[12], f[13], f[14], f[15]);
+    }
+};
+
+template <typename QT, typename KVT, int D>
+__global__ void __launch_bounds__(256)
+paged_decode_fast_kernel(const DecodeParams p) {
+    constexpr int EPL = 16 / (int)sizeof(KVT);   // elements per lane (one 16-byte slice)
+    constexpr int LPR = D / EPL;                 // lanes per row
+    constexpr int TPI = 32 / LPR;                // rows per warp-wide load
+    constexpr int U = (TPI * 8 <= 32) ? 8 : 32 / TPI;  // loads in flight per lane and tensor
+    constexpr int TILE = TPI * U;                // tokens per iteration (<= 32)
+    static_assert(LPR >= 1 && LPR <= 32 && TILE <= 32, "unsupported head_dim");
+
+    __shared__ int32_t s_off[kMaxStagedB];
+    SeqBounds sb{stage_offsets(p, s_off), p.uniform_ctx, p.n_tokens};
+
+    const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t u = blockIdx.x / p.head_groups;
+    const int h = (blockIdx.x % p.head_groups) * warps + warp;
+    Unit un;
+    if (!resolve_unit(u, p.B, p.chunk, sb, un) || h >= p.H) return;
+
+    const int sub = lane % LPR, grp = lane / LPR;
+    const int64_t row_bytes = (int64_t)p.H * D * sizeof(KVT);
+    const char* kbase = (const char*)p.k_cache + ((int64_t)h * D + sub * EPL) * sizeof(KVT);
+    const char* vbase = (const char*)p.v_cache + ((int64_t)h * D + sub * EPL) * sizeof(KVT);
+
+    float qf[EPL];
+    {
+        const QT* qp = (const QT*)p.q + ((int64_t)un.b * p.H + h) * D + sub * EPL;
+        const float qs = p.scale_log2 * (p.k_scale ? p.k_scale[h] : 1.f);
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) qf[i] = to_f32<QT>(qp[i]) * qs;
+    }
+    float m = -INFINITY, l = 0.f, o[EPL];
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) o[i] = 0.f;
+
+    auto load_slot = [&](int64_t t0) -> int {
+        const int64_t t = t0 + lane;
+        int s = -1;
+        if (lane < TILE && t < un.tend) {
+            const int64_t v = p.slots ? (int64_t)p.slots[t] : t;
+            if (v >= 0 && v < p.n_slots) s = (int)v;
+            else if (p.err_flag) atomicOr(p.err_flag, ATTN_B200_FLAG_BAD_SLOT);
+        }
+        return s;
+    };
+
+    int next_slot = load_slot(un.tbeg);
+    for (int64_t t0 = un.tbeg; t0 < un.tend; t0 += TILE) {
+        const int my_slot = next_slot;
+        uint4 kr[U], vr[U];
+        int sl[U];
+#pragma unroll
+        for (int j = 0; j < U; ++j) {
+            sl[j] = __shfl_sync(0xffffffffu, my_slot, j * TPI + grp);
+            if (sl[j] >= 0) {
+                kr[j] = ldg_stream128(kbase + (int64_t)sl[j] * row_bytes);
+            } else {
+                kr[j] = make_uint4(0, 0, 0, 0);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < U; ++j) {
+            if (sl[j] >= 0) {
+                vr[j] = ldg_stream128(vbase + (int64_t)sl[j] * row_bytes);
+            } else {
+                vr[j] = make_uint4(0, 0, 0, 0);
+            }
+        }
+        if (t0 + TILE < un.tend) next_slot = load_slot(t0 + TILE);
+
+        float s[U];
+        float tmax = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < U; ++j) {
+            float kf[EPL];
+            RowChunk<KVT, EPL>::unpack(kr[j], kf);
+            float acc = 0.f;
+#pragma unroll
+            for (int i = 0; i < EPL; ++i) acc = fmaf(qf[i], kf[i], acc);
+            acc = group_sum<LPR>(acc);
+            s[j] = sl[j] >= 0 ? acc : -INFINITY;
+            tmax = fmaxf(tmax, s[j]);
+        }
+        if (p.S) {
+            if (sub == 0) {
+#pragma unroll
+                for (int j = 0; j < U; ++j)
+                    if (sl[j] >= 0)
+                        p.S[((int64_t)un.b * p.H + h) * p.sp_stride + (t0 + j * TPI + grp - un.seq_beg)] =
+                            (double)(s[j] * kLn2);
+            }
+        }
+        // maximum over the TPI row groups of the warp
+#pragma unroll
+        for (int x = LPR; x < 32; x <<= 1) tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, x));
+        const float m_new = fmaxf(m, tmax);
+        if (m_new > -INFINITY) {  // at least one valid row so far
+            const float alpha = fast_exp2(m - m_new);
+            l *= alpha;
+#pragma unroll
+            for (int i = 0; i < EPL; ++i) o[i] *= alpha;
+#pragma unroll
+            for (int j = 0; j < U; ++j) {
+                const float pj = fast_exp2(s[j] - m_new);
+                l += pj;
+                float vf[EPL];
+                RowChunk<KVT, EPL>::unpack(vr[j], vf);
+#pragma unroll
+                for (int i = 0; i < EPL; ++i) o[i] = fmaf(pj, vf[i], o[i]);
+            }
+            m = m_new;
+        }
+    }
+    // fold the TPI row groups
+#pragma unroll
+    for (int x = LPR; x < 32; x <<= 1) {
+        l += __shfl_xor_sync(0xffffffffu, l, x);
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) o[i] += __shfl_xor_sync(0xffffffffu, o[i], x);
+    }
+    float* row = p.part + ((int64_t)u * p.H + h) * (D + 2);
+    if (grp == 0) {
+        const float vs = p.v_scale ? p.v_scale[h] : 1.f;
+        float2* dst = reinterpret_cast<float2*>(row + sub * EPL);
+#pragma unroll
+        for (int i = 0; i < EPL / 2; ++i) dst[i] = make_float2(o[2 * i] * vs, o[2 * i + 1] * vs);
+        if (sub == 0) *reinterpret_cast<float2*>(row + D) = make_float2(m, l);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// generic kernel: any dtype / head_dim, one CTA per (unit, head)
+// ---------------------------------------------------------------------------------------------
+template <typename QT, typename KVT>
+__global__ void __launch_bounds__(128)
+paged_decode_generic_kernel(const DecodeParams p) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __shared__ int32_t s_off[kMaxStagedB];
+    __shared__ float s_red[4];
+    float* s_q = reinterpret_cast<float*>(smem_raw);       // [D]
+    float* s_sc = s_q + p.D;                                // [chunk]
+    int32_t* s_slot = reinterpret_cast<int32_t*>(s_sc + p.chunk);  // [chunk]
+
+    SeqBounds sb{stage_offsets(p, s_off), p.uniform_ctx, p.n_tokens};
+    const int64_t u = blockIdx.x / p.H;
+    const int h = blockIdx.x % p.H;
+    Unit un;
+    if (!resolve_unit(u, p.B, p.chunk, sb, un)) return;
+    const int n = (int)(un.tend - un.tbeg);
+    const int D = p.D;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+
+    const float qs = p.scale_log2 * (p.k_scale ? p.k_scale[h] : 1.f);
+    for (int d = tid; d < D; d += blockDim.x)
+        s_q[d] = to_f32<QT>(((const QT*)p.q)[((int64_t)un.b * p.H + h) * D + d]) * qs;
+    for (int i = tid; i < n; i += blockDim.x) {
+        const int64_t t = un.tbeg + i;
+        const int64_t v = p.slots ? (int64_t)p.slots[t] : t;
+        int s = -1;
+        if (v >= 0 && v < p.n_slots) s = (int)v;
+        else if (p.err_flag) atomicOr(p.err_flag, ATTN_B200_FLAG_BAD_SLOT);
+        s_slot[i] = s;
+    }
+    __syncthreads();
+    float lmax = -INFINITY;
+    for (int i = tid; i < n; i += blockDim.x) {
+        float acc = -INFINITY;
+        if (s_slot[i] >= 0) {
+            const KVT* kr = (const KVT*)p.k_cache + ((int64_t)s_slot[i] * p.H + h) * D;
+            acc = 0.f;
+            for (int d = 0; d < D; ++d) acc = fmaf(s_q[d], to_f32<KVT>(kr[d]), acc);
+            if (p.S)
+                p.S[((int64_t)un.b * p.H + h) * p.sp_stride + (un.tbeg + i - un.seq_beg)] = (double)(acc * kLn2);
+        }
+        s_sc[i] = acc;
+        lmax = fmaxf(lmax, acc);
+    }
+    lmax = group_max<32>(lmax);
+    if (lane == 0) s_red[warp] = lmax;
+    __syncthreads();
+    const float m = fmaxf(fmaxf(s_red[0], s_red[1]), fmaxf(s_red[2], s_red[3]));
+    __syncthreads();
+    float lsum = 0.f;
+    for (int i = tid; i < n; i += blockDim.x) {
+        const float pj = (m > -INFINITY && s_sc[i] > -INFINITY) ? exp2f(s_sc[i] - m) : 0.f;
+        s_sc[i] = pj;
+        lsum += pj;
+    }
+    lsum = group_sum<32>(lsum);
+    if (lane == 0) s_red[warp] = lsum;
+    __syncthreads();
+    const float l = s_red[0] + s_red[1] + s_red[2] + s_red[3];
+    float* row = p.part + ((int64_t)u * p.H + h) * (D + 2);
+    const float vs = p.v_scale ? p.v_scale[h] : 1.f;
+    for (int d = tid; d < D; d += blockDim.x) {
+        float acc = 0.f;
+        for (int i = 0; i < n; ++i)
+            if (s_slot[i] >= 0)
+                acc = fmaf(s_sc[i], to_f32<KVT>(((const KVT*)p.v_cache)[((int64_t)s_slot[i] * p.H + h) * D + d]), acc);
+        row[d] = acc * vs;
+    }
+    if (tid == 0) { row[D] = m; row[D + 1] = l; }
+}
+
+// ---------------------------------------------------------------------------------------------
+// combine
+// ---------------------------------------------------------------------------------------------
+struct CombineParams {
+    const float* parts;   // unit partials [n_units, H, D+2]  or  gathered [n_parts, B, H, D+2]
+    int n_parts;          // > 0: gathered mode; 0: unit mode (rows found from offsets/chunk)
+    const void* q;
+    const void* k_new;    // may be null: new token not folded
+    const void* v_new;
+    void* out;            // final output [B, H*D] (QT) or null
+    float* part_out;      // [B, H, D+2] or null
+    double* S;
+    double* P;
+    int64_t sp_stride;
+    const int32_t* offsets;
+    int64_t uniform_ctx, n_tokens;
+    int B, H, D, chunk;
+    float scale_log2;
+};
+
+template <typename QT>
+__global__ void __launch_bounds__(128)
+lse_combine_kernel(const CombineParams p) {
+    const int lane = threadIdx.x & 31;
+    const int64_t w = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (w >= (int64_t)p.B * p.H) return;
+    const int b = (int)(w / p.H), h = (int)(w % p.H);
+    const int D = p.D, RS = D + 2;
+
+    int64_t first, stride;
+    int count;
+    int64_t n_ctx = 0;
+    if (p.n_parts > 0) {
+        first = (int64_t)b * p.H + h;
+        stride = (int64_t)p.B * p.H;
+        count = p.n_parts;
+    } else {
+        SeqBounds sb{p.offsets, p.uniform_ctx, p.n_tokens};
+        const int64_t sbeg = sb.beg(b), send = sb.beg(b + 1);
+        n_ctx = send > sbeg ? send - sbeg : 0;
+        const int64_t c0 = sbeg / p.chunk, c1 = n_ctx > 0 ? (send - 1) / p.chunk : c0 - 1;
+        first = (c0 + b) * p.H + h;
+        stride = p.H;
+        count = (int)(c1 - c0 + 1);
+    }
+    // pass 1: global max (log2 domain)
+    float M = -INFINITY;
+    for (int i = lane; i < count; i += 32) M = fmaxf(M, p.parts[(first + i * stride) * RS + D]);
+    float s_new = -INFINITY;
+    if (p.k_new) {
+        const QT* qp = (const QT*)p.q + ((int64_t)b * p.H + h) * D;
+        const QT* kp = (const QT*)p.k_new + ((int64_t)b * p.H + h) * D;
+        float acc = 0.f;
+        for (int d = lane; d < D; d += 32) acc = fmaf(to_f32<QT>(qp[d]), to_f32<QT>(kp[d]), acc);
+        s_new = group_sum<32>(acc) * p.scale_log2;
+        M = fmaxf(M, s_new);
+    }
+    M = group_max<32>(M);
+    // pass 2: denominator
+    float L = 0.f;
+    for (int i = lane; i < count; i += 32) {
+        const float mi = p.parts[(first + i * stride) * RS + D];
+        const float li = p.parts[(first + i * stride) * RS + D + 1];
+        if (mi > -INFINITY) L += li * exp2f(mi - M);
+    }
+    L = group_sum<32>(L);
+    const float w_new = p.k_new ? exp2f(s_new - M) : 0.f;
+    L += w_new;
+    // pass 3: numerator, lanes over dims
+    const float inv = (p.out && L > 0.f) ? 1.f / L : 1.f;
+    for (int d = lane; d < D; d += 32) {
+        float acc = 0.f;
+        for (int i = 0; i < count; ++i) {
+            const float* row = p.parts + (first + i * stride) * RS;
+            const float mi = row[D];
+            if (mi > -INFINITY) acc = fmaf(row[d], exp2f(mi - M), acc);
+        }
+        if (p.k_new) acc = fmaf(w_new, to_f32<QT>(((const QT*)p.v_new)[((int64_t)b * p.H + h) * D + d]), acc);
+        if (p.out) ((QT*)p.out)[((int64_t)b * p.H + h) * D + d] = from_f32<QT>(acc * inv);
+        else p.part_out[((int64_t)b * p.H + h) * RS + d] = acc;
+    }
+    if (!p.out && lane == 0) {
+        p.part_out[((int64_t)b * p.H + h) * RS + D] = M;
+        p.part_out[((int64_t)b * p.H + h) * RS + D + 1] = L;
+    }
+    if (p.S && p.out) {
+        double* Srow = p.S + ((int64_t)b * p.H + h) * p.sp_stride;
+        double* Prow = p.P + ((int64_t)b * p.H + h) * p.sp_stride;
+        const double Md = (double)M * (double)kLn2;   // natural-log maximum
+        const double Ld = (double)L;
+        for (int64_t t = lane; t < n_ctx; t += 32) Prow[t] = exp(Srow[t] - Md) / Ld;
+        if (lane == 0 && p.k_new) {
+            Srow[n_ctx] = (double)(s_new * kLn2);
+            Prow[n_ctx] = (double)w_new / Ld;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------
+static inline int64_t max_units(int B, int64_t n_tokens, int chunk) { return n_tokens / chunk + B + 1; }
+
+template <typename QT, typename KVT>
+static int launch_fast(const DecodeParams& p, int warps, int64_t n_units, cudaStream_t st) {
+    const int64_t blocks = n_units * p.head_groups;
+    if (blocks > 0x7fffffffLL) return ATTN_B200_ETOOLARGE;
+    switch (p.D) {
+        case 64: paged_decode_fast_kernel<QT, KVT, 64><<<(unsigned)blocks, warps * 32, 0, st>>>(p); break;
+        case 128: paged_decode_fast_kernel<QT, KVT, 128><<<(unsigned)blocks, warps * 32, 0, st>>>(p); break;
+        case 256: paged_decode_fast_kernel<QT, KVT, 256><<<(unsigned)blocks, warps * 32, 0, st>>>(p); break;
+        default: return ATTN_B200_ESHAPE;
+    }
+    return (int)cudaGetLastError();
+}
+
+template <typename QT, typename KVT>
+static int launch_generic(const DecodeParams& p, int64_t n_units, cudaStream_t st) {
+    const int64_t blocks = n_units * p.H;
+    if (blocks > 0x7fffffffLL) return ATTN_B200_ETOOLARGE;
+    const size_t smem = (size_t)p.D * 4 + (size_t)p.chunk * 8;
+    if (smem > 40 * 1024) return ATTN_B200_ESHAPE;
+    paged_decode_generic_kernel<QT, KVT><<<(unsigned)blocks, 128, smem, st>>>(p);
+    return (int)cudaGetLastError();
+}
+
+static bool fast_ok(const DecodeParams& p, int q_dtype, int kv_dtype) {
+    if (!(p.D == 64 || p.D == 128 || p.D == 256)) return false;
+    if (!(q_dtype == ATTN_B200_F16 || q_dtype == ATTN_B200_BF16)) return false;
+    if (!(kv_dtype == q_dtype || kv_dtype == ATTN_B200_E4M3)) return false;
+    if (((uintptr_t)p.k_cache | (uintptr_t)p.v_cache) % 16) return false;
+    return true;
+}
+
+static int run_stage1(DecodeParams& p, int q_dtype, int kv_dtype, cudaStream_t st) {
+    const int64_t n_units = max_units(p.B, p.n_tokens, p.chunk);
+    if (fast_ok(p, q_dtype, kv_dtype)) {
+        const int warps = p.H >= 8 ? 8 : p.H;
+        p.head_groups = (p.H + warps - 1) / warps;
+        if (q_dtype == ATTN_B200_F16) {
+            return kv_dtype == ATTN_B200_E4M3 ? launch_fast<__half, __nv_fp8_e4m3>(p, warps, n_units, st)
+                                              : launch_fast<__half, __half>(p, warps, n_units, st);
+        }
+        return kv_dtype == ATTN_B200_E4M3 ? launch_fast<__nv_bfloat16, __nv_fp8_e4m3>(p, warps, n_units, st)
+                                          : launch_fast<__nv_bfloat16, __nv_bfloat16>(p, warps, n_units, st);
+    }
+    p.head_groups = p.H;
+    if (kv_dtype == ATTN_B200_E4M3) {
+        if (q_dtype == ATTN_B200_F16) return launch_generic<__half, __nv_fp8_e4m3>(p, n_units, st);
+        if (q_dtype == ATTN_B200_BF16) return launch_generic<__nv_bfloat16, __nv_fp8_e4m3>(p, n_units, st);
+        return ATTN_B200_EDTYPE;
+    }
+    if (kv_dtype != q_dtype) return ATTN_B200_EDTYPE;
+    switch (q_dtype) {
+        case ATTN_B200_F16: return launch_generic<__half, __half>(p, n_units, st);
+        case ATTN_B200_BF16: return launch_generic<__nv_bfloat16, __nv_bfloat16>(p, n_units, st);
+        case ATTN_B200_F32: return launch_generic<float, float>(p, n_units, st);
+        default: return ATTN_B200_EDTYPE;
+    }
+}
+
+static int run_combine(const CombineParams& c, int q_dtype, cudaStream_t st) {
+    const int64_t warps = (int64_t)c.B * c.H;
+    const unsigned blocks = (unsigned)((warps + 3) / 4);
+    switch (q_dtype) {
+        case ATTN_B200_F16: lse_combine_kernel<__half><<<blocks, 128, 0, st>>>(c); break;
+        case ATTN_B200_BF16: lse_combine_kernel<__nv_bfloat16><<<blocks, 128, 0, st>>>(c); break;
+        case ATTN_B200_F32: lse_combine_kernel<float><<<blocks, 128, 0, st>>>(c); break;
+        default: return ATTN_B200_EDTYPE;
+    }
+    return (int)cudaGetLastError();
+}
+
+static int check_common(const void* q, const void* kc, const void* vc, int B, int H, int D, int64_t n_tokens,
+                        int64_t n_slots, int chunk, int kv_dtype, const float* ks, const float* vs) {
+    if (!q || !kc || !vc || B <= 0 || H <= 0 || D <= 0 || n_tokens < 0 || n_slots <= 0) return ATTN_B200_EINVAL;
+    if (chunk < 32 || chunk > 2048 || chunk % 32) return ATTN_B200_ESHAPE;
+    if (D > 1024) return ATTN_B200_ESHAPE;
+    if (n_tokens > 0x7fffffffLL) return ATTN_B200_ETOOLARGE;
+    if (kv_dtype == ATTN_B200_E4M3 && (!ks || !vs)) return ATTN_B200_EINVAL;
+    return 0;
+}
+
+}  // namespace attn
+
+using namespace attn;
+
+extern "C" size_t attn_b200_paged_decode_workspace_bytes(int B, int H, int D, int64_t n_tokens, int chunk) {
+    if (B <= 0 || H <= 0 || D <= 0 || n_tokens < 0 || chunk <= 0) return 0;
+    return (size_t)max_units(B, n_tokens, chunk) * H * (D + 2) * sizeof(float);
+}
+
+extern "C" int attn_b200_paged_decode_pick_chunk(int B, int H, int D, int64_t n_tokens, int sm_count) {
+    (void)D;
+    if (sm_count <= 0) sm_count = 148;
+    const int warps = H >= 8 ? 8 : (H > 0 ? H : 1);
+    const int64_t hg = (H + warps - 1) / warps;
+    int chunk = 1024;
+    // largest chunk that still yields >= 16 CTAs per SM (two resident CTAs x eight waves)
+    while (chunk > 32 && (n_tokens / chunk + B) * hg < 16LL * sm_count) chunk >>= 1;
+    return chunk;
+}
+
+extern "C" int attn_b200_paged_decode(const void* q, const void* k_new, const void* v_new, const void* k_cache,
+                                      const void* v_cache, const int32_t* slots, const int32_t* offsets, void* out,
+                                      void* workspace, size_t workspace_bytes, double* S, double* P,
+                                      int64_t sp_stride, int B, int H, int D, int64_t n_tokens, int64_t n_slots,
+                                      int uniform_ctx, int chunk, float scale, const float* k_scale,
+                                      const float* v_scale, int q_dtype, int kv_dtype, int stages,
+                                      int32_t* err_flag, void* stream) {
+    int rc = check_common(q, k_cache, v_cache, B, H, D, n_tokens, n_slots, chunk, kv_dtype, k_scale, v_scale);
+    if (rc) return rc;
+    if (!out || !workspace || !k_new || !v_new) return ATTN_B200_EINVAL;
+    if ((S == nullptr) != (P == nullptr)) return ATTN_B200_EINVAL;
+    if (!offsets && (uniform_ctx < 0 || (int64_t)uniform_ctx * B != n_tokens)) return ATTN_B200_EINVAL;
+    if (workspace_bytes < attn_b200_paged_decode_workspace_bytes(B, H, D, n_tokens, chunk) ||
+        (uintptr_t)workspace % 16)
+        return ATTN_B200_EWORKSPACE;
+    cudaStream_t st = (cudaStream_t)stream;
+    DecodeParams p{q, k_cache, v_cache, slots, offsets, (float*)workspace, S, sp_stride, B, H, D, n_tokens, n_slots,
+                   uniform_ctx, chunk, scale * kLog2e, kv_dtype == ATTN_B200_E4M3 ? k_scale : nullptr,
+                   kv_dtype == ATTN_B200_E4M3 ? v_scale : nullptr, err_flag, 1};
+    if (stages < 1 || stages > 3) return ATTN_B200_EINVAL;
+    if (stages & 1) {
+        rc = run_stage1(p, q_dtype, kv_dtype, st);
+        if (rc) return rc;
+    }
+    if (!(stages & 2)) return 0;
+    CombineParams c{(const float*)workspace, 0, q, k_new, v_new, out, nullptr, S, P, sp_stride, offsets,
+                    uniform_ctx, n_tokens, B, H, D, chunk, scale * kLog2e};
+    return run_combine(c, q_dtype, st);
+}
+
+extern "C" int attn_b200_paged_decode_partial(const void* q, const void* k_cache, const void* v_cache,
+                                              const int32_t* slots, const int32_t* offsets, float* part_out,
+                                              void* workspace, size_t workspace_bytes, int B, int H, int D,
+                                              int64_t n_tokens, int64_t n_slots, int chunk, float scale,
+                                              const float* k_scale, const float* v_scale, int q_dtype,
+                                              int kv_dtype, int32_t* err_flag, void* stream) {
+    int rc = check_common(q, k_cache, v_cache, B, H, D, n_tokens, n_slots, chunk, kv_dtype, k_scale, v_scale);
+    if (rc) return rc;
+    if (!part_out || !workspace || !offsets) return ATTN_B200_EINVAL;
+    if (workspace_bytes < attn_b200_paged_decode_workspace_bytes(B, H, D, n_tokens, chunk) ||
+        (uintptr_t)workspace % 16)
+        return ATTN_B200_EWORKSPACE;
+    cudaStream_t st = (cudaStream_t)stream;
+    DecodeParams p{q, k_cache, v_cache, slots, offsets, (float*)workspace, nullptr, 0, B, H, D, n_tokens, n_slots,
+                   0, chunk, scale * kLog2e, kv_dtype == ATTN_B200_E4M3 ? k_scale : nullptr,
+                   kv_dtype == ATTN_B200_E4M3 ? v_scale : nullptr, err_flag, 1};
+    rc = run_stage1(p, q_dtype, kv_dtype, st);
+    if (rc) return rc;
+    CombineParams c{(const float*)workspace, 0, q, nullptr, nullptr, nullptr, part_out, nullptr, nullptr, 0,
+                    offsets, 0, n_tokens, B, H, D, chunk, scale * kLog2e};
+    return run_combine(c, q_dtype, st);
+}
+
+extern "C" int attn_b200_lse_combine(const float* parts, int n_parts, const void* q, const void* k_new,
+                                     const void* v_new, void* out, int B, int H, int D, float scale, int q_dtype,
+                                     void* stream) {
+    if (!parts || n_parts <= 0 || !out || B <= 0 || H <= 0 || D <= 0) return ATTN_B200_EINVAL;
+    if ((k_new == nullptr) != (v_new == nullptr)) return ATTN_B200_EINVAL;
+    if (k_new && !q) return ATTN_B200_EINVAL;
+    CombineParams c{parts, n_parts, q, k_new, v_new, out, nullptr, nullptr, nullptr, 0, nullptr, 0, 0,
+                    B, H, D, 32, scale * kLog2e};
+    return run_combine(c, q_dtype, (cudaStream_t)stream);
+}

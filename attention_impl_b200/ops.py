@@ -1,0 +1,348 @@
+"""Host-side mirror of the reference's five operators, calling libattn_b200 through its C ABI.
+
+Names, positional argument order and return arity follow the reference's pybind blocks
+(attention_kernel.cu:282-285, paged_attention_kernel.cu:296-299, rotary_embedding.cu:80-84).
+Extra behaviour is keyword-only and defaults to the reference's.  torch is used for device
+memory and the current stream only; all arithmetic happens in the CUDA library.
+"""
+from __future__ import annotations
+
+import math
+from typing import List, Optional
+
+import torch
+
+from . import _lib
+from ._lib import lib, check
+
+_DT = {torch.float16: _lib.F16, torch.bfloat16: _lib.BF16, torch.float32: _lib.F32}
+_FP8 = tuple(t for t in (getattr(torch, "float8_e4m3fn", None),) if t is not None)
+
+
+def _check_input(x: torch.Tensor, name: str) -> None:
+    # same wording as the reference's CHECK_INPUT (util.cuh:4-6)
+    if not isinstance(x, torch.Tensor) or not x.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor")
+    if not x.is_contiguous():
+        raise RuntimeError(f"{name} must be contiguous")
+
+
+def _dtype_code(x: torch.Tensor, name: str) -> int:
+    if x.dtype not in _DT:
+        raise RuntimeError(f"{name}: dtype {x.dtype} is not supported (float16, bfloat16, float32; "
+                           "float64 inputs are rejected on purpose)")
+    return _DT[x.dtype]
+
+
+def _int32(x: torch.Tensor, name: str) -> None:
+    _check_input(x, name)
+    if x.dtype != torch.int32:
+        raise RuntimeError(f"{name} must be int32 (expected scalar type Int but found {x.dtype})")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(x: Optional[torch.Tensor]) -> Optional[int]:
+    return None if x is None else x.data_ptr()
+
+
+def sm_count(device) -> int:
+    return torch.cuda.get_device_properties(device).multi_processor_count
+
+
+# ----------------------------------------------------------------------------------------------
+# rotary embedding
+# ----------------------------------------------------------------------------------------------
+def rotary_embedding_inplace(Q, K, positions, cos, sin, head_dim: int, *, check_positions: bool = False) -> None:
+    """In-place NeoX rotary embedding on Q and K (rotary_embedding.cu:40-77).
+
+    Q ``[N, Hq*head_dim]``, K ``[N, Hk*head_dim]`` (the reference assumes Hk == Hq; any Hk works
+    here), positions int32 ``[N]``, cos/sin ``[max_pos, rot_half]`` in Q's dtype.
+    ``check_positions=True`` synchronises and raises if a position was outside the table
+    (such rows are skipped by the kernel either way).
+    """
+    for t, n in ((Q, "Q"), (K, "K"), (positions, "positions"), (cos, "cos"), (sin, "sin")):
+        _check_input(t, n)
+    _int32(positions, "positions")
+    dt = _dtype_code(Q, "Q")
+    if K.dtype != Q.dtype or cos.dtype != Q.dtype or sin.dtype != Q.dtype:
+        raise RuntimeError("K, cos and sin must have Q's dtype")
+    n_tokens = Q.size(0)
+    rot_half = cos.size(1)
+    if Q.size(1) % head_dim or K.size(1) % head_dim:
+        raise RuntimeError("Q.size(1) and K.size(1) must be multiples of head_dim")
+    flag = torch.zeros(1, dtype=torch.int32, device=Q.device) if check_positions else None
+    with torch.cuda.device(Q.device):
+        check(lib.attn_b200_rope_inplace(Q.data_ptr(), K.data_ptr(), positions.data_ptr(), cos.data_ptr(),
+                                         sin.data_ptr(), n_tokens, Q.size(1) // head_dim, K.size(1) // head_dim,
+                                         head_dim, rot_half, cos.size(0), dt, _ptr(flag), _stream()),
+              "rotary_embedding_inplace")
+    if flag is not None and int(flag.item()) & _lib.FLAG_BAD_POSITION:
+        raise RuntimeError("rotary_embedding_inplace: a position is outside [0, cos.size(0))")
+
+
+# ----------------------------------------------------------------------------------------------
+# paged decode
+# ----------------------------------------------------------------------------------------------
+def _kv_code(kc: torch.Tensor, q: torch.Tensor) -> int:
+    if kc.dtype in _FP8 or kc.dtype == torch.uint8:
+        if q.dtype not in (torch.float16, torch.bfloat16):
+            raise RuntimeError("FP8 KV needs float16 or bfloat16 queries")
+        return _lib.E4M3
+    if kc.dtype != q.dtype:
+        raise RuntimeError("K_cache/V_cache must have Q's dtype (or be float8_e4m3fn)")
+    return _DT[q.dtype]
+
+
+def pick_chunk(B: int, H: int, D: int, n_tokens: int, device) -> int:
+    return lib.attn_b200_paged_decode_pick_chunk(B, H, D, n_tokens, sm_count(device))
+
+
+def decode_workspace_bytes(B: int, H: int, D: int, n_tokens: int, chunk: int) -> int:
+    return lib.attn_b200_paged_decode_workspace_bytes(B, H, D, n_tokens, chunk)
+
+
+def paged_kv_attention_forward(Q, K, V, K_cache, V_cache, cache_indices, offsets, num_heads: int, *,
+                               scale: Optional[float] = None, return_sp: bool = True,
+                               chunk: Optional[int] = None, k_scale=None, v_scale=None,
+                               max_context_len: Optional[int] = None, workspace: Optional[torch.Tensor] = None,
+                               out: Optional[torch.Tensor] = None,
+                               err_flag: Optional[torch.Tensor] = None, stages: int = 3) -> List[torch.Tensor]:
+    """KV-paged single-query attention, block_size = 1 (paged_attention_kernel.cu:237-294).
+
+    Q, K, V ``[B, H*D]`` (the current token); K_cache, V_cache ``[slots, H*D]``; cache_indices
+    int32 ``[T]``; offsets int32 ``[B]`` inclusive cumulative context lengths.  Returns
+    ``[S, P, O]`` with S, P float64 ``[B, H, max_ctx+1]`` like the reference.  ``scale`` defaults
+    to ``1/sqrt(D)`` as in the reference launcher (:269).
+
+    Keyword-only extensions: ``return_sp=False`` skips S/P (empty placeholders are returned) and
+    with it the one device->host sync needed to size them (``max_context_len`` also avoids it);
+    ``k_scale``/``v_scale`` float32 ``[H]`` select the FP8-e4m3 KV path; ``chunk`` overrides the
+    split-KV chunk length; ``workspace``/``out`` let a caller reuse buffers; ``stages`` (1 = partial
+    kernel only, 2 = combine only, 3 = both) exists so a benchmark can time the two kernels apart.
+    """
+    for t, n in ((Q, "Q"), (K, "K"), (V, "V"), (K_cache, "K_cache"), (V_cache, "V_cache")):
+        _check_input(t, n)
+    _int32(cache_indices, "cache_indices")
+    _int32(offsets, "offsets")
+    qd = _dtype_code(Q, "Q")
+    kvd = _kv_code(K_cache, Q)
+    if V_cache.dtype != K_cache.dtype or K.dtype != Q.dtype or V.dtype != Q.dtype:
+        raise RuntimeError("dtype mismatch between Q/K/V or K_cache/V_cache")
+    B, dim = Q.shape
+    if dim % num_heads:
+        raise RuntimeError("Q.size(1) must be a multiple of num_heads")
+    H, D = num_heads, dim // num_heads
+    if offsets.numel() != B:
+        raise RuntimeError("offsets must have one entry per sequence")
+    if K_cache.size(1) != dim or V_cache.shape != K_cache.shape:
+        raise RuntimeError("K_cache/V_cache must be [slots, H*D]")
+    T = cache_indices.numel()
+    if scale is None:
+        scale = 1.0 / math.sqrt(D)
+    if kvd == _lib.E4M3:
+        if k_scale is None or v_scale is None:
+            raise RuntimeError("FP8 KV needs k_scale and v_scale (float32 [H])")
+        for t, n in ((k_scale, "k_scale"), (v_scale, "v_scale")):
+            _check_input(t, n)
+            if t.dtype != torch.float32 or t.numel() != H:
+                raise RuntimeError(f"{n} must be float32 [H]")
+    dev = Q.device
+    with torch.cuda.device(dev):
+        if chunk is None:
+            chunk = pick_chunk(B, H, D, T, dev)
+        need = decode_workspace_bytes(B, H, D, T, chunk)
+        if workspace is None:
+            workspace = torch.empty(need, dtype=torch.uint8, device=dev)
+        elif workspace.numel() * workspace.element_size() < need:
+            raise RuntimeError(f"workspace too small: {need} bytes needed")
+        O = torch.empty_like(Q) if out is None else out
+        if return_sp:
+            if max_context_len is None:
+                lens = torch.diff(offsets, prepend=offsets.new_zeros(1))
+                max_context_len = int(lens.max().item()) if B > 0 else 0
+            S = torch.zeros(B, H, max_context_len + 1, dtype=torch.float64, device=dev)
+            P = torch.zeros_like(S)
+            stride = max_context_len + 1
+        else:
+            S = torch.empty(0, dtype=torch.float64, device=dev)
+            P = torch.empty(0, dtype=torch.float64, device=dev)
+            stride = 0
+        check(lib.attn_b200_paged_decode(
+            Q.data_ptr(), K.data_ptr(), V.data_ptr(), K_cache.data_ptr(), V_cache.data_ptr(),
+            cache_indices.data_ptr(), offsets.data_ptr(), O.data_ptr(), workspace.data_ptr(),
+            workspace.numel() * workspace.element_size(),
+            S.data_ptr() if return_sp else None, P.data_ptr() if return_sp else None, stride,
+            B, H, D, T, K_cache.size(0), 0, chunk, float(scale), _ptr(k_scale), _ptr(v_scale), qd, kvd, stages,
+            _ptr(err_flag), _stream()), "paged_kv_attention_forward")
+    return [S, P, O]
+
+
+def paged_decode_partial(Q, K_cache, V_cache, cache_indices, offsets, num_heads: int, *,
+                         scale: Optional[float] = None, chunk: Optional[int] = None, k_scale=None, v_scale=None,
+                         workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One KV-split rank's share of a decode: float32 ``[B, H, D+2]`` rows ``[o[D], m, l]``
+    (un-normalised numerator, log2-domain maximum, denominator) over the rank's own tokens,
+    without the new token.  Feed the gathered rows of all ranks to :func:`lse_combine`."""
+    for t, n in ((Q, "Q"), (K_cache, "K_cache"), (V_cache, "V_cache")):
+        _check_input(t, n)
+    _int32(cache_indices, "cache_indices")
+    _int32(offsets, "offsets")
+    qd = _dtype_code(Q, "Q")
+    kvd = _kv_code(K_cache, Q)
+    B, dim = Q.shape
+    H, D = num_heads, dim // num_heads
+    T = cache_indices.numel()
+    if scale is None:
+        scale = 1.0 / math.sqrt(D)
+    dev = Q.device
+    with torch.cuda.device(dev):
+        if chunk is None:
+            chunk = pick_chunk(B, H, D, T, dev)
+        need = decode_workspace_bytes(B, H, D, T, chunk)
+        if workspace is None:
+            workspace = torch.empty(need, dtype=torch.uint8, device=dev)
+        part = torch.empty(B, H, D + 2, dtype=torch.float32, device=dev)
+        check(lib.attn_b200_paged_decode_partial(
+            Q.data_ptr(), K_cache.data_ptr(), V_cache.data_ptr(), cache_indices.data_ptr(), offsets.data_ptr(),
+            part.data_ptr(), workspace.data_ptr(), workspace.numel() * workspace.element_size(), B, H, D, T,
+            K_cache.size(0), chunk, float(scale), _ptr(k_scale), _ptr(v_scale), qd, kvd, None, _stream()),
+            "paged_decode_partial")
+    return part
+
+
+def lse_combine(parts, Q, K=None, V=None, *, num_heads: int, scale: Optional[float] = None) -> torch.Tensor:
+    """Fold ``parts`` float32 ``[n_parts, B, H, D+2]`` and, if given, the new token (K, V) into
+    the final ``[B, H*D]`` output in Q's dtype."""
+    _check_input(parts, "parts")
+    _check_input(Q, "Q")
+    n_parts, B, H, RS = parts.shape
+    D = RS - 2
+    if H != num_heads or Q.shape != (B, H * D) or parts.dtype != torch.float32:
+        raise RuntimeError("parts must be float32 [n_parts, B, H, D+2] matching Q [B, H*D]")
+    if scale is None:
+        scale = 1.0 / math.sqrt(D)
+    O = torch.empty_like(Q)
+    with torch.cuda.device(Q.device):
+        check(lib.attn_b200_lse_combine(parts.data_ptr(), n_parts, Q.data_ptr(), _ptr(K), _ptr(V), O.data_ptr(),
+                                        B, H, D, float(scale), _dtype_code(Q, "Q"), _stream()), "lse_combine")
+    return O
+
+
+# ----------------------------------------------------------------------------------------------
+# single query over a contiguous cache
+# ----------------------------------------------------------------------------------------------
+def kv_attention_forward(Q, K, V, K_cache, V_cache, num_heads: int, *, scale: float = 1.0,
+                         return_sp: bool = True) -> List[torch.Tensor]:
+    """Single-query attention over a contiguous ``[B, ctx, H*D]`` cache plus the new token
+    (attention_kernel.cu:231-280).  Scores are NOT scaled, as in the reference kernel (:129,143);
+    pass ``scale=`` to change that.  S, P are ``[B, H, ctx+1]`` in the input dtype."""
+    for t, n in ((Q, "Q"), (K, "K"), (V, "V"), (K_cache, "K_cache"), (V_cache, "V_cache")):
+        _check_input(t, n)
+    qd = _dtype_code(Q, "Q")
+    if any(t.dtype != Q.dtype for t in (K, V, K_cache, V_cache)):
+        raise RuntimeError("all tensors must share Q's dtype")
+    B, dim = Q.shape
+    if dim % num_heads:
+        raise RuntimeError("Q.size(1) must be a multiple of num_heads")
+    H, D = num_heads, dim // num_heads
+    ctx = K_cache.size(1)
+    T = B * ctx
+    dev = Q.device
+    with torch.cuda.device(dev):
+        chunk = pick_chunk(B, H, D, T, dev)
+        need = decode_workspace_bytes(B, H, D, T, chunk)
+        ws = torch.empty(need, dtype=torch.uint8, device=dev)
+        O = torch.empty_like(Q)
+        if return_sp:
+            S64 = torch.zeros(B, H, ctx + 1, dtype=torch.float64, device=dev)
+            P64 = torch.zeros_like(S64)
+        check(lib.attn_b200_paged_decode(
+            Q.data_ptr(), K.data_ptr(), V.data_ptr(), K_cache.data_ptr(), V_cache.data_ptr(), None, None,
+            O.data_ptr(), ws.data_ptr(), need, S64.data_ptr() if return_sp else None,
+            P64.data_ptr() if return_sp else None, ctx + 1 if return_sp else 0, B, H, D, T, max(T, 1), ctx, chunk,
+            float(scale), None, None, qd, qd, 3, None, _stream()), "kv_attention_forward")
+    if return_sp:
+        return [S64.to(Q.dtype), P64.to(Q.dtype), O]
+    e = torch.empty(0, dtype=Q.dtype, device=dev)
+    return [e, e.clone(), O]
+
+
+# ----------------------------------------------------------------------------------------------
+# packed causal prefill, dense masked attention
+# ----------------------------------------------------------------------------------------------
+def paged_attention_forward(Q, K, V, offsets, num_heads: int, *, scale: Optional[float] = None,
+                            return_sp: bool = True, max_seqlen: Optional[int] = None,
+                            out_dtype: Optional[torch.dtype] = None,
+                            force_generic: bool = False) -> List[torch.Tensor]:
+    """Causal attention over a packed ``[sum L, H*D]`` token buffer (paged_attention_kernel.cu:189-235).
+
+    ``offsets`` int32 ``[B]`` are inclusive cumulative lengths.  Returns ``[S, P, O]``; S, P are
+    ``[B, H, maxL, maxL]`` in the input dtype as in the reference unless ``return_sp=False``
+    (empty placeholders; required for the tensor-core path and for any large input).
+    ``out_dtype=torch.float32`` makes the tensor-core path store fp32 output.
+    """
+    for t, n in ((Q, "Q"), (K, "K"), (V, "V")):
+        _check_input(t, n)
+    _int32(offsets, "offsets")
+    dt = _dtype_code(Q, "Q")
+    if K.dtype != Q.dtype or V.dtype != Q.dtype or K.shape != Q.shape or V.shape != Q.shape:
+        raise RuntimeError("Q, K, V must share shape and dtype")
+    n_tokens, dim = Q.shape
+    if dim % num_heads:
+        raise RuntimeError("Q.size(1) must be a multiple of num_heads")
+    H, D = num_heads, dim // num_heads
+    B = offsets.numel()
+    if scale is None:
+        scale = 1.0 / math.sqrt(D)
+    dev = Q.device
+    with torch.cuda.device(dev):
+        if max_seqlen is None:
+            lens = torch.diff(offsets, prepend=offsets.new_zeros(1))
+            max_seqlen = int(lens.max().item()) if B > 0 else 0
+        out_f32 = out_dtype == torch.float32 and Q.dtype != torch.float32
+        O = torch.zeros(Q.shape, dtype=torch.float32 if out_f32 else Q.dtype, device=dev)
+        if return_sp:
+            S = torch.zeros(B, H, max_seqlen, max_seqlen, dtype=Q.dtype, device=dev)
+            P = torch.zeros_like(S)
+        else:
+            S = torch.empty(0, dtype=Q.dtype, device=dev)
+            P = torch.empty(0, dtype=Q.dtype, device=dev)
+        check(lib.attn_b200_varlen_prefill(
+            Q.data_ptr(), K.data_ptr(), V.data_ptr(), offsets.data_ptr(), O.data_ptr(),
+            S.data_ptr() if return_sp else None, P.data_ptr() if return_sp else None, B, n_tokens, max_seqlen, H, D,
+            float(scale), dt, int(out_f32), int(force_generic), None, _stream()), "paged_attention_forward")
+    return [S, P, O]
+
+
+def naive_attention_forward(Q, K, V, mask, num_heads: int, *, scale: Optional[float] = None,
+                            fill: float = 100000.0, return_sp: bool = True) -> List[torch.Tensor]:
+    """Dense masked MHA (attention_kernel.cu:187-229): Q, K, V ``[B, L, H*D]``, mask ``[B, L, L]``
+    (1 keeps, 0 masks; scores get ``(mask-1)*fill`` added).  Returns ``[S, P, O]``."""
+    for t, n in ((Q, "Q"), (K, "K"), (V, "V"), (mask, "mask")):
+        _check_input(t, n)
+    dt = _dtype_code(Q, "Q")
+    if any(t.dtype != Q.dtype for t in (K, V, mask)):
+        raise RuntimeError("Q, K, V and mask must share a dtype")
+    B, L, dim = Q.shape
+    if dim % num_heads:
+        raise RuntimeError("Q.size(2) must be a multiple of num_heads")
+    H, D = num_heads, dim // num_heads
+    if scale is None:
+        scale = 1.0 / math.sqrt(D)
+    dev = Q.device
+    with torch.cuda.device(dev):
+        O = torch.empty_like(Q)
+        if return_sp:
+            S = torch.zeros(B, H, L, L, dtype=Q.dtype, device=dev)
+            P = torch.zeros_like(S)
+        else:
+            S = torch.empty(0, dtype=Q.dtype, device=dev)
+            P = torch.empty(0, dtype=Q.dtype, device=dev)
+        check(lib.attn_b200_dense_attention(
+            Q.data_ptr(), K.data_ptr(), V.data_ptr(), mask.data_ptr(), O.data_ptr(),
+            S.data_ptr() if return_sp else None, P.data_ptr() if return_sp else None, B, L, H, D, float(scale),
+            float(fill), dt, _stream()), "naive_attention_forward")
+    return [S, P, O]

@@ -1,0 +1,155 @@
+/*
+ * attn_b200.h — C ABI of libattn_b200.so: sm_100a kernels for the attention hot path of
+ * ita9naiwa/attention-impl (paged single-query decode, packed causal prefill, dense masked
+ * attention, single-query over a contiguous cache, rotary embedding).
+ *
+ * Conventions
+ *  - Every pointer is a DEVICE pointer on the current CUDA device unless stated otherwise.
+ *  - Data tensors are dense row-major.  "[rows, H*D]" means one row per token with all heads
+ *    contiguous (the reference's layout, paged_attention_kernel.cu:132).
+ *  - `stream` is a cudaStream_t passed as void*; all work is enqueued on it, no call synchronises.
+ *  - Return value: 0 = ok; negative = argument error (ATTN_B200_E*); positive = cudaError_t of
+ *    a failed launch.  attn_b200_strerror() renders either.
+ *  - The library owns no memory: outputs and scratch are allocated by the caller.
+ *  - `err_flag` (optional, may be NULL): device int32 that kernels OR a bit into when they meet an
+ *    out-of-range slot / position; the offending row is skipped, never dereferenced.
+ */
+#ifndef ATTN_B200_H
+#define ATTN_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(ATTN_B200_BUILD) && defined(__GNUC__)
+#define ATTN_B200_API __attribute__((visibility("default")))
+#else
+#define ATTN_B200_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* element types */
+enum {
+    ATTN_B200_F16 = 0,
+    ATTN_B200_BF16 = 1,
+    ATTN_B200_F32 = 2,
+    ATTN_B200_E4M3 = 3 /* KV pools only */
+};
+
+/* argument errors */
+enum {
+    ATTN_B200_EINVAL = -1,       /* null pointer / non-positive size */
+    ATTN_B200_EDTYPE = -2,       /* unsupported element type for this entry point */
+    ATTN_B200_ESHAPE = -3,       /* head_dim / rot_half / chunk not supported */
+    ATTN_B200_EWORKSPACE = -4,   /* scratch buffer too small */
+    ATTN_B200_ETOOLARGE = -5     /* size beyond a documented limit */
+};
+
+/* bits a kernel may set in *err_flag */
+enum {
+    ATTN_B200_FLAG_BAD_SLOT = 1,     /* cache_indices entry outside [0, n_slots) */
+    ATTN_B200_FLAG_BAD_POSITION = 2, /* positions entry outside [0, max_pos) */
+    ATTN_B200_FLAG_BAD_OFFSETS = 4   /* offsets not non-decreasing / beyond n_tokens */
+};
+
+ATTN_B200_API const char* attn_b200_strerror(int status);
+/* ABI version of this header; bumped on any signature change. */
+ATTN_B200_API int attn_b200_abi_version(void);
+
+/* ------------------------------------------------------------------------------------------
+ * Rotary embedding, in place on q and k.
+ * Replaces rotary_embedding_inplace (rotary_embedding.cu:40-77, kernel :10-36).
+ *   q [n_tokens, n_heads_q*head_dim], k [n_tokens, n_heads_k*head_dim]   (dtype)
+ *   positions int32 [n_tokens]; cos, sin [max_pos, rot_half] (dtype)
+ * For d < rot_half:  x[d]        <- fl(fl(x[d]*c) + fl(-x[d+rot_half]*s))
+ *                    x[d+rot_half] <- fl(fl(x[d+rot_half]*c) + fl(x[d]*s)),  c,s = cos/sin[pos, d]
+ * each product and the sum rounded to `dtype` separately (no FMA contraction), dims >= 2*rot_half
+ * untouched.  k may be NULL (n_heads_k ignored).  dtype: F16, BF16, F32.
+ */
+ATTN_B200_API int attn_b200_rope_inplace(void* q, void* k, const int32_t* positions, const void* cos, const void* sin,
+                           int64_t n_tokens, int n_heads_q, int n_heads_k, int head_dim, int rot_half,
+                           int64_t max_pos, int dtype, int32_t* err_flag, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * KV-paged single-query decode (block_size = 1 slot table).
+ * Replaces paged_kv_attention_forward (paged_attention_kernel.cu:237-294, kernel :100-187) and,
+ * with slots == NULL and offsets == NULL, kv_attention_forward (attention_kernel.cu:231-280,
+ * kernel :96-185).
+ *   q, k_new, v_new, out  [B, H*D]            (q_dtype: F16, BF16, F32)
+ *   k_cache, v_cache      [n_slots, H*D]      (kv_dtype: q_dtype, or E4M3 with F16/BF16 q)
+ *   slots   int32 [n_tokens]  slot of the t-th token of the concatenated sequences, or NULL
+ *                             for the identity table (token t lives in row t)
+ *   offsets int32 [B]         INCLUSIVE cumulative context lengths, or NULL for a uniform
+ *                             length `uniform_ctx` (then n_tokens == B*uniform_ctx)
+ *   k_scale, v_scale float [H] per-head dequantisation scales (E4M3 only, else NULL)
+ *   S, P    double [B, H, sp_stride]  optional (both or neither): scaled scores and
+ *           probabilities, the new token's entry at index ctx_b; entries beyond are NOT written
+ *           (pass zeroed buffers, as the reference does).  sp_stride >= max ctx + 1.
+ * Per (b, h): softmax over the ctx_b cached tokens plus the new token (k_new, v_new) of
+ * `scale * <q, k>`; out = sum p * v.  Context tokens are cut into chunks of `chunk` tokens on a
+ * global grid; each (chunk, head) is reduced by one warp into an (m, l, o) partial in
+ * `workspace`, then attn_b200_lse_combine-style reduction folds the partials and the new token.
+ * `chunk` must be a multiple of 32 in [32, 2048]; use attn_b200_paged_decode_pick_chunk.
+ * `workspace` needs attn_b200_paged_decode_workspace_bytes(...) bytes, 16-byte aligned; it needs
+ * no initialisation and holds nothing between calls.
+ * `stages`: 3 runs both kernels (the normal call); 1 runs only the partial kernel, 2 only the
+ * combine kernel (same arguments) so that a profiler or benchmark can put events between them.
+ */
+ATTN_B200_API int attn_b200_paged_decode(const void* q, const void* k_new, const void* v_new, const void* k_cache,
+                           const void* v_cache, const int32_t* slots, const int32_t* offsets, void* out,
+                           void* workspace, size_t workspace_bytes, double* S, double* P, int64_t sp_stride,
+                           int B, int H, int D, int64_t n_tokens, int64_t n_slots, int uniform_ctx, int chunk,
+                           float scale, const float* k_scale, const float* v_scale, int q_dtype, int kv_dtype,
+                           int stages, int32_t* err_flag, void* stream);
+
+ATTN_B200_API size_t attn_b200_paged_decode_workspace_bytes(int B, int H, int D, int64_t n_tokens, int chunk);
+/* Heuristic chunk length: enough (chunk, head-group) work items to fill `sm_count` SMs. */
+ATTN_B200_API int attn_b200_paged_decode_pick_chunk(int B, int H, int D, int64_t n_tokens, int sm_count);
+
+/* Same first stage as attn_b200_paged_decode, but the second stage writes, per (b, h), one
+ * partial row  [m (log2 domain), l, o[D] (un-normalised)]  of D+2 floats into
+ * part_out [B, H, D+2] instead of the final output, and does NOT fold the new token.  This is
+ * what one rank of a KV-split group computes over its own slice of every sequence.
+ * No counterpart in the reference (it has no split-KV). */
+ATTN_B200_API int attn_b200_paged_decode_partial(const void* q, const void* k_cache, const void* v_cache,
+                                   const int32_t* slots, const int32_t* offsets, float* part_out,
+                                   void* workspace, size_t workspace_bytes, int B, int H, int D,
+                                   int64_t n_tokens, int64_t n_slots, int chunk, float scale,
+                                   const float* k_scale, const float* v_scale, int q_dtype, int kv_dtype,
+                                   int32_t* err_flag, void* stream);
+
+/* Log-sum-exp combine of n_parts partial sets  parts [n_parts, B, H, D+2]  (layout above) plus
+ * the new token (k_new, v_new; may both be NULL to skip it) into out [B, H*D] (q_dtype).
+ * No counterpart in the reference. */
+ATTN_B200_API int attn_b200_lse_combine(const float* parts, int n_parts, const void* q, const void* k_new,
+                          const void* v_new, void* out, int B, int H, int D, float scale, int q_dtype,
+                          void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Packed (non-contiguous) causal prefill.
+ * Replaces paged_attention_forward (paged_attention_kernel.cu:189-235, kernel :15-98).
+ *   q, k, v, out [n_tokens, H*D] (dtype); offsets int32 [B] inclusive cumulative lengths;
+ *   max_len >= longest sequence (sizes the grid; rows beyond a sequence's end are skipped).
+ *   S, P optional [B, H, max_len, max_len] (dtype) — both or neither; only the generic path
+ *   writes them.  Key j is visible to query i of the same sequence iff j <= i.
+ * dtype F16/BF16 with D == 128 and S == NULL runs the tcgen05 tensor-core kernel (`out_f32`
+ * != 0 stores fp32 output instead of dtype); everything else runs the generic kernel.
+ */
+ATTN_B200_API int attn_b200_varlen_prefill(const void* q, const void* k, const void* v, const int32_t* offsets, void* out,
+                             void* S, void* P, int B, int64_t n_tokens, int max_len, int H, int D,
+                             float scale, int dtype, int out_f32, int force_generic, int32_t* err_flag,
+                             void* stream);
+
+/* Dense masked attention.  Replaces naive_attention_forward (attention_kernel.cu:187-229,
+ * kernel :15-94).  q, k, v, out [B, L, H*D]; mask [B, L, L] (dtype) or NULL; scores are
+ * scale*<q,k> + (mask-1)*fill;  S, P optional [B, H, L, L] (dtype). */
+ATTN_B200_API int attn_b200_dense_attention(const void* q, const void* k, const void* v, const void* mask, void* out,
+                              void* S, void* P, int B, int L, int H, int D, float scale, float fill,
+                              int dtype, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ATTN_B200_H */

@@ -1,0 +1,179 @@
+"""GPU: KV-paged decode and single-query attention through the drop-in API vs the CPU oracle.
+
+Tolerance: <= 2e-3 max-abs on O for fp16/bf16 inputs against the oracle evaluated in fp32 on the
+same (rounded) inputs; the same-dtype oracle (the reference's literal torch math) is checked with
+the dtype's own rounding added.  FP8 KV: <= 2e-2 relative against the oracle on dequantised KV.
+"""
+import math
+
+import pytest
+import torch
+
+from oracle import attention_oracle as orc
+from conftest import load_golden
+from helpers import decode_inputs, uniform_lens
+
+pytestmark = pytest.mark.gpu
+
+TOL16 = 2e-3
+
+
+def _gpu(*ts):
+    return [t.cuda() for t in ts]
+
+
+def _decode(Q, K, V, Kc, Vc, ci, off, H, **kw):
+    import lm_ops
+    S, P, O = lm_ops.paged_kv_attention_forward(*_gpu(Q, K, V, Kc, Vc, ci, off), H, **kw)
+    torch.cuda.synchronize()
+    return S.cpu(), P.cpu(), O.cpu()
+
+
+@pytest.mark.parametrize("tag", ["paged_ref_shape", "paged_f32"])
+def test_paged_decode_golden_unscaled(tag):
+    """The reference's own torch function (unscaled, two cached tokens per sequence)."""
+    g = load_golden(tag)
+    S, P, O = _decode(g["Q"], g["K"], g["V"], g["K_cache"], g["V_cache"], g["cache_indices"], g["offsets"],
+                      int(g["num_heads"]), scale=1.0)
+    assert (S.float() - g["S"]).abs().max() < 1e-5
+    assert (P.float() - g["P"]).abs().max() < 1e-5
+    assert (O - g["O"]).abs().max() < 1e-5
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_paged_decode_small_batch_workload(dtype):
+    """B=8, H=32, D=128, ctx ~ U[128,1024], 16384-slot pool, scale 1/sqrt(128)."""
+    B, H, D = 8, 32, 128
+    lens = uniform_lens(B, 128, 1024, seed=1)
+    inp = decode_inputs(B, H, D, lens, 16384, dtype, seed=1001)
+    S, P, O = _decode(*inp, H)
+    S32, P32, O32 = orc.paged_decode(*inp, H, compute_dtype=torch.float32)
+    tol = TOL16 if dtype == torch.float16 else 8e-3   # bf16 output rounding: half-ulp 3.9e-3 at |O|<1
+    assert (O.float() - O32.float()).abs().max() <= tol
+    # fp32-evaluated comparison without the output rounding of the oracle
+    _, _, O64 = orc.paged_decode(*[t.double() if t.is_floating_point() else t for t in inp], H)
+    assert (O.double() - O64).abs().max() <= (TOL16 if dtype == torch.float16 else 8e-3)
+    assert (S - S32).abs().max() < 2e-4 * math.sqrt(D)
+    assert (P - P32).abs().max() < 1e-4
+    # the reference's literal same-dtype torch math
+    _, _, Oh = orc.paged_decode(*inp, H)
+    assert (O.float() - Oh.float()).abs().max() <= 4 * tol
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("H,D", [(2, 2), (4, 16), (8, 64), (3, 40), (16, 128), (4, 256), (1, 128)])
+@pytest.mark.parametrize("chunk", [None, 32, 64])
+def test_paged_decode_ragged_shapes(dtype, H, D, chunk):
+    """Ragged lengths incl. empty sequences, length 1, chunk-boundary lengths."""
+    lens = [0, 1, 31, 32, 33, 64, 0, 100, 257, 5]
+    B = len(lens)
+    inp = decode_inputs(B, H, D, lens, 1024, dtype, seed=H * 1000 + D)
+    S, P, O = _decode(*inp, H, chunk=chunk)
+    S32, P32, O32 = orc.paged_decode(*inp, H, compute_dtype=torch.float32)
+    tol = {torch.float16: TOL16, torch.bfloat16: 1.6e-2, torch.float32: 2e-5}[dtype]
+    assert (O.float() - O32.float()).abs().max() <= tol
+    assert (P - P32).abs().max() < 2e-4
+    # tail beyond ctx_b + 1 stays zero like the reference's zero-initialised buffers
+    for b, n in enumerate(lens):
+        assert S[b, :, n + 1:].abs().sum() == 0 and P[b, :, n + 1:].abs().sum() == 0
+    assert torch.allclose(P.sum(-1), torch.ones(B, H, dtype=torch.float64), atol=1e-5)
+
+
+def test_paged_decode_without_sp_matches_with_sp():
+    lens = uniform_lens(6, 10, 700, seed=4)
+    inp = decode_inputs(6, 8, 128, lens, 4096, torch.float16, seed=77)
+    _, _, O1 = _decode(*inp, 8)
+    S, P, O2 = _decode(*inp, 8, return_sp=False)
+    assert S.numel() == 0 and P.numel() == 0
+    assert torch.equal(O1, O2)
+
+
+def test_paged_decode_chunk_invariance():
+    """Split-KV must not change the answer beyond fp32 reassociation."""
+    lens = uniform_lens(4, 900, 3000, seed=9)
+    inp = decode_inputs(4, 8, 128, lens, 16384, torch.float16, seed=5)
+    outs = [_decode(*inp, 8, return_sp=False, chunk=c)[2].float() for c in (32, 256, 2048)]
+    assert (outs[0] - outs[1]).abs().max() < 1e-3 and (outs[0] - outs[2]).abs().max() < 1e-3
+
+
+def test_paged_decode_fp8_kv():
+    """e4m3 KV with per-head absmax scales: <= 2e-2 relative vs the oracle on dequantised KV."""
+    import lm_ops
+    B, H, D = 6, 8, 128
+    lens = uniform_lens(B, 300, 2000, seed=11)
+    Q, K, V, Kc, Vc, ci, off = decode_inputs(B, H, D, lens, 16384, torch.float16, seed=12)
+    K8, ks = orc.quantize_e4m3_per_head(Kc, H)
+    V8, vs = orc.quantize_e4m3_per_head(Vc, H)
+    Kd = orc.dequantize_e4m3_per_head(K8, ks, H)
+    Vd = orc.dequantize_e4m3_per_head(V8, vs, H)
+    _, _, Oref = orc.paged_decode(Q.float(), K.float(), V.float(), Kd, Vd, ci, off, H)
+    for kw in ({}, {"chunk": 64}):
+        _, _, O = lm_ops.paged_kv_attention_forward(Q.cuda(), K.cuda(), V.cuda(), K8.cuda(), V8.cuda(), ci.cuda(),
+                                                    off.cuda(), H, return_sp=False, k_scale=ks.cuda(),
+                                                    v_scale=vs.cuda(), **kw)
+        rel = (O.cpu().float() - Oref).norm() / Oref.norm()
+        assert rel <= 2e-2
+        assert (O.cpu().float() - Oref).abs().max() <= 2e-2 * Oref.abs().max()
+
+
+def test_paged_decode_bad_slot_is_flagged():
+    import lm_ops
+    Q, K, V, Kc, Vc, ci, off = decode_inputs(2, 8, 128, [40, 50], 256, torch.float16, seed=3)
+    ci[7] = 100000
+    ci[60] = -5
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    _, _, O = lm_ops.paged_kv_attention_forward(*_gpu(Q, K, V, Kc, Vc, ci, off), 8, return_sp=False, err_flag=flag)
+    assert int(flag.item()) & 1
+    assert torch.isfinite(O).all()
+
+
+def test_partial_plus_combine_equals_decode():
+    """KV split into 3 slices per sequence -> partials -> combine == one-shot decode."""
+    import attention_impl_b200 as A
+    B, H, D, G = 5, 8, 128, 3
+    lens = uniform_lens(B, 50, 900, seed=21)
+    Q, K, V, Kc, Vc, ci, off = decode_inputs(B, H, D, lens, 8192, torch.float16, seed=22)
+    _, _, O_full = _decode(Q, K, V, Kc, Vc, ci, off, H, return_sp=False)
+    parts = []
+    begs = [0] + off.tolist()[:-1]
+    for r in range(G):
+        idx, ln = [], []
+        for b, n in enumerate(lens):
+            lo, hi = n * r // G, n * (r + 1) // G
+            idx.append(ci[begs[b] + lo: begs[b] + hi])
+            ln.append(hi - lo)
+        ci_r = torch.cat(idx)
+        off_r = torch.tensor(ln).cumsum(0).int()
+        parts.append(A.paged_decode_partial(Q.cuda(), Kc.cuda(), Vc.cuda(), ci_r.cuda(), off_r.cuda(), H))
+    O = A.lse_combine(torch.stack(parts).contiguous(), Q.cuda(), K.cuda(), V.cuda(), num_heads=H)
+    assert (O.cpu().float() - O_full.float()).abs().max() < 1e-3
+
+
+@pytest.mark.parametrize("tag", ["single_f32", "single_f16"])
+def test_single_query_golden(tag):
+    import lm_ops
+    g = load_golden(tag)
+    S, P, O = lm_ops.single_query_attention(*_gpu(g["Q"], g["K"], g["V"], g["K_cache"], g["V_cache"]),
+                                            int(g["num_heads"]))
+    tol = 1e-5 if g["Q"].dtype == torch.float32 else 2e-3
+    assert (O.cpu().float() - g["O"].float()).abs().max() <= tol
+    assert (P.cpu().float() - g["P"].float()).abs().max() <= tol
+    assert (S.cpu().float() - g["S"].float()).abs().max() <= tol * 4
+
+
+@pytest.mark.parametrize("batch_size", [1, 4, 8])
+@pytest.mark.parametrize("context_size", [256, 512])
+@pytest.mark.parametrize("dim", [32, 64, 256])
+@pytest.mark.parametrize("num_heads", [1, 4, 8])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
+def test_single_query_reference_matrix(batch_size, context_size, dim, num_heads, dtype):
+    """The reference's parameter grid (tests/test_single_query_attention.py:35-39), with non-zero
+    caches, num_heads actually passed, and the result asserted."""
+    import lm_ops
+    gen = torch.Generator().manual_seed(batch_size * 7 + dim)
+    Q, K, V = ((torch.randn(batch_size, dim, generator=gen) * 0.1).to(dtype) for _ in range(3))
+    Kc, Vc = ((torch.randn(batch_size, context_size, dim, generator=gen) * 0.1).to(dtype) for _ in range(2))
+    S1, P1, O1 = orc.single_query(Q, K, V, Kc, Vc, num_heads, compute_dtype=torch.float32)
+    S2, P2, O2 = lm_ops.single_query_attention(*_gpu(Q, K, V, Kc, Vc), num_heads)
+    assert torch.allclose(O1.float(), O2.cpu().float(), atol=1e-2)     # the reference's tolerance
+    assert (O1.float() - O2.cpu().float()).abs().max() <= (2e-3 if dtype == torch.float16 else 1e-5)
