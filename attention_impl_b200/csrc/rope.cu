@@ -150,13 +150,13 @@ extern "C" int attn_b200_rope_inplace(void* q, void* k, const int32_t* positions
                                       const void* sin, int64_t n_tokens, int n_heads_q, int n_heads_k,
                                       int head_dim, int rot_half, int64_t max_pos, int dtype, int32_t* err_flag,
                                       void* stream) {
+    if (n_tokens == 0) return 0;
     if (!q || !positions || !cos || !sin || n_tokens < 0 || n_heads_q <= 0 || head_dim <= 0 || rot_half <= 0 ||
         max_pos <= 0)
         return ATTN_B200_EINVAL;
     if (2 * rot_half > head_dim) return ATTN_B200_ESHAPE;
     if (!k) n_heads_k = 0;
     if (n_heads_k < 0) return ATTN_B200_EINVAL;
-    if (n_tokens == 0) return 0;
     cudaStream_t st = (cudaStream_t)stream;
     switch (dtype) {
         case ATTN_B200_F16:
