@@ -343,9 +343,10 @@ def run_b200(args, cfg, lens):
         dist.destroy_process_group()
 
 
-# dram bytes moved per algorithmic byte by the partial kernel, from the ncu capture summarised in
-# profiles/ (None until a capture exists)
-DECODE_TRAFFIC_RATIO = None
+# dram__bytes_read.sum + dram__bytes_write.sum per algorithmic byte of the partial kernel, from the
+# ncu capture of a 5.3 GB case of this workload (profiles/paged_decode_fast_kernel_small_case_ncu.md);
+# every row is read once, so traffic grows in proportion to the tokens processed.
+DECODE_TRAFFIC_RATIO = 1.0017
 
 
 def cpu_baseline_and_parity(A, cfg, lens, Q, K, V, Kc, Vc, ci, off, H, dev):
