@@ -127,6 +127,28 @@ ATTN_B200_API int attn_b200_lse_combine(const float* parts, int n_parts, const v
                           const void* v_new, void* out, int B, int H, int D, float scale, int q_dtype,
                           void* stream);
 
+/* Paged decode that allocates nothing and needs no scratch from the caller.
+ * (No counterpart in the reference: its launcher allocates S, P and O itself with torch::zeros.)
+ * For hosts that cannot call cudaMalloc — an engine that gave all free HBM to its own KV pool, or
+ * a decode loop that cannot take the device-wide synchronisation an allocation implies.  Same
+ * arguments and result as attn_b200_paged_decode without workspace/S/P/uniform_ctx/stages; the
+ * split-KV partial rows go to a fixed ATTN_B200_STATIC_SCRATCH_BYTES array inside the library's
+ * device image (every device that loads the library holds it until the process exits).
+ *  - Returns ATTN_B200_ETOOLARGE when attn_b200_paged_decode_workspace_bytes(B, H, D, n_tokens,
+ *    chunk) exceeds ATTN_B200_STATIC_SCRATCH_BYTES; a larger `chunk` (up to 2048) lowers the need.
+ *  - The first call on each device looks the array's device address up (cudaGetSymbolAddress, with
+ *    that device current) and keeps it; make that first call outside any stream capture.
+ *  - All calls on a device share the one array.  Nothing in it has to be cleared between calls (a
+ *    call only reads rows it wrote itself), but two calls that overlap on the GPU — different
+ *    streams, no ordering between them — race on it: serialise them.
+ *  - Calls no cudaMalloc/cudaFree and no allocating library routine. */
+#define ATTN_B200_STATIC_SCRATCH_BYTES (16u << 20)
+ATTN_B200_API int attn_b200_paged_decode_static_scratch(
+    const void* q, const void* k_new, const void* v_new, const void* k_cache, const void* v_cache,
+    const int32_t* slots, const int32_t* offsets, void* out, int B, int H, int D, int64_t n_tokens,
+    int64_t n_slots, int chunk, float scale, const float* k_scale, const float* v_scale, int q_dtype,
+    int kv_dtype, int32_t* err_flag, void* stream);
+
 /* ------------------------------------------------------------------------------------------
  * Packed (non-contiguous) causal prefill.
  * Replaces paged_attention_forward (paged_attention_kernel.cu:189-235, kernel :15-98).
