@@ -13,7 +13,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "lib", "libattn_b200.so")
 
 F16, BF16, F32, E4M3 = 0, 1, 2, 3
-FLAG_BAD_SLOT, FLAG_BAD_POSITION, FLAG_BAD_OFFSETS = 1, 2, 4
+FLAG_BAD_SLOT, FLAG_BAD_POSITION, FLAG_BAD_OFFSETS, FLAG_TIMEOUT = 1, 2, 4, 8
 ABI_VERSION = 1
 STATIC_SCRATCH_BYTES = 16 << 20
 

@@ -1,10 +1,429 @@
-// Tensor-core packed causal prefill (placeholder until the tcgen05 kernel lands).
+// Packed (varlen) causal prefill on the 5th-generation tensor cores: tcgen05.mma with TMEM
+// accumulators, operands staged in shared memory by TMA (cp.async.bulk.tensor, 128-byte swizzle).
+//
+// Semantics: paged_attention_kernel.cu:15-98 of the reference (per sequence slice of the packed
+// buffer, key j visible to query i iff j <= i, softmax of scale*QK^T, O = P V), evaluated flash
+// style: S and P never leave the SM.
+//
+// One CTA = one 128-row query tile of one (sequence, head); it walks the key tiles 0..t of that
+// sequence (t = its own tile index, the diagonal tile is masked).
+//   warp 4      TMA producer: Q once, then K and V tiles into a 2-stage ring
+//   warp 5      MMA issuer (one lane): S = Q K^T  (8 x tcgen05.mma 128x128x16, both operands
+//               K-major) into TMEM columns [0,128); after the softmax warps have written P:
+//               PV = P V (A = P from shared memory, B = V as an MN-major operand) into [128,256)
+//   warps 0-3   softmax: thread r owns row r (TMEM lane r): tcgen05.ld of the S row, running max
+//               and sum in the log2 domain, P rounded to the input type and stored to shared
+//               memory in the swizzled K-major layout, then the PV tile is read back and added to
+//               a register accumulator  o = o*alpha + pv.  Final o/l is stored straight to global.
+// Every mbarrier wait is bounded (about one second of SM clocks); on expiry the kernel raises
+// ATTN_B200_FLAG_TIMEOUT, all roles leave their loops, outstanding copies are given a bounded
+// wait, TMEM is freed and the CTA returns.  CTAs that start after a timeout exit at once.
+#include <cuda.h>
+#include <mutex>
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace attn {
-bool prefill_tc_supported(int, int) { return false; }
-int prefill_tc_launch(const void*, const void*, const void*, const int32_t*, void*, int, int64_t, int, int, int,
-                      float, int, int, int32_t*, cudaStream_t) {
-    return ATTN_B200_ESHAPE;
+
+namespace tc {
+
+constexpr int BM = 128;          // query rows per CTA
+constexpr int BN = 128;          // keys per tile
+constexpr int HD = 128;          // head_dim
+constexpr int SUB_BYTES = 128 * 128;   // one [128 rows x 64 elements] swizzled sub-tile (16-bit elements)
+constexpr int TILE_BYTES = 2 * SUB_BYTES;
+constexpr int STAGES = 2;
+constexpr int THREADS = 192;
+constexpr long long WAIT_CYCLES = 2000000000LL;
+
+struct SmemLayout {
+    alignas(1024) unsigned char q[TILE_BYTES];
+    alignas(1024) unsigned char p[TILE_BYTES];
+    alignas(1024) unsigned char k[STAGES][TILE_BYTES];
+    alignas(1024) unsigned char v[STAGES][TILE_BYTES];
+    alignas(8) unsigned long long q_full, s_full, p_full, o_full, o_empty;
+    unsigned long long k_full[STAGES], v_full[STAGES], kv_empty[STAGES];
+    unsigned int tmem_base;
+    int abort;
+};
+
+__device__ int g_abort;   // set by the first CTA whose wait expired; reset by the launcher
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(void* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
 }
+__device__ __forceinline__ void mbar_expect_tx(void* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(void* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(void* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false if the CTA is aborting or the limit ran out (then it raises the abort).
+__device__ __forceinline__ bool mbar_wait(void* bar, uint32_t parity, volatile int* cta_abort, int32_t* err_flag) {
+    if (mbar_try(bar, parity)) return true;
+    const long long t0 = clock64();
+    int spins = 0;
+    while (!mbar_try(bar, parity)) {
+        if (((++spins) & 63) == 0) {
+            if (*cta_abort) return false;
+            if (clock64() - t0 > WAIT_CYCLES) {
+                *cta_abort = 1;
+                atomicExch(&g_abort, 1);
+                if (err_flag) atomicOr(err_flag, ATTN_B200_FLAG_TIMEOUT);
+                return false;
+            }
+        }
+    }
+    return true;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, void* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc), "r"(0u) : "memory");
+}
+__device__ __forceinline__ void umma_commit(void* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// 32 consecutive fp32 columns of this thread's TMEM lane.
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
+    uint32_t* r = reinterpret_cast<uint32_t*>(v);
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor, 128-byte swizzle, sm_100 version field.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    return (uint64_t)((addr >> 4) & 0x3FFF) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16) |
+           ((uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32) | (1ull << 46) | (2ull << 61);
+}
+
+template <typename T> __device__ __forceinline__ uint32_t pack2(float a, float b);
+template <> __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
+    __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+
+struct Params {
+    const int32_t* offsets;
+    void* out;
+    int B, H;
+    int64_t n_tokens;
+    int n_qtiles;
+    float scale_log2;
+    int out_f32;
+    int32_t* err_flag;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(THREADS, 1)
+prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                  const __grid_constant__ CUtensorMap map_v, const Params p) {
+    extern __shared__ unsigned char smem_raw[];
+    SmemLayout& sm = *reinterpret_cast<SmemLayout*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int b = blockIdx.z, h = blockIdx.y;
+    const int t = p.n_qtiles - 1 - (int)blockIdx.x;        // heavy (late) tiles first
+    const int64_t seq_beg = b ? p.offsets[b - 1] : 0;
+    const int64_t seq_end = p.offsets[b];
+    if (seq_beg < 0 || seq_end < seq_beg || seq_end > p.n_tokens) {
+        if (p.err_flag && threadIdx.x == 0) atomicOr(p.err_flag, ATTN_B200_FLAG_BAD_OFFSETS);
+        return;
+    }
+    const int L = (int)(seq_end - seq_beg);
+    const int q0 = t * BM;
+    if (q0 >= L) return;
+    if (*(volatile int*)&g_abort) return;
+    const int n_kv = t + 1;
+    volatile int* cta_abort = &sm.abort;
+
+    if (threadIdx.x == 0) {
+        mbar_init(&sm.q_full, 1);
+        mbar_init(&sm.s_full, 1);
+        mbar_init(&sm.p_full, 128);
+        mbar_init(&sm.o_full, 1);
+        mbar_init(&sm.o_empty, 128);
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&sm.k_full[s], 1);
+            mbar_init(&sm.v_full[s], 1);
+            mbar_init(&sm.kv_empty[s], 1);
+        }
+        sm.abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 5) {   // TMEM: 256 columns (S and PV accumulators)
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(256));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = sm.tmem_base;
+    const int col0 = h * HD;
+
+    int issued_k[STAGES] = {0, 0};   // producer bookkeeping for the drain on abort
+    if (warp == 4) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            mbar_expect_tx(&sm.q_full, TILE_BYTES);
+            tma_load_2d(sm.q, &map_q, col0, (int)(seq_beg + q0), &sm.q_full);
+            tma_load_2d(sm.q + SUB_BYTES, &map_q, col0 + 64, (int)(seq_beg + q0), &sm.q_full);
+            for (int j = 0; j < n_kv; ++j) {
+                const int s = j & 1;
+                if (j >= STAGES && !mbar_wait(&sm.kv_empty[s], ((j - STAGES) >> 1) & 1, cta_abort, p.err_flag)) break;
+                const int row = (int)(seq_beg + (int64_t)j * BN);
+                mbar_expect_tx(&sm.k_full[s], TILE_BYTES);
+                tma_load_2d(sm.k[s], &map_k, col0, row, &sm.k_full[s]);
+                tma_load_2d(sm.k[s] + SUB_BYTES, &map_k, col0 + 64, row, &sm.k_full[s]);
+                mbar_expect_tx(&sm.v_full[s], TILE_BYTES);
+                tma_load_2d(sm.v[s], &map_v, col0, row, &sm.v_full[s]);
+                tma_load_2d(sm.v[s] + SUB_BYTES, &map_v, col0 + 64, row, &sm.v_full[s]);
+                issued_k[s] = j + 1;
+            }
+        }
+    } else if (warp == 5) {
+        // ------------------------------------------------------------------ MMA issuer
+        constexpr uint32_t fmt = sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
+        constexpr uint32_t idesc_qk = (1u << 4) | (fmt << 7) | (fmt << 10) | ((BN >> 3) << 17) | ((BM >> 4) << 24);
+        constexpr uint32_t idesc_pv = idesc_qk | (1u << 16);   // B (= V) is MN-major
+        const uint32_t q_addr = smem_u32(sm.q), p_addr = smem_u32(sm.p);
+        bool ok = mbar_wait(&sm.q_full, 0, cta_abort, p.err_flag);
+        for (int j = 0; ok && j < n_kv; ++j) {
+            const int s = j & 1;
+            const uint32_t ph = (j >> 1) & 1;
+            if (!(ok = mbar_wait(&sm.k_full[s], ph, cta_abort, p.err_flag))) break;
+            tc_fence_after();
+            if (lane == 0) {
+                const uint32_t k_addr = smem_u32(sm.k[s]);
+#pragma unroll
+                for (int kk = 0; kk < HD / 16; ++kk) {
+                    const uint32_t off = (kk >> 2) * SUB_BYTES + (kk & 3) * 32;
+                    umma_f16(tmem, smem_desc(q_addr + off, 16, 1024), smem_desc(k_addr + off, 16, 1024), idesc_qk, kk > 0);
+                }
+                umma_commit(&sm.s_full);
+            }
+            __syncwarp();
+            if (!(ok = mbar_wait(&sm.p_full, j & 1, cta_abort, p.err_flag))) break;
+            if (!(ok = mbar_wait(&sm.v_full[s], ph, cta_abort, p.err_flag))) break;
+            if (j > 0 && !(ok = mbar_wait(&sm.o_empty, (j - 1) & 1, cta_abort, p.err_flag))) break;
+            tc_fence_after();
+            if (lane == 0) {
+                const uint32_t v_addr = smem_u32(sm.v[s]);
+#pragma unroll
+                for (int kk = 0; kk < BN / 16; ++kk) {
+                    const uint32_t a_off = (kk >> 2) * SUB_BYTES + (kk & 3) * 32;
+                    umma_f16(tmem + 128, smem_desc(p_addr + a_off, 16, 1024),
+                             smem_desc(v_addr + kk * 2048, SUB_BYTES, 1024), idesc_pv, kk > 0);
+                }
+                umma_commit(&sm.o_full);
+                umma_commit(&sm.kv_empty[s]);
+            }
+            __syncwarp();
+        }
+    } else {
+        // ------------------------------------------------------------------ softmax warps 0-3
+        const int r = threadIdx.x;                       // row of the tile == TMEM lane
+        const uint32_t lane_addr = tmem + ((uint32_t)(warp * 32) << 16);
+        float m = -INFINITY, l = 0.f;
+        float o[HD];
+#pragma unroll
+        for (int i = 0; i < HD; ++i) o[i] = 0.f;
+        bool ok = true;
+        for (int j = 0; j < n_kv; ++j) {
+            if (!(ok = mbar_wait(&sm.s_full, j & 1, cta_abort, p.err_flag))) break;
+            tc_fence_after();
+            const bool diag = (j == t);
+            float mx = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                float sv[32];
+                tmem_ld32(lane_addr + c * 32, sv);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const bool vis = !diag || (c * 32 + i <= r);
+                    mx = fmaxf(mx, vis ? sv[i] : -INFINITY);
+                }
+            }
+            const float m_new = fmaxf(m, mx * p.scale_log2);
+            const float alpha = fast_exp2(m - m_new);
+            float rs = 0.f;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                float sv[32];
+                tmem_ld32(lane_addr + c * 32, sv);
+                uint32_t pk[16];
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    const bool v0 = !diag || (c * 32 + i <= r), v1 = !diag || (c * 32 + i + 1 <= r);
+                    const float p0 = v0 ? fast_exp2(fmaf(sv[i], p.scale_log2, -m_new)) : 0.f;
+                    const float p1 = v1 ? fast_exp2(fmaf(sv[i + 1], p.scale_log2, -m_new)) : 0.f;
+                    rs += p0 + p1;
+                    pk[i >> 1] = pack2<T>(p0, p1);
+                }
+                // keys [c*32, c*32+32) -> sub-tile c>>1, 16-byte chunks (c&1)*4 .. +4, xor-swizzled by row
+                unsigned char* rowp = sm.p + (c >> 1) * SUB_BYTES + r * 128;
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) {
+                    const int chunk = ((c & 1) * 4 + q4) ^ (r & 7);
+                    *reinterpret_cast<uint4*>(rowp + chunk * 16) =
+                        make_uint4(pk[q4 * 4], pk[q4 * 4 + 1], pk[q4 * 4 + 2], pk[q4 * 4 + 3]);
+                }
+            }
+            l = l * alpha + rs;
+            m = m_new;
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            tc_fence_before();
+            mbar_arrive(&sm.p_full);
+            if (!(ok = mbar_wait(&sm.o_full, j & 1, cta_abort, p.err_flag))) break;
+            tc_fence_after();
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                float pv[32];
+                tmem_ld32(lane_addr + 128 + c * 32, pv);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) o[c * 32 + i] = fmaf(o[c * 32 + i], alpha, pv[i]);
+            }
+            tc_fence_before();
+            mbar_arrive(&sm.o_empty);
+        }
+        if (ok && q0 + r < L) {
+            const float inv = 1.f / l;
+            const int64_t row = seq_beg + q0 + r;
+            if (p.out_f32) {
+                float4* dst = reinterpret_cast<float4*>((float*)p.out + (row * p.H + h) * HD);
+#pragma unroll
+                for (int i = 0; i < HD / 4; ++i)
+                    dst[i] = make_float4(o[4 * i] * inv, o[4 * i + 1] * inv, o[4 * i + 2] * inv, o[4 * i + 3] * inv);
+            } else {
+                uint4* dst = reinterpret_cast<uint4*>((T*)p.out + (row * p.H + h) * HD);
+#pragma unroll
+                for (int i = 0; i < HD / 8; ++i)
+                    dst[i] = make_uint4(pack2<T>(o[8 * i] * inv, o[8 * i + 1] * inv), pack2<T>(o[8 * i + 2] * inv, o[8 * i + 3] * inv),
+                                        pack2<T>(o[8 * i + 4] * inv, o[8 * i + 5] * inv), pack2<T>(o[8 * i + 6] * inv, o[8 * i + 7] * inv));
+            }
+        }
+    }
+    // ---------------------------------------------------------------------- teardown
+    if (warp == 4 && lane == 0 && sm.abort) {
+        // give copies that were issued but never consumed a bounded chance to land
+        const long long t0 = clock64();
+        for (int s = 0; s < STAGES; ++s) {
+            if (!issued_k[s]) continue;
+            const uint32_t ph = ((issued_k[s] - 1) >> 1) & 1;
+            while (!(mbar_try(&sm.k_full[s], ph) && mbar_try(&sm.v_full[s], ph)) && clock64() - t0 < WAIT_CYCLES) {}
+        }
+        while (!mbar_try(&sm.q_full, 0) && clock64() - t0 < WAIT_CYCLES) {}
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 5) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(256));
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* f = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(f);
+    });
+    return fn;
+}
+
+// [n_tokens, H*128] 16-bit row-major; box = 64 elements (128 B) x 128 rows, 128-byte swizzle.
+static int make_map(CUtensorMap* map, const void* base, int64_t n_tokens, int H, int dtype) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return (int)cudaErrorNotSupported;
+    const cuuint64_t dims[2] = {(cuuint64_t)H * HD, (cuuint64_t)n_tokens};
+    const cuuint64_t strides[1] = {(cuuint64_t)H * HD * 2};
+    const cuuint32_t box[2] = {64, 128};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = fn(map, dtype == ATTN_B200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                          2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
+}
+
+}  // namespace tc
+
+bool prefill_tc_supported(int D, int dtype) {
+    return D == tc::HD && (dtype == ATTN_B200_F16 || dtype == ATTN_B200_BF16);
+}
+
+int prefill_tc_launch(const void* q, const void* k, const void* v, const int32_t* offsets, void* out, int B,
+                      int64_t n_tokens, int max_len, int H, int D, float scale, int dtype, int out_f32,
+                      int32_t* err_flag, cudaStream_t st) {
+    using namespace tc;
+    if (D != HD) return ATTN_B200_ESHAPE;
+    if (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)out) % 16) return ATTN_B200_EINVAL;
+    if (n_tokens > 0x7fffffffLL || B > 65535 || H > 65535) return ATTN_B200_ETOOLARGE;
+    CUtensorMap mq, mk, mv;
+    int rc;
+    if ((rc = make_map(&mq, q, n_tokens, H, dtype)) || (rc = make_map(&mk, k, n_tokens, H, dtype)) ||
+        (rc = make_map(&mv, v, n_tokens, H, dtype)))
+        return rc;
+    const int smem = (int)sizeof(SmemLayout) + 1024;
+    Params p{offsets, out, B, H, n_tokens, (max_len + BM - 1) / BM, scale * kLog2e, out_f32, err_flag};
+    dim3 grid(p.n_qtiles, H, B);
+    void* abort_addr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&abort_addr, g_abort);
+    if (e != cudaSuccess) return (int)e;
+    if ((e = cudaMemsetAsync(abort_addr, 0, sizeof(int), st)) != cudaSuccess) return (int)e;
+    if (dtype == ATTN_B200_BF16) {
+        if ((e = cudaFuncSetAttribute(prefill_tc_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) != cudaSuccess)
+            return (int)e;
+        prefill_tc_kernel<__nv_bfloat16><<<grid, THREADS, smem, st>>>(mq, mk, mv, p);
+    } else {
+        if ((e = cudaFuncSetAttribute(prefill_tc_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) != cudaSuccess)
+            return (int)e;
+        prefill_tc_kernel<__half><<<grid, THREADS, smem, st>>>(mq, mk, mv, p);
+    }
+    return (int)cudaGetLastError();
+}
+
 }  // namespace attn

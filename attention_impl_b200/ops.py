@@ -275,14 +275,15 @@ def kv_attention_forward(Q, K, V, K_cache, V_cache, num_heads: int, *, scale: fl
 # ----------------------------------------------------------------------------------------------
 def paged_attention_forward(Q, K, V, offsets, num_heads: int, *, scale: Optional[float] = None,
                             return_sp: bool = True, max_seqlen: Optional[int] = None,
-                            out_dtype: Optional[torch.dtype] = None,
-                            force_generic: bool = False) -> List[torch.Tensor]:
+                            out_dtype: Optional[torch.dtype] = None, force_generic: bool = False,
+                            err_flag: Optional[torch.Tensor] = None) -> List[torch.Tensor]:
     """Causal attention over a packed ``[sum L, H*D]`` token buffer (paged_attention_kernel.cu:189-235).
 
     ``offsets`` int32 ``[B]`` are inclusive cumulative lengths.  Returns ``[S, P, O]``; S, P are
     ``[B, H, maxL, maxL]`` in the input dtype as in the reference unless ``return_sp=False``
     (empty placeholders; required for the tensor-core path and for any large input).
-    ``out_dtype=torch.float32`` makes the tensor-core path store fp32 output.
+    ``out_dtype=torch.float32`` makes the tensor-core path store fp32 output.  ``err_flag`` (int32
+    device scalar) receives ATTN_B200_FLAG_* bits (bad offsets, an in-kernel wait that ran out).
     """
     for t, n in ((Q, "Q"), (K, "K"), (V, "V")):
         _check_input(t, n)
@@ -313,7 +314,7 @@ def paged_attention_forward(Q, K, V, offsets, num_heads: int, *, scale: Optional
         check(lib.attn_b200_varlen_prefill(
             Q.data_ptr(), K.data_ptr(), V.data_ptr(), offsets.data_ptr(), O.data_ptr(),
             S.data_ptr() if return_sp else None, P.data_ptr() if return_sp else None, B, n_tokens, max_seqlen, H, D,
-            float(scale), dt, int(out_f32), int(force_generic), None, _stream()), "paged_attention_forward")
+            float(scale), dt, int(out_f32), int(force_generic), _ptr(err_flag), _stream()), "paged_attention_forward")
     return [S, P, O]
 
 

@@ -51,7 +51,8 @@ enum {
 enum {
     ATTN_B200_FLAG_BAD_SLOT = 1,     /* cache_indices entry outside [0, n_slots) */
     ATTN_B200_FLAG_BAD_POSITION = 2, /* positions entry outside [0, max_pos) */
-    ATTN_B200_FLAG_BAD_OFFSETS = 4   /* offsets not non-decreasing / beyond n_tokens */
+    ATTN_B200_FLAG_BAD_OFFSETS = 4,  /* offsets not non-decreasing / beyond n_tokens */
+    ATTN_B200_FLAG_TIMEOUT = 8       /* a bounded in-kernel wait ran out; the kernel gave up cleanly */
 };
 
 ATTN_B200_API const char* attn_b200_strerror(int status);

@@ -1,0 +1,88 @@
+"""GPU: tensor-core (tcgen05) packed causal prefill vs the CPU oracle.
+
+Tolerances.  The kernel rounds P to the input type before P·V (as every flash-style kernel does):
+for fp16 that is 2^-12 relative per probability and the fp32-output result stays within 2e-3
+max-abs of the fp32-evaluated oracle; for bf16 P carries 2^-9, so short rows (a few keys with
+large probabilities) reach ~4e-3·|v|max and the bound used is 1e-2 for fp32 output and 2 bf16 ulp
+(1.6e-2 at |O| < 2) for bf16 output.
+"""
+import pytest
+import torch
+
+from oracle import attention_oracle as orc
+from helpers import prefill_inputs
+
+pytestmark = pytest.mark.gpu
+
+
+def _run(Q, K, V, off, H, **kw):
+    import lm_ops
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    S, P, O = lm_ops.packed_attention(Q.cuda(), K.cuda(), V.cuda(), off.cuda(), H, return_sp=False, err_flag=flag, **kw)
+    torch.cuda.synchronize()
+    assert int(flag.item()) == 0, f"kernel raised flag bits {int(flag.item())}"
+    return O.cpu()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("lens", [[128], [1], [5, 0, 1, 130, 64, 257], [127, 129, 256, 384, 1000]])
+def test_prefill_tc_fp32_out_vs_fp32_oracle(dtype, lens):
+    H = 2
+    Q, K, V, off = prefill_inputs(lens, H, 128, dtype, seed=sum(lens))
+    O = _run(Q, K, V, off, H, out_dtype=torch.float32)
+    assert O.dtype == torch.float32
+    O32 = orc.packed_prefill(Q, K, V, off, H, compute_dtype=torch.float32, out_dtype=torch.float32)
+    tol = 2e-3 if dtype == torch.float16 else 1e-2
+    assert (O - O32).abs().max() <= tol
+    # typical error is far below the bound
+    assert (O - O32).abs().mean() <= tol / 20
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_prefill_tc_native_out_and_matches_generic(dtype):
+    lens = [300, 17, 2048, 640]
+    H = 4
+    Q, K, V, off = prefill_inputs(lens, H, 128, dtype, seed=7)
+    O = _run(Q, K, V, off, H)
+    assert O.dtype == dtype
+    O32 = orc.packed_prefill(Q, K, V, off, H, compute_dtype=torch.float32, out_dtype=torch.float32)
+    tol = 2e-3 if dtype == torch.float16 else 1.6e-2
+    assert (O.float() - O32).abs().max() <= tol
+    Og = _run(Q, K, V, off, H, force_generic=True)
+    assert (O.float() - Og.float()).abs().max() <= tol
+
+
+def test_prefill_tc_many_heads_and_sequences():
+    """32 heads, 12 ragged sequences: exercises the column offset of every head in the tensor map."""
+    g = torch.Generator().manual_seed(3)
+    lens = torch.randint(1, 600, (12,), generator=g).tolist()
+    H = 32
+    Q, K, V, off = prefill_inputs(lens, H, 128, torch.bfloat16, seed=11)
+    O = _run(Q, K, V, off, H, out_dtype=torch.float32)
+    O32 = orc.packed_prefill(Q, K, V, off, H, compute_dtype=torch.float32, out_dtype=torch.float32)
+    assert (O - O32).abs().max() <= 1e-2
+
+
+def test_prefill_tc_rows_sum_property_at_workload_lengths():
+    """Lengths up to 4096 (workload range), V = ones: every output element must be exactly 1 (a
+    convex combination of ones) whatever the scores; checks masking and normalisation at sizes
+    the oracle would take minutes for."""
+    import lm_ops
+    g = torch.Generator().manual_seed(5)
+    lens = [4096, 3000, 257, 4095]
+    H = 4
+    T = sum(lens)
+    Q = torch.randn(T, H * 128, generator=g).bfloat16().cuda()
+    K = torch.randn(T, H * 128, generator=g).bfloat16().cuda()
+    V = torch.ones(T, H * 128, dtype=torch.bfloat16, device="cuda")
+    off = torch.tensor(lens).cumsum(0).int().cuda()
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    _, _, O = lm_ops.packed_attention(Q, K, V, off, H, return_sp=False, out_dtype=torch.float32, err_flag=flag)
+    assert int(flag.item()) == 0
+    assert (O - 1).abs().max() <= 4e-3     # l is summed in fp32 from unrounded p, P·V uses rounded p
+    # first row of every sequence attends only to itself
+    V2 = torch.randn(T, H * 128, generator=g).bfloat16().cuda()
+    _, _, O2 = lm_ops.packed_attention(Q, K, V2, off, H, return_sp=False, out_dtype=torch.float32)
+    begs = [0] + off.tolist()[:-1]
+    for b in begs:
+        assert torch.allclose(O2[b], V2[b].float(), atol=4e-3 * 4)
