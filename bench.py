@@ -1,31 +1,36 @@
 #!/usr/bin/env python
-"""Benchmark of the paged-decode hot path on B200.
+"""Benchmark of the attention hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference] [--workload NAME]
 
-Workload (the configuration the headline metric is quoted on): large-batch KV-paged single-query
-decode, fp16 MHA, batch 256, 32 heads, head_dim 128, context lengths uniform in [1024, 32768]
-(~71 GB of KV), block_size = 1 slot table = random permutation over the whole pool, q/k/v ~ N(0,1).
-At N GPUs the heads are sharded N ways (each rank owns H/N heads of every token: its pool is
-[slots, (H/N)*128]); there is no collective in the data path.  Total work is fixed, so this is
-strong scaling.
+Default workload `large_decode` (the configuration the headline metric is quoted on): large-batch
+KV-paged single-query decode, fp16 MHA, batch 256, 32 heads, head_dim 128, context lengths uniform
+in [1024, 32768] (~76 GB of KV at the seeded lengths), block_size = 1 slot table = random
+permutation over the whole pool, q/k/v ~ N(0,1).  At N GPUs the heads are sharded N ways (each rank
+owns H/N heads of every token: its pool is [slots, (H/N)*128]); there is no collective in the data
+path.  Total work is fixed, so this is strong scaling.
 
-One step = one decode of the whole batch (partial kernel + combine kernel).  `value` is the
-aggregate KV-read bandwidth  2*T*H*D*2 bytes / step time  with all inputs resident in HBM, timed
-with CUDA events, maximum over ranks.  `e2e` is the same through the public Python operator with
-the per-step inputs (q, k, v, slot table, offsets) in pinned HOST memory copied in, and the
-output copied back, inside the timed region; the KV pool itself is device-resident state (it is a
-cache), as it is for any caller of the reference operator.
+One step = one pass of the operator over the whole batch.  `value` is the aggregate throughput
+with all inputs resident in HBM, timed with CUDA events, maximum over ranks.  `e2e` is the same
+through the public Python operator with the per-step inputs in pinned HOST memory copied in, and
+the output copied back, inside the timed region; for the decode workloads the KV pool itself is
+device-resident state (it is the cache), as it is for any caller of the reference operator.
 
-`--impl reference` times the reference's torch CPU math (the oracle restatement, since the
-reference's test modules cannot be imported without a GPU) on a bounded sample of the same
+Other workloads (measurement of the remaining configurations, same JSON shape):
+  small_decode  batch 8, ctx U[128,1024], 16384-slot pool (4 pools rotated to defeat L2)
+  rope          rotary embedding on q,k [16384, 32*128] fp16, positions U[0,8191]
+  prefill       packed causal prefill, bf16, 64 sequences U[256,4096], 32 heads (tensor-core path)
+  fp8_split     long-context e4m3-KV decode, batch 64, ctx U[32768,131072]; each sequence's KV is
+                split across the N ranks, partial rows all-gathered over NCCL, LSE-combined
+
+`--impl reference` times the reference's torch CPU math (the oracle restatement: the reference's
+test modules cannot be imported without a GPU and its `lm_ops`) on a bounded sample of the same
 workload with all host threads.
 """
 from __future__ import annotations
 
 import argparse
 import json
-import math
 import os
 import sys
 import threading
@@ -36,23 +41,25 @@ import torch
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-CFG = dict(batch=256, heads=32, head_dim=128, ctx_lo=1024, ctx_hi=32768, dtype="f16", seed=4)
 FALLBACK_HBM_GBS = 6650.0
+FALLBACK_BF16_TFLOPS = 1590.0
+
+# dram__bytes_read.sum + dram__bytes_write.sum per algorithmic byte of the decode partial kernel, from
+# the ncu capture of a 5.3 GB case of the large_decode workload
+# (profiles/paged_decode_fast_kernel_small_case_ncu.md); every row is read once, so traffic grows in
+# proportion to the tokens processed.
+DECODE_TRAFFIC_RATIO = 1.0017
 
 
-def measured_peak():
+def measured_peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
         try:
-            return float(json.load(open(p))["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+            j = json.load(open(p))
+            return float(j["hbm_gbs"]), float(j["bf16_tflops"]), "measured (MEASURED_PEAKS.json)"
         except Exception:
             pass
-    return FALLBACK_HBM_GBS, "fallback (6.65 TB/s, earlier measurement on this pool)"
-
-
-def workload_lengths(cfg):
-    g = torch.Generator().manual_seed(cfg["seed"])
-    return torch.randint(cfg["ctx_lo"], cfg["ctx_hi"] + 1, (cfg["batch"],), generator=g)
+    return FALLBACK_HBM_GBS, FALLBACK_BF16_TFLOPS, "fallback (earlier measurement on this pool)"
 
 
 class ClockSampler(threading.Thread):
@@ -119,15 +126,23 @@ def physical_gpu_index(local_index: int) -> int:
     return local_index
 
 
-# ------------------------------------------------------------------------------------------------
-# CPU legs (oracle = the reference's torch math)
-# ------------------------------------------------------------------------------------------------
-def cpu_sample_inputs(cfg, lens, n_seq, heads, seed):
-    """The first n_seq sequences of the workload with a compact pool (rows in slot order, so the
-    gather stays random within the sample)."""
-    from oracle import attention_oracle  # noqa: F401  (CPU baseline leg only)
+def seeded_lengths(n, lo, hi, seed):
     g = torch.Generator().manual_seed(seed)
-    D = cfg["head_dim"]
+    return torch.randint(lo, hi + 1, (n,), generator=g)
+
+
+def fill_normal(t: torch.Tensor, rows_per_chunk: int = 1 << 18):
+    for r in range(0, t.size(0), rows_per_chunk):
+        t[r:r + rows_per_chunk].normal_()
+
+
+# ================================================================================================
+# CPU legs (oracle = the reference's torch math).  The only place bench.py touches oracle/.
+# ================================================================================================
+def cpu_decode_inputs(lens, n_seq, heads, D, seed):
+    """The first n_seq sequences of a decode workload with a compact pool (rows in slot order, so
+    the gather stays random within the sample)."""
+    g = torch.Generator().manual_seed(seed)
     sl = lens[:n_seq]
     T = int(sl.sum())
     dim = heads * D
@@ -142,23 +157,22 @@ def cpu_sample_inputs(cfg, lens, n_seq, heads, seed):
     return Q, K, V, Kc, Vc, ci, off
 
 
-def time_cpu_oracle(inputs, heads, steps=1, warmup=0):
-    from oracle import attention_oracle as orc
+def time_cpu(fn, steps=1, warmup=0):
     torch.set_num_threads(os.cpu_count() or 1)
     for _ in range(warmup):
-        orc.paged_decode(*inputs, heads)
+        fn()
     t0 = time.perf_counter()
-    out = None
     for _ in range(steps):
-        out = orc.paged_decode(*inputs, heads)
-    return (time.perf_counter() - t0) / steps, out
+        fn()
+    return (time.perf_counter() - t0) / steps
 
 
-def pick_cpu_sample(cfg, lens, heads, budget_s, max_tokens):
-    """Choose how many leading sequences fit a CPU time budget (and a token cap that bounds host
-    memory and set-up time), from a one-sequence probe.  Returns (n_sequences, seconds/token)."""
-    probe = cpu_sample_inputs(cfg, lens, 1, heads, seed=99)
-    t, _ = time_cpu_oracle(probe, heads, warmup=1)
+def pick_decode_sample(lens, heads, D, budget_s, max_tokens):
+    """How many leading sequences fit a CPU time budget and a token cap (bounds host memory and
+    set-up time), from a one-sequence probe.  Returns (n_sequences, seconds/token)."""
+    from oracle import attention_oracle as orc
+    probe = cpu_decode_inputs(lens, 1, heads, D, seed=99)
+    t = time_cpu(lambda: orc.paged_decode(*probe, heads), warmup=1)
     per_tok = t / max(1, int(lens[0]))
     n, tok = 1, int(lens[0])
     while n < len(lens) and tok + int(lens[n]) <= max_tokens and (tok + int(lens[n])) * per_tok <= budget_s:
@@ -167,45 +181,446 @@ def pick_cpu_sample(cfg, lens, heads, budget_s, max_tokens):
     return n, per_tok
 
 
-def run_reference(args, cfg, lens):
-    """CPU arm: the reference's torch math on the host cores, bounded sample per step."""
-    H, D = cfg["heads"], cfg["head_dim"]
-    n_seq, _ = pick_cpu_sample(cfg, lens, H, budget_s=max(1.0, 90.0 / max(1, args.steps + args.warmup)),
-                               max_tokens=131072)
-    inputs = cpu_sample_inputs(cfg, lens, n_seq, H, seed=7)
-    T = int(lens[:n_seq].sum())
-    sec, _ = time_cpu_oracle(inputs, H, steps=args.steps, warmup=args.warmup)
-    kv_bytes = 2 * T * H * D * 2
-    value = kv_bytes / sec / 1e12
-    cores = torch.get_num_threads()
-    sample = f"first {n_seq} of {cfg['batch']} sequences ({T} tokens, {kv_bytes / 1e9:.2f} GB of KV) per step"
+# ================================================================================================
+# Workloads
+# ================================================================================================
+class Workload:
+    name = metric = unit = dtype = ""
+    scaling = "strong"
+    bound = "hbm"
+
+    def __init__(self, args, world, rank, dev):
+        self.args, self.world, self.rank, self.dev = args, world, rank, dev
+
+    def step_split(self):               # (dominant kernel, rest) as two callables, or None
+        return None
+
+    def traffic(self):
+        return None
+
+    def cpu_baseline(self):             # (cpu_baseline dict, parity dict) or (None, None)
+        return None, None
+
+
+class LargeDecode(Workload):
+    name, metric, unit, dtype = "large_decode", "paged_decode_kv_read_bandwidth", "TB/s", "f16"
+    B, H, D, LO, HI, SEED = 256, 32, 128, 1024, 32768, 4
+    kv_bytes_el = 2
+
+    def lens(self):
+        return seeded_lengths(self.args.batch or self.B, self.LO, self.HI, self.SEED)
+
+    def setup(self):
+        import attention_impl_b200 as A
+        self.A = A
+        dev, world = self.dev, self.world
+        self.lens_ = self.lens()
+        self.Bn = len(self.lens_)
+        if self.H % world:
+            raise SystemExit("heads must divide by the number of GPUs")
+        self.Hl = self.H // world
+        dim = self.Hl * self.D
+        self.T = int(self.lens_.sum())
+        torch.manual_seed(1000 * self.SEED + self.rank)
+        self.Kc = torch.empty(self.T, dim, dtype=torch.float16, device=dev)
+        self.Vc = torch.empty(self.T, dim, dtype=torch.float16, device=dev)
+        fill_normal(self.Kc)
+        fill_normal(self.Vc)
+        gperm = torch.Generator(device=dev).manual_seed(self.SEED)   # same slot table on every rank
+        self.ci = torch.randperm(self.T, device=dev, generator=gperm).to(torch.int32)
+        self.off = self.lens_.cumsum(0).to(torch.int32).to(dev)
+        self.Q, self.K, self.V = (torch.randn(self.Bn, dim, device=dev, dtype=torch.float16) for _ in range(3))
+        self.O = torch.empty_like(self.Q)
+        self.chunk = A.ops.pick_chunk(self.Bn, self.Hl, self.D, self.T, dev)
+        self.ws = torch.empty(A.ops.decode_workspace_bytes(self.Bn, self.Hl, self.D, self.T, self.chunk),
+                              dtype=torch.uint8, device=dev)
+
+    def _call(self, stages):
+        self.A.paged_kv_attention_forward(self.Q, self.K, self.V, self.Kc, self.Vc, self.ci, self.off, self.Hl,
+                                          return_sp=False, chunk=self.chunk, workspace=self.ws, out=self.O,
+                                          stages=stages)
+
+    def step(self):
+        self._call(3)
+
+    def step_split(self):
+        return (lambda: self._call(1)), (lambda: self._call(2))
+
+    def e2e_setup(self):
+        self.h_in = [x.cpu().pin_memory() for x in (self.Q, self.K, self.V, self.ci, self.off)]
+        self.h_out = torch.empty(self.O.shape, dtype=self.O.dtype).pin_memory()
+        return sum(x.numel() * x.element_size() for x in self.h_in), self.h_out.numel() * self.h_out.element_size()
+
+    def e2e_step(self):
+        dQ, dK, dV, dci, doff = (x.to(self.dev, non_blocking=True) for x in self.h_in)
+        _, _, o = self.A.paged_kv_attention_forward(dQ, dK, dV, self.Kc, self.Vc, dci, doff, self.Hl, return_sp=False)
+        self.h_out.copy_(o, non_blocking=True)
+        torch.cuda.current_stream().synchronize()   # the caller reads the result every step
+
+    def units_per_step_rank(self):
+        return 2.0 * self.T * self.Hl * self.D * self.kv_bytes_el
+
+    def sequences_per_step(self):
+        return self.Bn
+
+    def launches_per_step(self):
+        return 2
+
+    def kernel_name(self):
+        return "paged_decode_fast_kernel<half,half,128>"
+
+    def traffic(self):
+        return DECODE_TRAFFIC_RATIO * self.units_per_step_rank()
+
+    def config(self):
+        per = self.units_per_step_rank()
+        return {"workload": "large_batch_paged_decode", "batch": self.Bn, "heads": self.H, "head_dim": self.D,
+                "ctx_range": [self.LO, self.HI], "context_tokens": self.T, "kv_bytes_total": per * self.world,
+                "kv_bytes_per_gpu": per, "sharding": f"heads/{self.world} per GPU, no collective",
+                "chunk": self.chunk, "l2": f"inputs larger than L2 ({per / 1e9:.1f} GB of KV per GPU per step)"}
+
+    def cpu_baseline(self):
+        """Oracle on the first sequences of the very tensors the GPU used: CPU timing + parity."""
+        from oracle import attention_oracle as orc
+        H, D, dev = self.Hl, self.D, self.dev
+        n_seq, per_tok = pick_decode_sample(self.lens_, H, D, budget_s=15.0, max_tokens=262144)
+        T = int(self.lens_[:n_seq].sum())
+        passes = max(1, min(20, int(round(12.0 / max(1e-3, per_tok * T)))))   # ~12 s of CPU work
+        rows = self.ci[:T].long()
+        order = torch.argsort(rows)                       # compact pool in slot order
+        rank_of = torch.empty_like(order)
+        rank_of[order] = torch.arange(T, device=dev)
+        inputs = (self.Q[:n_seq].cpu(), self.K[:n_seq].cpu(), self.V[:n_seq].cpu(), self.Kc[rows[order]].cpu(),
+                  self.Vc[rows[order]].cpu(), rank_of.int().cpu(), self.off[:n_seq].cpu())
+        sec = time_cpu(lambda: orc.paged_decode(*inputs, H), steps=passes)
+        _, _, O_gpu = self.A.paged_kv_attention_forward(self.Q, self.K, self.V, self.Kc, self.Vc, self.ci, self.off,
+                                                        H, return_sp=False)
+        _, _, O32 = orc.paged_decode(*inputs, H, compute_dtype=torch.float32)
+        err = (O_gpu[:n_seq].cpu().float() - O32.float()).abs().max().item()
+        kv_bytes = 2 * T * H * D * 2
+        sample = (f"first {n_seq} of {self.Bn} sequences ({T} tokens, {kv_bytes / 1e9:.2f} GB of KV), "
+                  f"mean of {passes} passes")
+        return ({"value": kv_bytes / sec / 1e12, "unit": "TB/s", "cores": torch.get_num_threads(), "kind": "port",
+                 "sample": sample, "seconds": sec, "torch": torch.__version__},
+                {"max_abs_err_vs_fp32_oracle": err, "tolerance": 2e-3, "sequences_checked": n_seq})
+
+    def reference_run(self, steps, warmup):
+        from oracle import attention_oracle as orc
+        lens = self.lens()
+        n_seq, _ = pick_decode_sample(lens, self.H, self.D, budget_s=max(1.0, 90.0 / max(1, steps + warmup)),
+                                      max_tokens=131072)
+        inputs = cpu_decode_inputs(lens, n_seq, self.H, self.D, seed=7)
+        T = int(lens[:n_seq].sum())
+        sec = time_cpu(lambda: orc.paged_decode(*inputs, self.H), steps=steps, warmup=warmup)
+        kv_bytes = 2 * T * self.H * self.D * 2
+        sample = f"first {n_seq} of {len(lens)} sequences ({T} tokens, {kv_bytes / 1e9:.2f} GB of KV) per step"
+        return kv_bytes / sec / 1e12, sec, sample, n_seq
+
+
+class SmallDecode(LargeDecode):
+    name = "small_decode"
+    B, LO, HI, SEED = 8, 128, 1024, 1
+    POOLS, SLOTS = 4, 16384
+
+    def setup(self):
+        import attention_impl_b200 as A
+        self.A = A
+        dev = self.dev
+        self.lens_ = self.lens()
+        self.Bn, self.Hl = len(self.lens_), self.H
+        dim = self.H * self.D
+        self.T = int(self.lens_.sum())
+        torch.manual_seed(1000 * self.SEED + self.rank)
+        self.pools = [(torch.randn(self.SLOTS, dim, device=dev, dtype=torch.float16),
+                       torch.randn(self.SLOTS, dim, device=dev, dtype=torch.float16)) for _ in range(self.POOLS)]
+        self.Kc, self.Vc = self.pools[0]
+        self.ci = torch.randperm(self.SLOTS, device=dev)[: self.T].to(torch.int32)
+        self.off = self.lens_.cumsum(0).to(torch.int32).to(dev)
+        self.Q, self.K, self.V = (torch.randn(self.Bn, dim, device=dev, dtype=torch.float16) for _ in range(3))
+        self.O = torch.empty_like(self.Q)
+        self.chunk = A.ops.pick_chunk(self.Bn, self.H, self.D, self.T, dev)
+        self.ws = torch.empty(A.ops.decode_workspace_bytes(self.Bn, self.H, self.D, self.T, self.chunk),
+                              dtype=torch.uint8, device=dev)
+        self.i = 0
+
+    def _call(self, stages):
+        if stages & 1:
+            self.i += 1
+            self.Kc, self.Vc = self.pools[self.i % self.POOLS]
+        super()._call(stages)
+
+    def config(self):
+        c = super().config()
+        c.update(workload="small_batch_paged_decode", sharding="replicas only",
+                 l2=f"{self.POOLS} KV pools of {self.SLOTS} slots rotated: {self.POOLS} x "
+                    f"{self.units_per_step_rank() / 1e6:.0f} MB touched cyclically (> 126 MB L2)")
+        return c
+
+    def cpu_baseline(self):
+        return None, None
+
+
+class Rope(Workload):
+    name, metric, unit, dtype = "rope", "rope_bandwidth", "TB/s", "f16"
+    N, H, D, MAXPOS = 16384, 32, 128, 8192
+
+    def setup(self):
+        import attention_impl_b200 as A
+        self.A = A
+        dev = self.dev
+        torch.manual_seed(2000 + self.rank)
+        self.q = torch.randn(self.N, self.H * self.D, device=dev, dtype=torch.float16)
+        self.k = torch.randn(self.N, self.H * self.D, device=dev, dtype=torch.float16)
+        self.pos = torch.randint(0, self.MAXPOS, (self.N,), device=dev, dtype=torch.int32)
+        inv = 1.0 / (10000.0 ** (torch.arange(0, self.D, 2, device=dev).float() / self.D))
+        fr = torch.outer(torch.arange(self.MAXPOS, device=dev).float(), inv)
+        self.cos, self.sin = fr.cos().half(), fr.sin().half()
+
+    def step(self):
+        self.A.rotary_embedding_inplace(self.q, self.k, self.pos, self.cos, self.sin, self.D)
+
+    def e2e_setup(self):
+        self.hq, self.hk, self.hpos = self.q.cpu().pin_memory(), self.k.cpu().pin_memory(), self.pos.cpu().pin_memory()
+        b = 2 * self.hq.numel() * 2
+        return b + self.hpos.numel() * 4, b
+
+    def e2e_step(self):
+        dq, dk = self.hq.to(self.dev, non_blocking=True), self.hk.to(self.dev, non_blocking=True)
+        dpos = self.hpos.to(self.dev, non_blocking=True)
+        self.A.rotary_embedding_inplace(dq, dk, dpos, self.cos, self.sin, self.D)
+        self.hq.copy_(dq, non_blocking=True)
+        self.hk.copy_(dk, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    def units_per_step_rank(self):
+        return 4.0 * self.N * self.H * self.D * 2
+
+    def sequences_per_step(self):
+        return self.N
+
+    def launches_per_step(self):
+        return 1
+
+    def kernel_name(self):
+        return "rope_vec8_kernel<half2>"
+
+    def config(self):
+        return {"workload": "rotary_embedding", "tokens": self.N, "heads": self.H, "head_dim": self.D,
+                "positions": [0, self.MAXPOS - 1], "sharding": "replicas only",
+                "l2": "537 MB read+written in place per step (> 126 MB L2)"}
+
+    def reference_run(self, steps, warmup):
+        from oracle import attention_oracle as orc
+        g = torch.Generator().manual_seed(2)
+        n = 2048
+        q = torch.randn(n, self.H * self.D, generator=g).half()
+        k = torch.randn(n, self.H * self.D, generator=g).half()
+        pos = torch.randint(0, self.MAXPOS, (n,), generator=g).int()
+        cos, sin = orc.rope_tables(self.D, self.MAXPOS)
+        sec = time_cpu(lambda: orc.rope(q, k, pos, cos, sin, self.D), steps=steps, warmup=warmup)
+        return 4.0 * n * self.H * self.D * 2 / sec / 1e12, sec, f"{n} of {self.N} tokens per step", n
+
+
+class Prefill(Workload):
+    name, metric, unit, dtype, bound = "prefill", "packed_causal_prefill_throughput", "TFLOP/s", "bf16", "tensor"
+    B, H, D, LO, HI, SEED = 64, 32, 128, 256, 4096, 3
+
+    def setup(self):
+        import attention_impl_b200 as A
+        self.A = A
+        dev = self.dev
+        self.lens_ = seeded_lengths(self.args.batch or self.B, self.LO, self.HI, self.SEED)
+        self.T = int(self.lens_.sum())
+        torch.manual_seed(3000 + self.rank)
+        self.off = self.lens_.cumsum(0).to(torch.int32).to(dev)
+        self.Q, self.K, self.V = (torch.randn(self.T, self.H * self.D, device=dev, dtype=torch.bfloat16)
+                                  for _ in range(3))
+        self.maxlen = int(self.lens_.max())
+        self.flag = torch.zeros(1, dtype=torch.int32, device=dev)
+
+    def step(self):
+        self.out = self.A.paged_attention_forward(self.Q, self.K, self.V, self.off, self.H, return_sp=False,
+                                                  max_seqlen=self.maxlen, err_flag=self.flag)[2]
+
+    def e2e_setup(self):
+        self.h_in = [x.cpu().pin_memory() for x in (self.Q, self.K, self.V, self.off)]
+        self.h_out = torch.empty(self.Q.shape, dtype=self.Q.dtype).pin_memory()
+        return sum(x.numel() * x.element_size() for x in self.h_in), self.h_out.numel() * 2
+
+    def e2e_step(self):
+        dQ, dK, dV, doff = (x.to(self.dev, non_blocking=True) for x in self.h_in)
+        o = self.A.paged_attention_forward(dQ, dK, dV, doff, self.H, return_sp=False, max_seqlen=self.maxlen)[2]
+        self.h_out.copy_(o, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    def units_per_step_rank(self):
+        l = self.lens_.double()
+        return 4.0 * self.D * self.H * float((l * (l + 1) / 2).sum())
+
+    def sequences_per_step(self):
+        return self.T
+
+    def launches_per_step(self):
+        return 1
+
+    def kernel_name(self):
+        return "prefill_tc_kernel<bf16>"
+
+    def config(self):
+        return {"workload": "packed_varlen_causal_prefill", "sequences": len(self.lens_), "heads": self.H,
+                "head_dim": self.D, "len_range": [self.LO, self.HI], "tokens": self.T,
+                "flops_per_step": self.units_per_step_rank(), "sharding": "replicas only",
+                "l2": f"Q,K,V,O = {4 * self.T * self.H * self.D * 2 / 1e9:.1f} GB per step (> 126 MB L2)"}
+
+    def cpu_baseline(self):
+        from oracle import attention_oracle as orc
+        n_seq = 2
+        T = int(self.lens_[:n_seq].sum())
+        Q, K, V = (x[:T].cpu() for x in (self.Q, self.K, self.V))
+        off = self.off[:n_seq].cpu()
+        sec = time_cpu(lambda: orc.packed_prefill(Q, K, V, off, self.H))
+        O32 = orc.packed_prefill(Q, K, V, off, self.H, compute_dtype=torch.float32, out_dtype=torch.float32)
+        self.step()
+        torch.cuda.synchronize()
+        err = (self.out[:T].cpu().float() - O32).abs().max().item()
+        l = self.lens_[:n_seq].double()
+        fl = 4.0 * self.D * self.H * float((l * (l + 1) / 2).sum())
+        return ({"value": fl / sec / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+                 "sample": f"first {n_seq} of {len(self.lens_)} sequences ({T} tokens), causal flops counted",
+                 "seconds": sec, "torch": torch.__version__},
+                {"max_abs_err_vs_fp32_oracle": err, "tolerance": 1.6e-2, "sequences_checked": n_seq,
+                 "kernel_flag": int(self.flag.item())})
+
+    def reference_run(self, steps, warmup):
+        from oracle import attention_oracle as orc
+        lens = seeded_lengths(self.B, self.LO, self.HI, self.SEED)[:1].clamp(max=2048)
+        T = int(lens.sum())
+        g = torch.Generator().manual_seed(3)
+        Q, K, V = (torch.randn(T, self.H * self.D, generator=g).bfloat16() for _ in range(3))
+        off = lens.cumsum(0).int()
+        sec = time_cpu(lambda: orc.packed_prefill(Q, K, V, off, self.H), steps=steps, warmup=warmup)
+        l = lens.double()
+        fl = 4.0 * self.D * self.H * float((l * (l + 1) / 2).sum())
+        return fl / sec / 1e12, sec, f"1 of {self.B} sequences ({T} tokens) per step", T
+
+
+class Fp8Split(Workload):
+    name, metric, unit, dtype = "fp8_split", "paged_decode_kv_read_bandwidth", "TB/s", "e4m3"
+    B, H, D, LO, HI, SEED = 64, 32, 128, 32768, 131072, 5
+
+    def setup(self):
+        import attention_impl_b200 as A
+        from attention_impl_b200 import dist as adist
+        self.A, self.adist = A, adist
+        dev, G, r = self.dev, self.world, self.rank
+        self.lens_ = seeded_lengths(self.args.batch or self.B, self.LO, self.HI, self.SEED)
+        self.Bn = len(self.lens_)
+        lo, hi = adist.kv_split_bounds(self.lens_, G, r)
+        self.llens = hi - lo                                   # this rank's slice of every sequence
+        self.T = int(self.llens.sum())
+        self.T_all = int(self.lens_.sum())
+        dim = self.H * self.D
+        torch.manual_seed(5000 + r)
+
+        def pool():   # random finite e4m3 codes: exponent field <= 7 (|x| <= 1.875), random sign
+            t = torch.empty(self.T, dim, dtype=torch.uint8, device=dev)
+            for a in range(0, self.T, 1 << 18):
+                c = t[a:a + (1 << 18)]
+                c.random_(0, 64)
+                c.add_((torch.rand(c.shape[0], 1, device=dev) < 0.5).to(torch.uint8) * 128)
+            return t.view(torch.float8_e4m3fn)
+        self.Kc, self.Vc = pool(), pool()
+        self.ks = torch.full((self.H,), 0.5, device=dev)
+        self.vs = torch.full((self.H,), 0.5, device=dev)
+        self.ci = torch.randperm(self.T, device=dev).to(torch.int32)
+        self.off = self.llens.cumsum(0).to(torch.int32).to(dev)
+        g = torch.Generator(device=dev).manual_seed(self.SEED)   # q, k, v replicated on every rank
+        self.Q, self.K, self.V = (torch.randn(self.Bn, dim, device=dev, dtype=torch.float16, generator=g)
+                                  for _ in range(3))
+        self.chunk = A.ops.pick_chunk(self.Bn, self.H, self.D, self.T, dev)
+
+    def step(self):
+        self.out = self.adist.kv_split_decode(self.Q, self.K, self.V, self.Kc, self.Vc, self.ci, self.off, self.H,
+                                              k_scale=self.ks, v_scale=self.vs, chunk=self.chunk)
+
+    def e2e_setup(self):
+        self.h_in = [x.cpu().pin_memory() for x in (self.Q, self.K, self.V, self.ci, self.off)]
+        self.h_out = torch.empty(self.Q.shape, dtype=self.Q.dtype).pin_memory()
+        return sum(x.numel() * x.element_size() for x in self.h_in), self.h_out.numel() * 2
+
+    def e2e_step(self):
+        dQ, dK, dV, dci, doff = (x.to(self.dev, non_blocking=True) for x in self.h_in)
+        o = self.adist.kv_split_decode(dQ, dK, dV, self.Kc, self.Vc, dci, doff, self.H, k_scale=self.ks,
+                                       v_scale=self.vs)
+        self.h_out.copy_(o, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    def units_per_step_rank(self):
+        return 2.0 * self.T * self.H * self.D * 1
+
+    def sequences_per_step(self):
+        return self.Bn
+
+    def launches_per_step(self):
+        return 3 + (1 if self.world > 1 else 0)     # partial, local combine, (all-gather), final combine
+
+    def kernel_name(self):
+        return "paged_decode_fast_kernel<half,e4m3,128>"
+
+    def config(self):
+        per = self.units_per_step_rank()
+        return {"workload": "long_context_fp8_kv_paged_decode", "batch": self.Bn, "heads": self.H,
+                "head_dim": self.D, "ctx_range": [self.LO, self.HI], "context_tokens": self.T_all,
+                "kv_bytes_total": 2.0 * self.T_all * self.H * self.D, "kv_bytes_per_gpu": per,
+                "sharding": f"each sequence's KV split {self.world} ways; all-gather of [B,H,D+2] fp32 partials "
+                            f"over NCCL + LSE combine", "chunk": self.chunk,
+                "l2": f"inputs larger than L2 ({per / 1e9:.1f} GB of KV per GPU per step)"}
+
+    def reference_run(self, steps, warmup):
+        from oracle import attention_oracle as orc
+        g = torch.Generator().manual_seed(5)
+        T, H, D = 32768, self.H, self.D
+        Q, K, V = (torch.randn(1, H * D, generator=g).half() for _ in range(3))
+        Kc, Vc = (torch.randn(T, H * D, generator=g) for _ in range(2))
+        K8, ks = orc.quantize_e4m3_per_head(Kc, H)
+        V8, vs = orc.quantize_e4m3_per_head(Vc, H)
+        ci = torch.randperm(T, generator=g).int()
+        off = torch.tensor([T]).int()
+
+        def fn():   # oracle on dequantised KV, dequantisation included (it is part of the path)
+            Kd = orc.dequantize_e4m3_per_head(K8, ks, H)
+            Vd = orc.dequantize_e4m3_per_head(V8, vs, H)
+            orc.paged_decode(Q.float(), K.float(), V.float(), Kd, Vd, ci, off, H)
+        sec = time_cpu(fn, steps=steps, warmup=warmup)
+        return 2.0 * T * H * D / sec / 1e12, sec, f"1 sequence of {T} tokens per step", 1
+
+
+WORKLOADS = {w.name: w for w in (LargeDecode, SmallDecode, Rope, Prefill, Fp8Split)}
+
+
+# ================================================================================================
+# Drivers
+# ================================================================================================
+def run_reference(args, W):
+    w = W(args, 1, 0, None)
+    value, sec, sample, seqs = w.reference_run(args.steps, args.warmup)
     line = {
-        "impl": "reference", "metric": "paged_decode_kv_read_bandwidth", "value": value, "unit": "TB/s",
-        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3,
-        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": cfg["dtype"],
-        "data": "synthetic", "tokens_per_s": n_seq / sec,
-        "config": {"workload": "large_batch_paged_decode", "batch": cfg["batch"], "heads": H, "head_dim": D,
-                   "ctx_range": [cfg["ctx_lo"], cfg["ctx_hi"]], "note": "torch CPU path, " + sample},
-        "cpu_baseline": {"value": value, "unit": "TB/s", "cores": cores, "kind": "port", "sample": sample,
-                         "torch": torch.__version__},
-        "e2e": {"value": value, "unit": "TB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "impl": "reference", "metric": W.metric, "value": value, "unit": W.unit, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
+        "scaling": W.scaling, "vs_baseline": None, "dtype": W.dtype, "data": "synthetic",
+        "tokens_per_s": seqs / sec,
+        "config": {"workload": W.name, "note": "torch CPU path (oracle restatement of the reference's test-side "
+                                               "math), " + sample},
+        "cpu_baseline": {"value": value, "unit": W.unit, "cores": torch.get_num_threads(), "kind": "port",
+                         "sample": sample, "torch": torch.__version__},
+        "e2e": {"value": value, "unit": W.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
 
 
-# ------------------------------------------------------------------------------------------------
-# GPU arm
-# ------------------------------------------------------------------------------------------------
-def fill_normal(t: torch.Tensor, rows_per_chunk: int = 1 << 18):
-    for r in range(0, t.size(0), rows_per_chunk):
-        t[r:r + rows_per_chunk].normal_()
-
-
-def run_b200(args, cfg, lens):
+def run_b200(args, W):
     import torch.distributed as dist
-    import attention_impl_b200 as A
-    from attention_impl_b200 import _lib
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -217,32 +632,8 @@ def run_b200(args, cfg, lens):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
-    H, D, B = cfg["heads"], cfg["head_dim"], cfg["batch"]
-    if H % world:
-        raise SystemExit("heads must divide by the number of GPUs")
-    Hl = H // world
-    dim = Hl * D
-    T = int(lens.sum())
-    torch.manual_seed(1000 * cfg["seed"] + rank)
-
-    # device-resident state: this rank's head shard of the KV pool, slot table, offsets
-    Kc = torch.empty(T, dim, dtype=torch.float16, device=dev)
-    Vc = torch.empty(T, dim, dtype=torch.float16, device=dev)
-    fill_normal(Kc)
-    fill_normal(Vc)
-    gperm = torch.Generator(device=dev).manual_seed(cfg["seed"])  # same table on every rank
-    ci = torch.randperm(T, device=dev, generator=gperm).to(torch.int32)
-    off = lens.cumsum(0).to(torch.int32).to(dev)
-    Q, K, V = (torch.randn(B, dim, device=dev, dtype=torch.float16) for _ in range(3))
-    O = torch.empty_like(Q)
-    chunk = A.ops.pick_chunk(B, Hl, D, T, dev)
-    ws = torch.empty(A.ops.decode_workspace_bytes(B, Hl, D, T, chunk), dtype=torch.uint8, device=dev)
-    kv_bytes_rank = 2 * T * Hl * D * 2
-    kv_bytes_total = kv_bytes_rank * world
-
-    def step(stages=3):
-        A.paged_kv_attention_forward(Q, K, V, Kc, Vc, ci, off, Hl, return_sp=False, chunk=chunk, workspace=ws,
-                                     out=O, stages=stages)
+    w = W(args, world, rank, dev)
+    w.setup()
 
     def fence():
         torch.cuda.synchronize()
@@ -257,22 +648,28 @@ def run_b200(args, cfg, lens):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    for _ in range(max(3, args.warmup)):
-        step()
+    warm = max(3, args.warmup)
+    for _ in range(warm):
+        w.step()
     sampler = ClockSampler(physical_gpu_index(local))
     fence()
     sampler.start()
 
-    # ---- timed region 1: inputs resident in HBM; events split the two kernels of a step
+    # ---- timed region 1: inputs resident in HBM; events isolate the dominant kernel of a step
     K_ = args.steps
+    split = w.step_split()
     ev = [[torch.cuda.Event(enable_timing=True) for _ in range(2)] for _ in range(K_)]
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for i in range(K_):
         ev[i][0].record()
-        step(1)            # partial kernel (the one that streams the KV pool)
-        ev[i][1].record()
-        step(2)            # combine kernel
+        if split:
+            split[0]()         # the kernel that moves the bytes / does the flops
+            ev[i][1].record()
+            split[1]()
+        else:
+            w.step()
+            ev[i][1].record()
     e1.record()
     fence()
     total_ms = max_over_ranks(e0.elapsed_time(e1))
@@ -280,97 +677,49 @@ def run_b200(args, cfg, lens):
     ms_per_step = total_ms / K_
 
     # ---- timed region 2: end to end through the public operator, per-step inputs from pinned host
-    hQ, hK, hV = (x.cpu().pin_memory() for x in (Q, K, V))
-    hci, hoff = ci.cpu().pin_memory(), off.cpu().pin_memory()
-    hO = torch.empty(O.shape, dtype=O.dtype).pin_memory()
-    h2d = sum(x.numel() * x.element_size() for x in (hQ, hK, hV, hci, hoff))
-    d2h = hO.numel() * hO.element_size()
-
-    def e2e_step():
-        dQ, dK, dV = (x.to(dev, non_blocking=True) for x in (hQ, hK, hV))
-        dci, doff = hci.to(dev, non_blocking=True), hoff.to(dev, non_blocking=True)
-        _, _, o = A.paged_kv_attention_forward(dQ, dK, dV, Kc, Vc, dci, doff, Hl, return_sp=False)
-        hO.copy_(o, non_blocking=True)
-        torch.cuda.current_stream().synchronize()   # the caller reads the result every step
-
+    h2d, d2h = w.e2e_setup()
     for _ in range(2):
-        e2e_step()
+        w.e2e_step()
     fence()
     f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     f0.record()
     for _ in range(K_):
-        e2e_step()
+        w.e2e_step()
     f1.record()
     fence()
     e2e_ms = max_over_ranks(f0.elapsed_time(f1)) / K_
     sampler.stop()
     sampler.join(timeout=2)
 
-    if rank != 0:
-        if world > 1:
-            dist.barrier()
-            dist.destroy_process_group()
-        return
-
-    peak, peak_src = measured_peak()
-    achieved = kv_bytes_rank / (kern_ms * 1e-3) / 1e9
-    line = {
-        "metric": "paged_decode_kv_read_bandwidth", "value": kv_bytes_total / (ms_per_step * 1e-3) / 1e12,
-        "unit": "TB/s", "n_gpus": world, "steps": K_, "warmup": max(3, args.warmup), "ms_per_step": ms_per_step,
-        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": cfg["dtype"],
-        "data": "synthetic", "tokens_per_s": B / (ms_per_step * 1e-3),
-        "config": {"workload": "large_batch_paged_decode", "batch": B, "heads": H, "head_dim": D,
-                   "ctx_range": [cfg["ctx_lo"], cfg["ctx_hi"]], "context_tokens": T,
-                   "kv_bytes_total": kv_bytes_total, "kv_bytes_per_gpu": kv_bytes_rank,
-                   "sharding": f"heads/{world} per GPU, no collective", "chunk": chunk,
-                   "l2": f"inputs larger than L2 ({kv_bytes_rank / 1e9:.1f} GB of KV per GPU per step)"},
-        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": DECODE_TRAFFIC_RATIO * kv_bytes_rank if DECODE_TRAFFIC_RATIO else None,
-                     "kernel": "paged_decode_fast_kernel<half,half,128>", "kernel_ms": kern_ms,
-                     "algorithmic_bytes_per_launch": kv_bytes_rank, "peak_source": peak_src},
-        "e2e": {"value": kv_bytes_total / (e2e_ms * 1e-3) / 1e12, "unit": "TB/s", "ms_per_step": e2e_ms,
-                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "note": "KV pool is device-resident state; q/k/v/slot table/offsets come from pinned host memory"},
-        "gpu_launches": 2 * K_,
-        "clocks": sampler.summary(),
-    }
-    if world == 1 and not args.no_cpu:
-        line["cpu_baseline"], line["parity"] = cpu_baseline_and_parity(A, cfg, lens, Q, K, V, Kc, Vc, ci, off, Hl,
-                                                                       dev)
-    print(json.dumps(line), flush=True)
+    if rank == 0:
+        hbm, tflops, src = measured_peaks()
+        per_rank = w.units_per_step_rank()
+        total_units = per_rank * world
+        if W.bound == "hbm":
+            achieved, peak, runit = per_rank / (kern_ms * 1e-3) / 1e9, hbm, "GB/s"
+        else:
+            achieved, peak, runit = per_rank / (kern_ms * 1e-3) / 1e12, tflops, "TFLOP/s"
+        line = {
+            "metric": W.metric, "value": total_units / (ms_per_step * 1e-3) / 1e12, "unit": W.unit, "n_gpus": world,
+            "steps": K_, "warmup": warm, "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": W.scaling, "vs_baseline": None, "dtype": W.dtype, "data": "synthetic",
+            "tokens_per_s": w.sequences_per_step() / (ms_per_step * 1e-3), "config": w.config(),
+            "roofline": {"bound": W.bound, "achieved": achieved, "peak": peak, "unit": runit,
+                         "frac": achieved / peak, "traffic": w.traffic(), "kernel": w.kernel_name(),
+                         "kernel_ms": kern_ms, "algorithmic_units_per_launch": per_rank, "peak_source": src},
+            "e2e": {"value": total_units / (e2e_ms * 1e-3) / 1e12, "unit": W.unit, "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "gpu_launches": w.launches_per_step() * K_,
+            "clocks": sampler.summary(),
+        }
+        if world == 1 and not args.no_cpu:
+            cb, par = w.cpu_baseline()
+            if cb:
+                line["cpu_baseline"], line["parity"] = cb, par
+        print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
-
-
-# dram__bytes_read.sum + dram__bytes_write.sum per algorithmic byte of the partial kernel, from the
-# ncu capture of a 5.3 GB case of this workload (profiles/paged_decode_fast_kernel_small_case_ncu.md);
-# every row is read once, so traffic grows in proportion to the tokens processed.
-DECODE_TRAFFIC_RATIO = 1.0017
-
-
-def cpu_baseline_and_parity(A, cfg, lens, Q, K, V, Kc, Vc, ci, off, H, dev):
-    """Oracle on the first sequences of the very tensors the GPU used: CPU timing + parity."""
-    from oracle import attention_oracle as orc
-    n_seq, per_tok = pick_cpu_sample(cfg, lens, H, budget_s=15.0, max_tokens=262144)
-    T = int(lens[:n_seq].sum())
-    passes = max(1, min(20, int(round(12.0 / max(1e-3, per_tok * T)))))   # ~12 s of CPU work
-    rows = ci[:T].long()
-    order = torch.argsort(rows)                       # compact pool in slot order
-    rank_of = torch.empty_like(order)
-    rank_of[order] = torch.arange(T, device=dev)
-    Kc_s, Vc_s = Kc[rows[order]].cpu(), Vc[rows[order]].cpu()
-    inputs = (Q[:n_seq].cpu(), K[:n_seq].cpu(), V[:n_seq].cpu(), Kc_s, Vc_s, rank_of.int().cpu(),
-              off[:n_seq].cpu())
-    sec, _ = time_cpu_oracle(inputs, H, steps=passes)
-    _, _, O_gpu = A.paged_kv_attention_forward(Q, K, V, Kc, Vc, ci, off, H, return_sp=False)
-    _, _, O32 = orc.paged_decode(*inputs, H, compute_dtype=torch.float32)
-    err = (O_gpu[:n_seq].cpu().float() - O32.float()).abs().max().item()
-    kv_bytes = 2 * T * H * cfg["head_dim"] * 2
-    sample = f"first {n_seq} of {cfg['batch']} sequences ({T} tokens, {kv_bytes / 1e9:.2f} GB of KV), mean of {passes} passes"
-    return ({"value": kv_bytes / sec / 1e12, "unit": "TB/s", "cores": torch.get_num_threads(), "kind": "port",
-             "sample": sample, "seconds": sec, "torch": torch.__version__},
-            {"max_abs_err_vs_fp32_oracle": err, "tolerance": 2e-3, "sequences_checked": n_seq})
 
 
 def main():
@@ -379,18 +728,16 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="large_decode", choices=sorted(WORKLOADS))
     ap.add_argument("--batch", type=int, default=None, help="override the batch size (profiling a small case)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (profiling runs)")
     args = ap.parse_args()
-    cfg = dict(CFG)
-    if args.batch:
-        cfg["batch"] = args.batch
-    lens = workload_lengths(cfg)
+    W = WORKLOADS[args.workload]
     if args.impl == "reference":
         if int(os.environ.get("RANK", "0")) == 0:
-            run_reference(args, cfg, lens)
+            run_reference(args, W)
         return
-    run_b200(args, cfg, lens)
+    run_b200(args, W)
 
 
 if __name__ == "__main__":

@@ -103,6 +103,54 @@ def paged_decode(
     return S_out, P_out, O
 
 
+def paged_decode_partial(Q, K_cache, V_cache, cache_indices, offsets, num_heads, scale=None):
+    """fp32 partial rows ``[B, H, D+2] = [o[D] un-normalised, m (log2 domain), l]`` of a decode over
+    the given tokens only (no new token).  Not in the reference; this is the quantity one rank of a
+    KV-split group exchanges, defined so that ``lse_combine`` of the partials of a partition of the
+    tokens plus the new token equals ``paged_decode``."""
+    B, dim = Q.shape
+    H, D = num_heads, dim // num_heads
+    if scale is None:
+        scale = 1.0 / math.sqrt(D)
+    begs, ends = _starts(offsets)
+    out = torch.zeros(B, H, D + 2, dtype=torch.float32)
+    idx = cache_indices.long()
+    log2e = 1.4426950408889634
+    for b in range(B):
+        rows = idx[begs[b]:ends[b]]
+        n = rows.numel()
+        if n == 0:
+            out[b, :, D] = float("-inf")
+            continue
+        q = Q[b].float().reshape(H, D)
+        k = K_cache[rows].float().reshape(n, H, D).permute(1, 0, 2)
+        v = V_cache[rows].float().reshape(n, H, D).permute(1, 0, 2)
+        s = torch.matmul(k, q.unsqueeze(-1)).squeeze(-1) * (scale * log2e)  # [H, n]
+        m = s.max(dim=-1).values
+        p = torch.exp2(s - m.unsqueeze(-1))
+        out[b, :, :D] = torch.matmul(p.unsqueeze(1), v).squeeze(1)
+        out[b, :, D] = m
+        out[b, :, D + 1] = p.sum(-1)
+    return out
+
+
+def lse_combine(parts, Q, K, V, num_heads, scale=None):
+    """Fold partial rows ``[G, B, H, D+2]`` and the new token (K, V) into ``[B, H*D]`` (fp32)."""
+    G, B, H, RS = parts.shape
+    D = RS - 2
+    if scale is None:
+        scale = 1.0 / math.sqrt(D)
+    log2e = 1.4426950408889634
+    q = Q.float().reshape(B, H, D)
+    s_new = (q * K.float().reshape(B, H, D)).sum(-1) * (scale * log2e)       # [B, H]
+    m_all = torch.cat([parts[..., D], s_new.unsqueeze(0)], 0)                   # [G+1, B, H]
+    M = m_all.max(0).values
+    w = torch.exp2(m_all - M)                                                    # exp2(-inf) = 0
+    num = (parts[..., :D] * w[:G].unsqueeze(-1)).sum(0) + w[G].unsqueeze(-1) * V.float().reshape(B, H, D)
+    den = (parts[..., D + 1] * w[:G]).sum(0) + w[G]
+    return (num / den.unsqueeze(-1)).reshape(B, H * D)
+
+
 def quantize_e4m3_per_head(x: torch.Tensor, num_heads: int):
     """Per-head absmax e4m3 quantisation of a ``[rows, H*D]`` pool.
 
