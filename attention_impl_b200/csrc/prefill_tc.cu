@@ -19,10 +19,11 @@
 // ATTN_B200_FLAG_TIMEOUT, all roles leave their loops, outstanding copies are given a bounded
 // wait, TMEM is freed and the CTA returns.  CTAs that start after a timeout exit at once.
 #include <cuda.h>
+#include <cstdlib>
 #include <mutex>
 #include <type_traits>
 
-#include "common.cuh"
+#include "tcgen05_utils.cuh"
 
 namespace attn {
 
@@ -35,8 +36,6 @@ constexpr int SUB_BYTES = 128 * 128;   // one [128 rows x 64 elements] swizzled 
 constexpr int TILE_BYTES = 2 * SUB_BYTES;
 constexpr int STAGES = 2;
 constexpr int THREADS = 192;
-constexpr long long WAIT_CYCLES = 2000000000LL;
-
 struct SmemLayout {
     alignas(1024) unsigned char q[TILE_BYTES];
     alignas(1024) unsigned char p[TILE_BYTES];
@@ -47,93 +46,6 @@ struct SmemLayout {
     unsigned int tmem_base;
     int abort;
 };
-
-__device__ int g_abort;   // set by the first CTA whose wait expired; reset by the launcher
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(void* bar, int count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(void* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(void* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(void* bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-    return ok != 0;
-}
-// Bounded wait.  Returns false if the CTA is aborting or the limit ran out (then it raises the abort).
-__device__ __forceinline__ bool mbar_wait(void* bar, uint32_t parity, volatile int* cta_abort, int32_t* err_flag) {
-    if (mbar_try(bar, parity)) return true;
-    const long long t0 = clock64();
-    int spins = 0;
-    while (!mbar_try(bar, parity)) {
-        if (((++spins) & 63) == 0) {
-            if (*cta_abort) return false;
-            if (clock64() - t0 > WAIT_CYCLES) {
-                *cta_abort = 1;
-                atomicExch(&g_abort, 1);
-                if (err_flag) atomicOr(err_flag, ATTN_B200_FLAG_TIMEOUT);
-                return false;
-            }
-        }
-    }
-    return true;
-}
-
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, void* bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-        ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
-}
-
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc), "r"(0u) : "memory");
-}
-__device__ __forceinline__ void umma_commit(void* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-
-// 32 consecutive fp32 columns of this thread's TMEM lane.
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
-    uint32_t* r = reinterpret_cast<uint32_t*>(v);
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr) : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-
-// Shared-memory matrix descriptor, 128-byte swizzle, sm_100 version field.
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
-    return (uint64_t)((addr >> 4) & 0x3FFF) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16) |
-           ((uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32) | (1ull << 46) | (2ull << 61);
-}
-
-template <typename T> __device__ __forceinline__ uint32_t pack2(float a, float b);
-template <> __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
-    __half2 h = __floats2half2_rn(a, b);
-    return *reinterpret_cast<uint32_t*>(&h);
-}
-template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
-    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
-    return *reinterpret_cast<uint32_t*>(&h);
-}
 
 struct Params {
     const int32_t* offsets;
@@ -354,6 +266,278 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     }
 }
 
+
+// =============================================================================================
+// Version 2: two query tiles per CTA, P kept in tensor memory, O accumulated in tensor memory.
+//
+//   warps 0-3 / 4-7   softmax warpgroup 0 / 1, one 128-row query tile each (rows q0.. / q0+128..)
+//   warp 8            TMA producer: both Q tiles, then K and V tiles into separate 2-stage rings
+//   warp 9            MMA issuer.  Per key tile j:  PV0_j, QK0_{j+1}, PV1_j, QK1_{j+1}, so that one
+//                     warpgroup's softmax runs while the tensor pipe works for the other.
+// TMEM (512 columns): S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512).  A thread reads its whole
+// S row into registers (one wait), then overwrites the first 64 columns of the same S region with P
+// rounded to the input type, two per 32-bit column; the PV MMA takes A from tensor memory.  O is
+// accumulated by the MMA itself.  The running maximum used for P is only advanced when a row's
+// new maximum exceeds it by more than 8 (log2 domain), so P <= 256; only then is O read back,
+// scaled and written again (rare after the first tiles).  The true maximum never enters the result:
+// O and l are consistent with the reference maximum, and O/l is formed in the epilogue.
+// =============================================================================================
+constexpr int THREADS2 = 320;
+
+struct SmemLayout2 {
+    alignas(1024) unsigned char q[2][TILE_BYTES];
+    alignas(1024) unsigned char k[STAGES][TILE_BYTES];
+    alignas(1024) unsigned char v[STAGES][TILE_BYTES];
+    alignas(8) unsigned long long q_full;
+    unsigned long long s_full[2], p_full[2], o_full[2];
+    unsigned long long k_full[STAGES], k_empty[STAGES], v_full[STAGES], v_empty[STAGES];
+    unsigned int tmem_base;
+    int abort;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(THREADS2, 1)
+prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                   const __grid_constant__ CUtensorMap map_v, const Params p) {
+    extern __shared__ unsigned char smem_raw[];
+    SmemLayout2& sm = *reinterpret_cast<SmemLayout2*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int b = blockIdx.z, h = blockIdx.y;
+    const int tp = p.n_qtiles - 1 - (int)blockIdx.x;       // pair index, heavy first (n_qtiles counts pairs here)
+    const int64_t seq_beg = b ? p.offsets[b - 1] : 0;
+    const int64_t seq_end = p.offsets[b];
+    if (seq_beg < 0 || seq_end < seq_beg || seq_end > p.n_tokens) {
+        if (p.err_flag && threadIdx.x == 0) atomicOr(p.err_flag, ATTN_B200_FLAG_BAD_OFFSETS);
+        return;
+    }
+    const int L = (int)(seq_end - seq_beg);
+    const int q0 = tp * 2 * BM;
+    if (q0 >= L) return;
+    if (*(volatile int*)&g_abort) return;
+    // key tiles per warpgroup: tile index of its query tile + 1; warpgroup 1 idle if its rows are past the end
+    const int n0 = 2 * tp + 1;
+    const int n1 = (q0 + BM < L) ? 2 * tp + 2 : 0;
+    const int nmax = n1 > n0 ? n1 : n0;
+    volatile int* cta_abort = &sm.abort;
+
+    if (threadIdx.x == 0) {
+        mbar_init(&sm.q_full, 1);
+        for (int w = 0; w < 2; ++w) {
+            mbar_init(&sm.s_full[w], 1);
+            mbar_init(&sm.p_full[w], 128);
+            mbar_init(&sm.o_full[w], 1);
+        }
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&sm.k_full[s], 1);
+            mbar_init(&sm.k_empty[s], 1);
+            mbar_init(&sm.v_full[s], 1);
+            mbar_init(&sm.v_empty[s], 1);
+        }
+        sm.abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 9) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(512));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = sm.tmem_base;
+    const int col0 = h * HD;
+
+    int issued = 0;   // producer: key tiles issued (for the drain on abort)
+    if (warp == 8) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            mbar_expect_tx(&sm.q_full, 2 * TILE_BYTES);
+            for (int w = 0; w < 2; ++w) {
+                tma_load_2d(sm.q[w], &map_q, col0, (int)(seq_beg + q0 + w * BM), &sm.q_full);
+                tma_load_2d(sm.q[w] + SUB_BYTES, &map_q, col0 + 64, (int)(seq_beg + q0 + w * BM), &sm.q_full);
+            }
+            for (int j = 0; j < nmax; ++j) {
+                const int s = j & 1;
+                const uint32_t ph = ((j - STAGES) >> 1) & 1;
+                const int row = (int)(seq_beg + (int64_t)j * BN);
+                if (j >= STAGES && !mbar_wait(&sm.k_empty[s], ph, cta_abort, p.err_flag)) break;
+                mbar_expect_tx(&sm.k_full[s], TILE_BYTES);
+                tma_load_2d(sm.k[s], &map_k, col0, row, &sm.k_full[s]);
+                tma_load_2d(sm.k[s] + SUB_BYTES, &map_k, col0 + 64, row, &sm.k_full[s]);
+                if (j >= STAGES && !mbar_wait(&sm.v_empty[s], ph, cta_abort, p.err_flag)) { issued = j; break; }
+                mbar_expect_tx(&sm.v_full[s], TILE_BYTES);
+                tma_load_2d(sm.v[s], &map_v, col0, row, &sm.v_full[s]);
+                tma_load_2d(sm.v[s] + SUB_BYTES, &map_v, col0 + 64, row, &sm.v_full[s]);
+                issued = j + 1;
+            }
+        }
+    } else if (warp == 9) {
+        // ------------------------------------------------------------------ MMA issuer
+        constexpr uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
+        constexpr uint32_t idesc_qk = (1u << 4) | (fmt << 7) | (fmt << 10) | ((BN >> 3) << 17) | ((BM >> 4) << 24);
+        constexpr uint32_t idesc_pv = idesc_qk | (1u << 16);   // B (= V) is MN-major
+        const int nw[2] = {n0, n1};
+        auto issue_qk = [&](int w, int j) {      // S_w = Q_w K_j^T
+            const uint32_t q_addr = smem_u32(sm.q[w]), k_addr = smem_u32(sm.k[j & 1]);
+#pragma unroll
+            for (int kk = 0; kk < HD / 16; ++kk) {
+                const uint32_t off = (kk >> 2) * SUB_BYTES + (kk & 3) * 32;
+                umma_f16(tmem + w * 128, smem_desc(q_addr + off, 16, 1024), smem_desc(k_addr + off, 16, 1024),
+                         idesc_qk, kk > 0);
+            }
+            umma_commit(&sm.s_full[w]);
+        };
+        auto issue_pv = [&](int w, int j) {      // O_w (+)= P_w V_j, P_w in the first 64 columns of S_w
+            const uint32_t v_addr = smem_u32(sm.v[j & 1]);
+#pragma unroll
+            for (int kk = 0; kk < BN / 16; ++kk)
+                umma_f16_ts(tmem + 256 + w * 128, tmem + w * 128 + kk * 8,
+                            smem_desc(v_addr + kk * 2048, SUB_BYTES, 1024), idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+            umma_commit(&sm.o_full[w]);
+        };
+        bool ok = mbar_wait(&sm.q_full, 0, cta_abort, p.err_flag) && mbar_wait(&sm.k_full[0], 0, cta_abort, p.err_flag);
+        if (ok) {
+            tc_fence_after();
+            if (lane == 0) {
+                issue_qk(0, 0);
+                if (n1 > 0) issue_qk(1, 0);
+                umma_commit(&sm.k_empty[0]);
+            }
+            __syncwarp();
+        }
+        for (int j = 0; ok && j < nmax; ++j) {
+            const int s = j & 1;
+            const uint32_t ph = (j >> 1) & 1;
+            for (int w = 0; w < 2 && ok; ++w) {
+                if (j < nw[w]) {
+                    if (!(ok = mbar_wait(&sm.p_full[w], j & 1, cta_abort, p.err_flag))) break;
+                    if (w == 0 || j >= n0) { if (!(ok = mbar_wait(&sm.v_full[s], ph, cta_abort, p.err_flag))) break; }
+                    tc_fence_after();
+                    if (lane == 0) issue_pv(w, j);
+                    __syncwarp();
+                }
+                if (w == 1 && lane == 0) umma_commit(&sm.v_empty[s]);
+                if (j + 1 < nw[w]) {
+                    if (w == 0 || j + 1 >= n0) {
+                        if (!(ok = mbar_wait(&sm.k_full[(j + 1) & 1], ((j + 1) >> 1) & 1, cta_abort, p.err_flag))) break;
+                    }
+                    tc_fence_after();
+                    if (lane == 0) issue_qk(w, j + 1);
+                    __syncwarp();
+                }
+                if (w == 1 && j + 1 < nmax && lane == 0) umma_commit(&sm.k_empty[(j + 1) & 1]);
+                __syncwarp();
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ softmax warpgroups
+        const int w = warp >> 2;                          // warpgroup = query tile of the pair
+        const int r = threadIdx.x & 127;                  // row of the tile == TMEM lane
+        const int nk = w ? n1 : n0;
+        const int tq = 2 * tp + w;                        // query tile index == index of its diagonal key tile
+        const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+        const uint32_t s_addr = lane_base + w * 128, o_addr = lane_base + 256 + w * 128;
+        float m_ref = -INFINITY, l = 0.f;
+        bool ok = true;
+        for (int j = 0; j < nk; ++j) {
+            if (!(ok = mbar_wait(&sm.s_full[w], j & 1, cta_abort, p.err_flag))) break;
+            tc_fence_after();
+            float sv[BN];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) tmem_ld32_nowait(s_addr + c * 32, sv + c * 32);
+            tmem_ld_wait();
+            float mx = -INFINITY;
+            if (j == tq) {
+#pragma unroll
+                for (int i = 0; i < BN; ++i) {
+                    if (i > r) sv[i] = -INFINITY;
+                    mx = fmaxf(mx, sv[i]);
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < BN; ++i) mx = fmaxf(mx, sv[i]);
+            }
+            const float m_new = fmaxf(m_ref, mx * p.scale_log2);
+            // advance the reference maximum only when some row of the warp outgrew it by 2^8
+            if (__any_sync(0xffffffffu, m_new > m_ref + 8.f)) {
+                if (j > 0) {
+                    const float alpha = fast_exp2(m_ref - m_new);
+                    l *= alpha;
+                    if (!(ok = mbar_wait(&sm.o_full[w], (j - 1) & 1, cta_abort, p.err_flag))) break;
+                    tc_fence_after();
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        float ov[32];
+                        tmem_ld32(o_addr + c * 32, ov);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) ov[i] *= alpha;
+                        tmem_st32(o_addr + c * 32, reinterpret_cast<const uint32_t*>(ov));
+                    }
+                    tmem_st_wait();
+                }
+                m_ref = m_new;
+            }
+            float rs = 0.f;
+            uint32_t pk[BN / 2];
+#pragma unroll
+            for (int i = 0; i < BN; i += 2) {
+                const float p0 = fast_exp2(fmaf(sv[i], p.scale_log2, -m_ref));
+                const float p1 = fast_exp2(fmaf(sv[i + 1], p.scale_log2, -m_ref));
+                rs += p0 + p1;
+                pk[i >> 1] = pack2<T>(p0, p1);
+            }
+            l += rs;
+            tmem_st32(s_addr, pk);
+            tmem_st32(s_addr + 32, pk + 32);
+            tmem_st_wait();
+            tc_fence_before();
+            mbar_arrive(&sm.p_full[w]);
+        }
+        if (ok && nk > 0) ok = mbar_wait(&sm.o_full[w], (nk - 1) & 1, cta_abort, p.err_flag);
+        if (ok && nk > 0) {
+            tc_fence_after();
+            const bool valid = q0 + w * BM + r < L;
+            const float inv = 1.f / l;
+            const int64_t row = seq_beg + q0 + w * BM + r;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                float ov[32];
+                tmem_ld32(o_addr + c * 32, ov);
+                if (!valid) continue;
+                if (p.out_f32) {
+                    float4* dst = reinterpret_cast<float4*>((float*)p.out + (row * p.H + h) * HD + c * 32);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i)
+                        dst[i] = make_float4(ov[4 * i] * inv, ov[4 * i + 1] * inv, ov[4 * i + 2] * inv, ov[4 * i + 3] * inv);
+                } else {
+                    uint4* dst = reinterpret_cast<uint4*>((T*)p.out + (row * p.H + h) * HD + c * 32);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        dst[i] = make_uint4(pack2<T>(ov[8 * i] * inv, ov[8 * i + 1] * inv),
+                                            pack2<T>(ov[8 * i + 2] * inv, ov[8 * i + 3] * inv),
+                                            pack2<T>(ov[8 * i + 4] * inv, ov[8 * i + 5] * inv),
+                                            pack2<T>(ov[8 * i + 6] * inv, ov[8 * i + 7] * inv));
+                }
+            }
+        }
+    }
+    // ---------------------------------------------------------------------- teardown
+    if (warp == 8 && lane == 0 && sm.abort) {
+        const long long t0 = clock64();
+        while (!mbar_try(&sm.q_full, 0) && clock64() - t0 < WAIT_CYCLES) {}
+        for (int j = issued > STAGES ? issued - STAGES : 0; j < issued; ++j) {
+            const uint32_t ph = (j >> 1) & 1;
+            while (!(mbar_try(&sm.k_full[j & 1], ph) && mbar_try(&sm.v_full[j & 1], ph)) && clock64() - t0 < WAIT_CYCLES) {}
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 9) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512));
+    }
+}
+
 // ---------------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------------
@@ -407,13 +591,28 @@ int prefill_tc_launch(const void* q, const void* k, const void* v, const int32_t
     if ((rc = make_map(&mq, q, n_tokens, H, dtype)) || (rc = make_map(&mk, k, n_tokens, H, dtype)) ||
         (rc = make_map(&mv, v, n_tokens, H, dtype)))
         return rc;
-    const int smem = (int)sizeof(SmemLayout) + 1024;
-    Params p{offsets, out, B, H, n_tokens, (max_len + BM - 1) / BM, scale * kLog2e, out_f32, err_flag};
+    static const bool use_v1 = [] { const char* e = getenv("ATTN_B200_PREFILL_V1"); return e && e[0] == '1'; }();
+    const int rows_per_cta = use_v1 ? BM : 2 * BM;
+    const int smem = (int)(use_v1 ? sizeof(SmemLayout) : sizeof(SmemLayout2)) + 1024;
+    Params p{offsets, out, B, H, n_tokens, (max_len + rows_per_cta - 1) / rows_per_cta, scale * kLog2e, out_f32,
+             err_flag};
     dim3 grid(p.n_qtiles, H, B);
     void* abort_addr = nullptr;
     cudaError_t e = cudaGetSymbolAddress(&abort_addr, g_abort);
     if (e != cudaSuccess) return (int)e;
     if ((e = cudaMemsetAsync(abort_addr, 0, sizeof(int), st)) != cudaSuccess) return (int)e;
+    if (!use_v1) {
+        if (dtype == ATTN_B200_BF16) {
+            if ((e = cudaFuncSetAttribute(prefill_tc2_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) != cudaSuccess)
+                return (int)e;
+            prefill_tc2_kernel<__nv_bfloat16><<<grid, THREADS2, smem, st>>>(mq, mk, mv, p);
+        } else {
+            if ((e = cudaFuncSetAttribute(prefill_tc2_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) != cudaSuccess)
+                return (int)e;
+            prefill_tc2_kernel<__half><<<grid, THREADS2, smem, st>>>(mq, mk, mv, p);
+        }
+        return (int)cudaGetLastError();
+    }
     if (dtype == ATTN_B200_BF16) {
         if ((e = cudaFuncSetAttribute(prefill_tc_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) != cudaSuccess)
             return (int)e;
