@@ -272,17 +272,28 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
 //
 //   warps 0-3 / 4-7   softmax warpgroup 0 / 1, one 128-row query tile each (rows q0.. / q0+128..)
 //   warp 8            TMA producer: both Q tiles, then K and V tiles into separate 2-stage rings
+//   warps 10-11       idle (they complete the third warpgroup so that setmaxnreg can move registers)
 //   warp 9            MMA issuer.  Per key tile j:  PV0_j, QK0_{j+1}, PV1_j, QK1_{j+1}, so that one
 //                     warpgroup's softmax runs while the tensor pipe works for the other.
 // TMEM (512 columns): S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512).  A thread reads its whole
 // S row into registers (one wait), then overwrites the first 64 columns of the same S region with P
-// rounded to the input type, two per 32-bit column; the PV MMA takes A from tensor memory.  O is
+// in the input type, two per 32-bit column; the PV MMA takes A from tensor memory and B = V from
+// shared memory.  O is
 // accumulated by the MMA itself.  The running maximum used for P is only advanced when a row's
-// new maximum exceeds it by more than 8 (log2 domain), so P <= 256; only then is O read back,
+// new maximum exceeds it by more than 1 (fp16 inputs) or 4 (bf16 inputs) in the log2 domain, so P
+// stays small; only then is O read back,
 // scaled and written again (rare after the first tiles).  The true maximum never enters the result:
 // O and l are consistent with the reference maximum, and O/l is formed in the epilogue.
 // =============================================================================================
-constexpr int THREADS2 = 320;
+#ifdef ATTN_B200_TRACE
+// Development aid (not part of the product build): clock64 stamps of one CTA's pipeline events.
+__device__ long long g_trace[3 * 64 * 8];
+#define TRACE(role, j, slot) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (j) < 64) \
+    g_trace[((role) * 64 + (j)) * 8 + (slot)] = clock64(); } while (0)
+#else
+#define TRACE(role, j, slot) do {} while (0)
+#endif
+constexpr int THREADS2 = 384;   // 3 warpgroups: softmax 0, softmax 1, {TMA, MMA, 2 idle warps}
 
 struct SmemLayout2 {
     alignas(1024) unsigned char q[2][TILE_BYTES];
@@ -347,7 +358,12 @@ prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     const uint32_t tmem = sm.tmem_base;
     const int col0 = h * HD;
 
+    // Register reallocation.  The CTA is launched with 168 registers per thread (12 warps), and
+    // setmaxnreg can only move registers inside that allocation: 8 * 224 + 4 * 56 = 12 * 168.  A
+    // request beyond the pool would block forever, so these two numbers must keep that identity.
     int issued = 0;   // producer: key tiles issued (for the drain on abort)
+    if (warp >= 8) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
     if (warp == 8) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
@@ -375,7 +391,9 @@ prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         // ------------------------------------------------------------------ MMA issuer
         constexpr uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
         constexpr uint32_t idesc_qk = (1u << 4) | (fmt << 7) | (fmt << 10) | ((BN >> 3) << 17) | ((BM >> 4) << 24);
-        constexpr uint32_t idesc_pv = idesc_qk | (1u << 16);   // B (= V) is MN-major
+        // P (A, from tensor memory) and V (B, MN-major) share the input type: a kind::f16 MMA with an
+        // fp16 A and a bf16 B raised an illegal-instruction fault on this hardware.
+        constexpr uint32_t idesc_pv = idesc_qk | (1u << 16);
         const int nw[2] = {n0, n1};
         auto issue_qk = [&](int w, int j) {      // S_w = Q_w K_j^T
             const uint32_t q_addr = smem_u32(sm.q[w]), k_addr = smem_u32(sm.k[j & 1]);
@@ -413,7 +431,7 @@ prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                     if (!(ok = mbar_wait(&sm.p_full[w], j & 1, cta_abort, p.err_flag))) break;
                     if (w == 0 || j >= n0) { if (!(ok = mbar_wait(&sm.v_full[s], ph, cta_abort, p.err_flag))) break; }
                     tc_fence_after();
-                    if (lane == 0) issue_pv(w, j);
+                    if (lane == 0) { TRACE(2, j, w * 4 + 0); issue_pv(w, j); TRACE(2, j, w * 4 + 1); }
                     __syncwarp();
                 }
                 if (w == 1 && lane == 0) umma_commit(&sm.v_empty[s]);
@@ -422,15 +440,17 @@ prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                         if (!(ok = mbar_wait(&sm.k_full[(j + 1) & 1], ((j + 1) >> 1) & 1, cta_abort, p.err_flag))) break;
                     }
                     tc_fence_after();
-                    if (lane == 0) issue_qk(w, j + 1);
+                    if (lane == 0) { TRACE(2, j, w * 4 + 2); issue_qk(w, j + 1); TRACE(2, j, w * 4 + 3); }
                     __syncwarp();
                 }
                 if (w == 1 && j + 1 < nmax && lane == 0) umma_commit(&sm.k_empty[(j + 1) & 1]);
                 __syncwarp();
             }
         }
+    }
     } else {
         // ------------------------------------------------------------------ softmax warpgroups
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
         const int w = warp >> 2;                          // warpgroup = query tile of the pair
         const int r = threadIdx.x & 127;                  // row of the tile == TMEM lane
         const int nk = w ? n1 : n0;
@@ -438,28 +458,37 @@ prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
         const uint32_t s_addr = lane_base + w * 128, o_addr = lane_base + 256 + w * 128;
         float m_ref = -INFINITY, l = 0.f;
+        // P <= 2^kLazy.  The exponent argument passes through fp16: keeping it below 1 (fp16
+        // inputs) or 4 (bf16 inputs) keeps its rounding below the rounding of P itself.
+        constexpr float kLazy = std::is_same<T, __nv_bfloat16>::value ? 4.f : 1.f;
         bool ok = true;
         for (int j = 0; j < nk; ++j) {
+            if (r == 0) TRACE(w, j, 0);
             if (!(ok = mbar_wait(&sm.s_full[w], j & 1, cta_abort, p.err_flag))) break;
             tc_fence_after();
+            if (r == 0) TRACE(w, j, 1);
             float sv[BN];
 #pragma unroll
             for (int c = 0; c < 4; ++c) tmem_ld32_nowait(s_addr + c * 32, sv + c * 32);
             tmem_ld_wait();
-            float mx = -INFINITY;
+            if (r == 0) TRACE(w, j, 2);
             if (j == tq) {
 #pragma unroll
-                for (int i = 0; i < BN; ++i) {
+                for (int i = 0; i < BN; ++i)
                     if (i > r) sv[i] = -INFINITY;
-                    mx = fmaxf(mx, sv[i]);
-                }
-            } else {
-#pragma unroll
-                for (int i = 0; i < BN; ++i) mx = fmaxf(mx, sv[i]);
             }
+            // eight independent chains, then a tree: a single 128-long dependent chain would cost
+            // its full latency with only two softmax warps per scheduler to hide it
+            float mx8[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) mx8[i] = sv[i];
+#pragma unroll
+            for (int i = 8; i < BN; ++i) mx8[i & 7] = fmaxf(mx8[i & 7], sv[i]);
+            const float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
+                                   fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
             const float m_new = fmaxf(m_ref, mx * p.scale_log2);
             // advance the reference maximum only when some row of the warp outgrew it by 2^8
-            if (__any_sync(0xffffffffu, m_new > m_ref + 8.f)) {
+            if (__any_sync(0xffffffffu, m_new > m_ref + kLazy)) {
                 if (j > 0) {
                     const float alpha = fast_exp2(m_ref - m_new);
                     l *= alpha;
@@ -477,21 +506,59 @@ prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 }
                 m_ref = m_new;
             }
+            if (r == 0) TRACE(w, j, 3);
+            // P = 2^(s*scale - m_ref): the exponent argument is formed in fp32, packed to f16x2 and
+            // passed through the packed ex2 of the special-function unit (two results per
+            // operation).  fp16 inputs: that result is P itself and row sums run over eight short
+            // fp16x2 chains before widening.  bf16 inputs: A and B of one MMA must share a type, so
+            // the pair is widened, summed in fp32 and re-packed as bf16.
             float rs = 0.f;
-            uint32_t pk[BN / 2];
+            if constexpr (std::is_same<T, __half>::value) {
+                __half2 hs[8];
 #pragma unroll
-            for (int i = 0; i < BN; i += 2) {
-                const float p0 = fast_exp2(fmaf(sv[i], p.scale_log2, -m_ref));
-                const float p1 = fast_exp2(fmaf(sv[i + 1], p.scale_log2, -m_ref));
-                rs += p0 + p1;
-                pk[i >> 1] = pack2<T>(p0, p1);
+                for (int c = 0; c < 2; ++c) {           // 64 keys -> 32 packed columns per store
+                    uint32_t pk[32];
+#pragma unroll
+                    for (int i = 0; i < 64; i += 2) {
+                        const float x0 = fmaf(sv[c * 64 + i], p.scale_log2, -m_ref);
+                        const float x1 = fmaf(sv[c * 64 + i + 1], p.scale_log2, -m_ref);
+                        const uint32_t e = ex2_f16x2(pack2<__half>(x0, x1));
+                        pk[i >> 1] = e;
+                        const __half2 eh = *reinterpret_cast<const __half2*>(&e);
+                        const int g = (i >> 1) & 7;
+                        hs[g] = (c == 0 && i < 16) ? eh : __hadd2(hs[g], eh);
+                    }
+                    tmem_st32(s_addr + c * 32, pk);
+                }
+#pragma unroll
+                for (int g = 0; g < 8; g += 2) {
+                    const float2 a = __half22float2(hs[g]), b2 = __half22float2(hs[g + 1]);
+                    rs += (a.x + a.y) + (b2.x + b2.y);
+                }
+            } else {
+                float rs4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    uint32_t pk[32];
+#pragma unroll
+                    for (int i = 0; i < 64; i += 2) {
+                        const float x0 = fmaf(sv[c * 64 + i], p.scale_log2, -m_ref);
+                        const float x1 = fmaf(sv[c * 64 + i + 1], p.scale_log2, -m_ref);
+                        const uint32_t e = ex2_f16x2(pack2<__half>(x0, x1));
+                        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&e));
+                        rs4[(i >> 1) & 3] += f.x + f.y;
+                        pk[i >> 1] = pack2<__nv_bfloat16>(f.x, f.y);
+                    }
+                    tmem_st32(s_addr + c * 32, pk);
+                }
+                rs = (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
             }
             l += rs;
-            tmem_st32(s_addr, pk);
-            tmem_st32(s_addr + 32, pk + 32);
+            if (r == 0) TRACE(w, j, 4);
             tmem_st_wait();
             tc_fence_before();
             mbar_arrive(&sm.p_full[w]);
+            if (r == 0) TRACE(w, j, 5);
         }
         if (ok && nk > 0) ok = mbar_wait(&sm.o_full[w], (nk - 1) & 1, cta_abort, p.err_flag);
         if (ok && nk > 0) {
@@ -574,6 +641,12 @@ static int make_map(CUtensorMap* map, const void* base, int64_t n_tokens, int H,
 }
 
 }  // namespace tc
+
+#ifdef ATTN_B200_TRACE
+extern "C" __attribute__((visibility("default"))) int attn_b200_debug_read_trace(long long* host, int n) {
+    return (int)cudaMemcpyFromSymbol(host, tc::g_trace, sizeof(long long) * n);
+}
+#endif
 
 bool prefill_tc_supported(int D, int dtype) {
     return D == tc::HD && (dtype == ATTN_B200_F16 || dtype == ATTN_B200_BF16);
