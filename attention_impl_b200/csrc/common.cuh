@@ -49,6 +49,16 @@ __device__ __forceinline__ void unpack4_e4m3(uint32_t w, float& a, float& b, flo
     a = f0.x; b = f0.y; c = f1.x; d = f1.y;
 }
 
+// Four e4m3 bytes -> two packed fp16 pairs (elements 0,1 and 2,3).
+__device__ __forceinline__ void e4m3x4_to_half2x2(uint32_t w, __half2& lo, __half2& hi) {
+    uint32_t a, b;
+    asm("{\n\t.reg .b16 l, h;\n\tmov.b32 {l, h}, %2;\n\t"
+        "cvt.rn.f16x2.e4m3x2 %0, l;\n\tcvt.rn.f16x2.e4m3x2 %1, h;\n\t}"
+        : "=r"(a), "=r"(b) : "r"(w));
+    lo = *reinterpret_cast<__half2*>(&a);
+    hi = *reinterpret_cast<__half2*>(&b);
+}
+
 // ---------------------------------------------------------------------------------------------
 // memory
 // ---------------------------------------------------------------------------------------------

@@ -137,12 +137,24 @@ paged_decode_fast_kernel(const DecodeParams p) {
     const char* kbase = (const char*)p.k_cache + ((int64_t)h * D + sub * EPL) * sizeof(KVT);
     const char* vbase = (const char*)p.v_cache + ((int64_t)h * D + sub * EPL) * sizeof(KVT);
 
-    float qf[EPL];
+    // 16-bit KV: q in fp32, pre-multiplied by scale*log2(e).  e4m3 KV: q stays unscaled in packed
+    // fp16 (products with the 4-significant-bit e4m3 values are formed by HFMA2 and the 16
+    // products of a lane are summed in fp16 before widening: the error, ~1e-3 of a score's
+    // standard deviation, is far below the e4m3 quantisation it rides on); the combined factor
+    // scale*log2(e)*k_scale[h] is applied to the reduced fp32 score.
+    constexpr bool kFp8 = sizeof(KVT) == 1;
+    float qf[kFp8 ? 1 : EPL];
+    __half2 q2[kFp8 ? EPL / 2 : 1];
+    float qs = p.scale_log2 * (p.k_scale ? p.k_scale[h] : 1.f);
     {
         const QT* qp = (const QT*)p.q + ((int64_t)un.b * p.H + h) * D + sub * EPL;
-        const float qs = p.scale_log2 * (p.k_scale ? p.k_scale[h] : 1.f);
+        if constexpr (kFp8) {
 #pragma unroll
-        for (int i = 0; i < EPL; ++i) qf[i] = to_f32<QT>(qp[i]) * qs;
+            for (int i = 0; i < EPL / 2; ++i) q2[i] = __floats2half2_rn(to_f32<QT>(qp[2 * i]), to_f32<QT>(qp[2 * i + 1]));
+        } else {
+#pragma unroll
+            for (int i = 0; i < EPL; ++i) qf[i] = to_f32<QT>(qp[i]) * qs;
+        }
     }
     float m = -INFINITY, l = 0.f, o[EPL];
 #pragma unroll
@@ -187,12 +199,26 @@ paged_decode_fast_kernel(const DecodeParams p) {
         float tmax = -INFINITY;
 #pragma unroll
         for (int j = 0; j < U; ++j) {
-            float kf[EPL];
-            RowChunk<KVT, EPL>::unpack(kr[j], kf);
             float acc = 0.f;
+            if constexpr (kFp8) {
+                const uint32_t w4[4] = {kr[j].x, kr[j].y, kr[j].z, kr[j].w};
+                __half2 a0 = __float2half2_rn(0.f), a1 = a0;
 #pragma unroll
-            for (int i = 0; i < EPL; ++i) acc = fmaf(qf[i], kf[i], acc);
-            acc = group_sum<LPR>(acc);
+                for (int i = 0; i < 4; ++i) {
+                    __half2 lo, hi;
+                    e4m3x4_to_half2x2(w4[i], lo, hi);
+                    a0 = __hfma2(q2[2 * i], lo, a0);
+                    a1 = __hfma2(q2[2 * i + 1], hi, a1);
+                }
+                const float2 f = __half22float2(__hadd2(a0, a1));
+                acc = group_sum<LPR>(f.x + f.y) * qs;
+            } else {
+                float kf[EPL];
+                RowChunk<KVT, EPL>::unpack(kr[j], kf);
+#pragma unroll
+                for (int i = 0; i < EPL; ++i) acc = fmaf(qf[i], kf[i], acc);
+                acc = group_sum<LPR>(acc);
+            }
             s[j] = sl[j] >= 0 ? acc : -INFINITY;
             tmax = fmaxf(tmax, s[j]);
         }
@@ -214,14 +240,41 @@ paged_decode_fast_kernel(const DecodeParams p) {
             l *= alpha;
 #pragma unroll
             for (int i = 0; i < EPL; ++i) o[i] *= alpha;
+            if constexpr (kFp8) {
+                // p*v summed over the tile's U rows in fp16x2 (p <= 1, |v| <= 448), widened once per tile
+                __half2 oa[EPL / 2];
 #pragma unroll
-            for (int j = 0; j < U; ++j) {
-                const float pj = fast_exp2(s[j] - m_new);
-                l += pj;
-                float vf[EPL];
-                RowChunk<KVT, EPL>::unpack(vr[j], vf);
+                for (int i = 0; i < EPL / 2; ++i) oa[i] = __float2half2_rn(0.f);
 #pragma unroll
-                for (int i = 0; i < EPL; ++i) o[i] = fmaf(pj, vf[i], o[i]);
+                for (int j = 0; j < U; ++j) {
+                    const float pj = fast_exp2(s[j] - m_new);
+                    l += pj;
+                    const __half2 p2 = __float2half2_rn(pj);
+                    const uint32_t w4[4] = {vr[j].x, vr[j].y, vr[j].z, vr[j].w};
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        __half2 lo, hi;
+                        e4m3x4_to_half2x2(w4[i], lo, hi);
+                        oa[2 * i] = __hfma2(p2, lo, oa[2 * i]);
+                        oa[2 * i + 1] = __hfma2(p2, hi, oa[2 * i + 1]);
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < EPL / 2; ++i) {
+                    const float2 f = __half22float2(oa[i]);
+                    o[2 * i] += f.x;
+                    o[2 * i + 1] += f.y;
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < U; ++j) {
+                    const float pj = fast_exp2(s[j] - m_new);
+                    l += pj;
+                    float vf[EPL];
+                    RowChunk<KVT, EPL>::unpack(vr[j], vf);
+#pragma unroll
+                    for (int i = 0; i < EPL; ++i) o[i] = fmaf(pj, vf[i], o[i]);
+                }
             }
             m = m_new;
         }

@@ -458,9 +458,9 @@ prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
         const uint32_t s_addr = lane_base + w * 128, o_addr = lane_base + 256 + w * 128;
         float m_ref = -INFINITY, l = 0.f;
-        // P <= 2^kLazy.  The exponent argument passes through fp16: keeping it below 1 (fp16
-        // inputs) or 4 (bf16 inputs) keeps its rounding below the rounding of P itself.
-        constexpr float kLazy = std::is_same<T, __nv_bfloat16>::value ? 4.f : 1.f;
+        // P <= 2^kLazy.  On the fp16 path the exponent argument passes through fp16: keeping it
+        // below 1 keeps its rounding below the rounding of P itself.
+        constexpr float kLazy = std::is_same<T, __nv_bfloat16>::value ? 8.f : 1.f;
         bool ok = true;
         for (int j = 0; j < nk; ++j) {
             if (r == 0) TRACE(w, j, 0);
@@ -510,8 +510,9 @@ prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             // P = 2^(s*scale - m_ref): the exponent argument is formed in fp32, packed to f16x2 and
             // passed through the packed ex2 of the special-function unit (two results per
             // operation).  fp16 inputs: that result is P itself and row sums run over eight short
-            // fp16x2 chains before widening.  bf16 inputs: A and B of one MMA must share a type, so
-            // the pair is widened, summed in fp32 and re-packed as bf16.
+            // fp16x2 chains before widening.  bf16 inputs: A and B of one MMA must share a type, and
+            // widening + re-packing the f16x2 result costs more issue slots than it saves, so that
+            // path uses the fp32 ex2.
             float rs = 0.f;
             if constexpr (std::is_same<T, __half>::value) {
                 __half2 hs[8];
@@ -542,12 +543,10 @@ prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                     uint32_t pk[32];
 #pragma unroll
                     for (int i = 0; i < 64; i += 2) {
-                        const float x0 = fmaf(sv[c * 64 + i], p.scale_log2, -m_ref);
-                        const float x1 = fmaf(sv[c * 64 + i + 1], p.scale_log2, -m_ref);
-                        const uint32_t e = ex2_f16x2(pack2<__half>(x0, x1));
-                        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&e));
-                        rs4[(i >> 1) & 3] += f.x + f.y;
-                        pk[i >> 1] = pack2<__nv_bfloat16>(f.x, f.y);
+                        const float p0 = fast_exp2(fmaf(sv[c * 64 + i], p.scale_log2, -m_ref));
+                        const float p1 = fast_exp2(fmaf(sv[c * 64 + i + 1], p.scale_log2, -m_ref));
+                        rs4[(i >> 1) & 3] += p0 + p1;
+                        pk[i >> 1] = pack2<T>(p0, p1);
                     }
                     tmem_st32(s_addr + c * 32, pk);
                 }
