@@ -438,18 +438,33 @@ lse_combine_kernel(const CombineParams p) {
     L = group_sum<32>(L);
     const float w_new = p.k_new ? exp2f(s_new - M) : 0.f;
     L += w_new;
-    // pass 3: numerator, lanes over dims
+    // pass 3: numerator.  Lanes over dims (stride 32, up to 8 accumulators = 256 dims per sweep), units
+    // in the outer loop so that the row loads of successive units are independent and overlap.
     const float inv = (p.out && L > 0.f) ? 1.f / L : 1.f;
-    for (int d = lane; d < D; d += 32) {
-        float acc = 0.f;
+    for (int dbase = 0; dbase < D; dbase += 256) {
+        float acc[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+#pragma unroll 4
         for (int i = 0; i < count; ++i) {
             const float* row = p.parts + (first + i * stride) * RS;
             const float mi = row[D];
-            if (mi > -INFINITY) acc = fmaf(row[d], exp2f(mi - M), acc);
+            const float wi = mi > -INFINITY ? exp2f(mi - M) : 0.f;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const int d = dbase + k * 32 + lane;
+                if (d < D) acc[k] = fmaf(row[d], wi, acc[k]);
+            }
         }
-        if (p.k_new) acc = fmaf(w_new, to_f32<QT>(((const QT*)p.v_new)[((int64_t)b * p.H + h) * D + d]), acc);
-        if (p.out) ((QT*)p.out)[((int64_t)b * p.H + h) * D + d] = from_f32<QT>(acc * inv);
-        else p.part_out[((int64_t)b * p.H + h) * RS + d] = acc;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const int d = dbase + k * 32 + lane;
+            if (d >= D) continue;
+            float a = acc[k];
+            if (p.k_new) a = fmaf(w_new, to_f32<QT>(((const QT*)p.v_new)[((int64_t)b * p.H + h) * D + d]), a);
+            if (p.out) ((QT*)p.out)[((int64_t)b * p.H + h) * D + d] = from_f32<QT>(a * inv);
+            else p.part_out[((int64_t)b * p.H + h) * RS + d] = a;
+        }
     }
     if (!p.out && lane == 0) {
         p.part_out[((int64_t)b * p.H + h) * RS + D] = M;

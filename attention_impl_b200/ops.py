@@ -180,6 +180,82 @@ def paged_kv_attention_forward(Q, K, V, K_cache, V_cache, cache_indices, offsets
     return [S, P, O]
 
 
+class PagedDecodeGraph:
+    """A paged decode step captured in a CUDA graph: one graph launch per step instead of two kernel
+    launches plus the Python wrapper, which is what bounds small batches (a B=8 step is ~25 us of
+    GPU work).  Not in the reference; it is how a serving loop would call this path.
+
+    The kernels take sequence lengths from the device-side ``offsets`` and derive their grid from
+    the slot-table CAPACITY, so one captured graph serves every step whose total context fits
+    ``max_tokens``: write the step's q/k/v, slot table (first ``offsets[-1]`` entries) and offsets
+    into the static tensors (``q``, ``k``, ``v``, ``cache_indices``, ``offsets``) — or into their
+    pinned host mirrors (``host_q`` ...) followed by :meth:`upload`, one copy for all five — call
+    :meth:`replay`, read ``out``.  The KV pools are captured by address.
+    """
+
+    def __init__(self, K_cache, V_cache, batch: int, num_heads: int, max_tokens: int, *, dtype=None,
+                 scale: Optional[float] = None, chunk: Optional[int] = None, k_scale=None, v_scale=None):
+        dev = K_cache.device
+        dim = K_cache.size(1)
+        dtype = dtype or (K_cache.dtype if K_cache.dtype in _DT else torch.float16)
+        self.H, self.max_tokens = num_heads, max_tokens
+        # one device arena (and one pinned host mirror) for all per-step inputs, so that a step
+        # needs a single host->device copy: [q | k | v | cache_indices | offsets]
+        es = torch.empty(0, dtype=dtype).element_size()
+        sizes = [batch * dim * es] * 3 + [max_tokens * 4, batch * 4]
+        starts = [0]
+        for n in sizes:
+            starts.append((starts[-1] + n + 255) // 256 * 256)
+        self.arena = torch.zeros(starts[-1], dtype=torch.uint8, device=dev)
+        self.host_arena = torch.zeros(starts[-1], dtype=torch.uint8).pin_memory()
+
+        def views(buf):
+            qkv = [buf[starts[i]:starts[i] + sizes[i]].view(dtype).view(batch, dim) for i in range(3)]
+            ci = buf[starts[3]:starts[3] + sizes[3]].view(torch.int32)
+            off = buf[starts[4]:starts[4] + sizes[4]].view(torch.int32)
+            return (*qkv, ci, off)
+        self.q, self.k, self.v, self.cache_indices, self.offsets = views(self.arena)
+        self.host_q, self.host_k, self.host_v, self.host_cache_indices, self.host_offsets = views(self.host_arena)
+        self._ci_start = starts[3]
+        self.out = torch.zeros(batch, dim, dtype=dtype, device=dev)
+        D = dim // num_heads
+        self.chunk = chunk or pick_chunk(batch, num_heads, D, max_tokens, dev)
+        self.workspace = torch.empty(decode_workspace_bytes(batch, num_heads, D, max_tokens, self.chunk),
+                                     dtype=torch.uint8, device=dev)
+        self._kw = dict(scale=scale, return_sp=False, chunk=self.chunk, k_scale=k_scale, v_scale=v_scale,
+                        workspace=self.workspace, out=self.out)
+        self._pools = (K_cache, V_cache)
+
+        def call():
+            paged_kv_attention_forward(self.q, self.k, self.v, K_cache, V_cache, self.cache_indices, self.offsets,
+                                       num_heads, **self._kw)
+
+        with torch.cuda.device(dev):
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):           # warm-up outside capture (module load, attribute set-up)
+                call()
+            torch.cuda.current_stream().wait_stream(side)
+            self.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph):
+                call()
+
+    def upload(self, n_tokens: Optional[int] = None) -> None:
+        """Copy the pinned host mirror (``host_q`` ... ``host_offsets``) to the device arena in one
+        transfer; with ``n_tokens`` the unused tail of the slot table is skipped (offsets, which sit
+        after it, then go in a second small copy)."""
+        if n_tokens is None or n_tokens >= self.max_tokens:
+            self.arena.copy_(self.host_arena, non_blocking=True)
+        else:
+            end = self._ci_start + 4 * n_tokens
+            self.arena[:end].copy_(self.host_arena[:end], non_blocking=True)
+            self.offsets.copy_(self.host_offsets, non_blocking=True)
+
+    def replay(self) -> torch.Tensor:
+        self.graph.replay()
+        return self.out
+
+
 def paged_decode_partial(Q, K_cache, V_cache, cache_indices, offsets, num_heads: int, *,
                          scale: Optional[float] = None, chunk: Optional[int] = None, k_scale=None, v_scale=None,
                          workspace: Optional[torch.Tensor] = None) -> torch.Tensor:

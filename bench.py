@@ -356,6 +356,21 @@ class SmallDecode(LargeDecode):
                     f"{self.units_per_step_rank() / 1e6:.0f} MB touched cyclically (> 126 MB L2)")
         return c
 
+    def e2e_setup(self):
+        # the serving-loop form: one CUDA-graph launch per step, inputs copied into its static tensors
+        h2d, d2h = super().e2e_setup()
+        g = self.graph = self.A.PagedDecodeGraph(self.pools[0][0], self.pools[0][1], self.Bn, self.H, self.T)
+        # the step's inputs live in the graph's pinned host mirror (that is where a caller builds them)
+        g.host_q.copy_(self.h_in[0]); g.host_k.copy_(self.h_in[1]); g.host_v.copy_(self.h_in[2])
+        g.host_cache_indices[: self.T].copy_(self.h_in[3]); g.host_offsets.copy_(self.h_in[4])
+        return h2d, d2h
+
+    def e2e_step(self):
+        g = self.graph
+        g.upload()                                   # one host->device copy of q, k, v, slot table, offsets
+        self.h_out.copy_(g.replay(), non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
     def cpu_baseline(self):
         return None, None
 

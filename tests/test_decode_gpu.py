@@ -177,3 +177,24 @@ def test_single_query_reference_matrix(batch_size, context_size, dim, num_heads,
     S2, P2, O2 = lm_ops.single_query_attention(*_gpu(Q, K, V, Kc, Vc), num_heads)
     assert torch.allclose(O1.float(), O2.cpu().float(), atol=1e-2)     # the reference's tolerance
     assert (O1.float() - O2.cpu().float()).abs().max() <= (2e-3 if dtype == torch.float16 else 1e-5)
+
+
+def test_decode_graph_replays_with_changing_lengths():
+    """One captured graph, two steps with different context lengths and slot tables."""
+    import attention_impl_b200 as A
+    B, H, D, cap = 8, 32, 128, 8192
+    g = torch.Generator().manual_seed(41)
+    Kc, Vc = (torch.randn(16384, H * D, generator=g).half().cuda() for _ in range(2))
+    graph = A.PagedDecodeGraph(Kc, Vc, B, H, cap)
+    for seed, (lo, hi) in ((1, (128, 1024)), (2, (1, 300))):
+        lens = uniform_lens(B, lo, hi, seed=seed)
+        Q, K, V, _, _, ci, off = decode_inputs(B, H, D, lens, 16384, torch.float16, seed=seed)
+        graph.q.copy_(Q); graph.k.copy_(K); graph.v.copy_(V)
+        graph.cache_indices[: ci.numel()].copy_(ci)
+        graph.offsets.copy_(off)
+        O = graph.replay().clone()
+        _, _, O_ref = A.paged_kv_attention_forward(Q.cuda(), K.cuda(), V.cuda(), Kc, Vc, ci.cuda(), off.cuda(), H,
+                                                   return_sp=False)
+        assert (O.float() - O_ref.float()).abs().max() < 1e-3
+        _, _, O32 = orc.paged_decode(Q, K, V, Kc.cpu(), Vc.cpu(), ci, off, H, compute_dtype=torch.float32)
+        assert (O.cpu().float() - O32.float()).abs().max() <= TOL16
