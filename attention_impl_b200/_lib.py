@@ -24,6 +24,8 @@ PROTOTYPES = {
     "attn_b200_strerror": (C.c_char_p, [_i32]),
     "attn_b200_abi_version": (_i32, []),
     "attn_b200_rope_inplace": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _i64, _i32, _vp, _vp]),
+    "attn_b200_rope_write_kv": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _i64,
+                                       _i64, _i32, _i32, _vp, _vp, _vp, _vp]),
     "attn_b200_paged_decode": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp, _vp, _i64,
                                       _i32, _i32, _i32, _i64, _i64, _i32, _i32, _f32, _vp, _vp, _i32, _i32,
                                       _i32, _vp, _vp]),

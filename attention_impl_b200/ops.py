@@ -83,6 +83,32 @@ def rotary_embedding_inplace(Q, K, positions, cos, sin, head_dim: int, *, check_
         raise RuntimeError("rotary_embedding_inplace: a position is outside [0, cos.size(0))")
 
 
+def rope_and_cache_write(Q, K, V, positions, cos, sin, slots, K_cache, V_cache, head_dim: int, *,
+                         k_scale=None, v_scale=None, err_flag: Optional[torch.Tensor] = None) -> None:
+    """Rotate Q and K in place (as :func:`rotary_embedding_inplace`) and append the rotated K and V
+    of every token to the KV pools at ``slots`` (int32 ``[N]``).  With ``k_scale``/``v_scale`` (float32
+    ``[Hk]``) the pools are ``float8_e4m3fn`` and receive ``x / scale`` rounded to nearest.  This is the
+    step the reference leaves to its caller before ``paged_kv_attention_forward``."""
+    for t, n in ((Q, "Q"), (K, "K"), (V, "V"), (cos, "cos"), (sin, "sin"), (K_cache, "K_cache"), (V_cache, "V_cache")):
+        _check_input(t, n)
+    _int32(positions, "positions")
+    _int32(slots, "slots")
+    dt = _dtype_code(Q, "Q")
+    if any(t.dtype != Q.dtype for t in (K, V, cos, sin)):
+        raise RuntimeError("K, V, cos and sin must have Q's dtype")
+    kvd = _kv_code(K_cache, Q)
+    n = Q.size(0)
+    hk = K.size(1) // head_dim
+    if V.shape != K.shape or K_cache.size(1) != K.size(1) or V_cache.shape != K_cache.shape:
+        raise RuntimeError("V must match K, and the pools must be [slots, Hk*head_dim]")
+    with torch.cuda.device(Q.device):
+        check(lib.attn_b200_rope_write_kv(Q.data_ptr(), K.data_ptr(), V.data_ptr(), positions.data_ptr(),
+                                          cos.data_ptr(), sin.data_ptr(), slots.data_ptr(), K_cache.data_ptr(),
+                                          V_cache.data_ptr(), n, Q.size(1) // head_dim, hk, head_dim, cos.size(1),
+                                          cos.size(0), K_cache.size(0), dt, kvd, _ptr(k_scale), _ptr(v_scale),
+                                          _ptr(err_flag), _stream()), "rope_and_cache_write")
+
+
 # ----------------------------------------------------------------------------------------------
 # paged decode
 # ----------------------------------------------------------------------------------------------

@@ -73,6 +73,22 @@ ATTN_B200_API int attn_b200_rope_inplace(void* q, void* k, const int32_t* positi
                            int64_t n_tokens, int n_heads_q, int n_heads_k, int head_dim, int rot_half,
                            int64_t max_pos, int dtype, int32_t* err_flag, void* stream);
 
+/* Rotary embedding fused with the KV-cache append.  No counterpart in the reference: its decode
+ * operator receives the current token's k, v as arguments (paged_attention_kernel.cu:137-146,
+ * 179-185) and leaves writing them into the pools to the caller; this is that step.
+ *   q [n_tokens, n_heads_q*head_dim], k, v [n_tokens, n_heads_k*head_dim]  (dtype F16/BF16)
+ *   slots int32 [n_tokens]: pool row of each token;  k_cache, v_cache [n_slots, n_heads_k*head_dim]
+ *   in `dtype`, or E4M3 with k_scale, v_scale float [n_heads_k] (stored value = rn_e4m3(x / scale)).
+ * q and k are rotated in place exactly as attn_b200_rope_inplace does; rotated k and v are stored
+ * at their slot.  rot_half and head_dim must be multiples of 8.  Out-of-range slots/positions set
+ * err_flag bits and skip the store. */
+ATTN_B200_API int attn_b200_rope_write_kv(void* q, void* k, const void* v, const int32_t* positions,
+                                          const void* cos, const void* sin, const int32_t* slots, void* k_cache,
+                                          void* v_cache, int64_t n_tokens, int n_heads_q, int n_heads_k,
+                                          int head_dim, int rot_half, int64_t max_pos, int64_t n_slots, int dtype,
+                                          int kv_dtype, const float* k_scale, const float* v_scale,
+                                          int32_t* err_flag, void* stream);
+
 /* ------------------------------------------------------------------------------------------
  * KV-paged single-query decode (block_size = 1 slot table).
  * Replaces paged_kv_attention_forward (paged_attention_kernel.cu:237-294, kernel :100-187) and,
