@@ -113,14 +113,20 @@ template <> struct RowChunk<__nv_fp8_e4m3, 16> {
     }
 };
 
-template <typename QT, typename KVT, int D>
+// MH = false: the 32/LPR row groups of a warp take different TOKENS of one head.
+// MH = true:  they take adjacent HEADS of one token, so a warp-wide load is one contiguous 512-byte
+//             piece of a token's row and a CTA of 8 warps streams 4 KB per token; each group then
+//             keeps its own softmax state and nothing is merged across groups.
+template <typename QT, typename KVT, int D, bool MH>
 __global__ void __launch_bounds__(256)
 paged_decode_fast_kernel(const DecodeParams p) {
     constexpr int EPL = 16 / (int)sizeof(KVT);   // elements per lane (one 16-byte slice)
     constexpr int LPR = D / EPL;                 // lanes per row
     constexpr int TPI = 32 / LPR;                // rows per warp-wide load
-    constexpr int U = (TPI * 8 <= 32) ? 8 : 32 / TPI;  // loads in flight per lane and tensor
-    constexpr int TILE = TPI * U;                // tokens per iteration (<= 32)
+    constexpr int U = MH ? 8 : ((TPI * 8 <= 32) ? 8 : 32 / TPI);  // loads in flight per lane and tensor
+    constexpr int TSTEP = MH ? 1 : TPI;          // tokens per warp-wide load
+    constexpr int TILE = TSTEP * U;              // tokens per iteration (<= 32)
+    constexpr int HPW = MH ? TPI : 1;            // heads per warp
     static_assert(LPR >= 1 && LPR <= 32 && TILE <= 32, "unsupported head_dim");
 
     __shared__ int32_t s_off[kMaxStagedB];
@@ -128,11 +134,13 @@ paged_decode_fast_kernel(const DecodeParams p) {
 
     const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t u = blockIdx.x / p.head_groups;
-    const int h = (blockIdx.x % p.head_groups) * warps + warp;
-    Unit un;
-    if (!resolve_unit(u, p.B, p.chunk, sb, un) || h >= p.H) return;
-
     const int sub = lane % LPR, grp = lane / LPR;
+    const int h_raw = ((blockIdx.x % p.head_groups) * warps + warp) * HPW + (MH ? grp : 0);
+    Unit un;
+    if (!resolve_unit(u, p.B, p.chunk, sb, un) || h_raw - (MH ? grp : 0) >= p.H) return;
+    const bool h_ok = h_raw < p.H;               // MH: trailing groups of the last warp may have no head
+    const int h = h_ok ? h_raw : p.H - 1;
+    const int tsel = MH ? 0 : grp;               // which token of a warp-wide load this lane reads
     const int64_t row_bytes = (int64_t)p.H * D * sizeof(KVT);
     const char* kbase = (const char*)p.k_cache + ((int64_t)h * D + sub * EPL) * sizeof(KVT);
     const char* vbase = (const char*)p.v_cache + ((int64_t)h * D + sub * EPL) * sizeof(KVT);
@@ -178,7 +186,7 @@ paged_decode_fast_kernel(const DecodeParams p) {
         int sl[U];
 #pragma unroll
         for (int j = 0; j < U; ++j) {
-            sl[j] = __shfl_sync(0xffffffffu, my_slot, j * TPI + grp);
+            sl[j] = __shfl_sync(0xffffffffu, my_slot, j * TSTEP + tsel);
             if (sl[j] >= 0) {
                 kr[j] = ldg_stream128(kbase + (int64_t)sl[j] * row_bytes);
             } else {
@@ -227,13 +235,16 @@ paged_decode_fast_kernel(const DecodeParams p) {
 #pragma unroll
                 for (int j = 0; j < U; ++j)
                     if (sl[j] >= 0)
-                        p.S[((int64_t)un.b * p.H + h) * p.sp_stride + (t0 + j * TPI + grp - un.seq_beg)] =
-                            (double)(s[j] * kLn2);
+                        if (h_ok)
+                            p.S[((int64_t)un.b * p.H + h) * p.sp_stride + (t0 + j * TSTEP + tsel - un.seq_beg)] =
+                                (double)(s[j] * kLn2);
             }
         }
-        // maximum over the TPI row groups of the warp
+        // maximum over the row groups of the warp (they share one head unless MH)
+        if constexpr (!MH) {
 #pragma unroll
-        for (int x = LPR; x < 32; x <<= 1) tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, x));
+            for (int x = LPR; x < 32; x <<= 1) tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, x));
+        }
         const float m_new = fmaxf(m, tmax);
         if (m_new > -INFINITY) {  // at least one valid row so far
             const float alpha = fast_exp2(m - m_new);
@@ -279,15 +290,17 @@ paged_decode_fast_kernel(const DecodeParams p) {
             m = m_new;
         }
     }
-    // fold the TPI row groups
+    // fold the row groups (same head, different tokens)
+    if constexpr (!MH) {
 #pragma unroll
-    for (int x = LPR; x < 32; x <<= 1) {
-        l += __shfl_xor_sync(0xffffffffu, l, x);
+        for (int x = LPR; x < 32; x <<= 1) {
+            l += __shfl_xor_sync(0xffffffffu, l, x);
 #pragma unroll
-        for (int i = 0; i < EPL; ++i) o[i] += __shfl_xor_sync(0xffffffffu, o[i], x);
+            for (int i = 0; i < EPL; ++i) o[i] += __shfl_xor_sync(0xffffffffu, o[i], x);
+        }
     }
     float* row = p.part + ((int64_t)u * p.H + h) * (D + 2);
-    if (grp == 0) {
+    if (MH ? h_ok : grp == 0) {
         const float vs = p.v_scale ? p.v_scale[h] : 1.f;
         float2* dst = reinterpret_cast<float2*>(row + sub * EPL);
 #pragma unroll
@@ -488,18 +501,21 @@ lse_combine_kernel(const CombineParams p) {
 // ---------------------------------------------------------------------------------------------
 static inline int64_t max_units(int B, int64_t n_tokens, int chunk) { return n_tokens / chunk + B + 1; }
 
-template <typename QT, typename KVT>
+template <typename QT, typename KVT, bool MH>
 static int launch_fast(const DecodeParams& p, int warps, int64_t n_units, cudaStream_t st) {
     const int64_t blocks = n_units * p.head_groups;
     if (blocks > 0x7fffffffLL) return ATTN_B200_ETOOLARGE;
     switch (p.D) {
-        case 64: paged_decode_fast_kernel<QT, KVT, 64><<<(unsigned)blocks, warps * 32, 0, st>>>(p); break;
-        case 128: paged_decode_fast_kernel<QT, KVT, 128><<<(unsigned)blocks, warps * 32, 0, st>>>(p); break;
-        case 256: paged_decode_fast_kernel<QT, KVT, 256><<<(unsigned)blocks, warps * 32, 0, st>>>(p); break;
+        case 64: paged_decode_fast_kernel<QT, KVT, 64, MH><<<(unsigned)blocks, warps * 32, 0, st>>>(p); break;
+        case 128: paged_decode_fast_kernel<QT, KVT, 128, MH><<<(unsigned)blocks, warps * 32, 0, st>>>(p); break;
+        case 256: paged_decode_fast_kernel<QT, KVT, 256, MH><<<(unsigned)blocks, warps * 32, 0, st>>>(p); break;
         default: return ATTN_B200_ESHAPE;
     }
     return (int)cudaGetLastError();
 }
+
+// rows per warp-wide load = heads per warp in the multi-head mapping
+static int heads_per_warp(int D, int kv_bytes) { return 32 / (D * kv_bytes / 16); }
 
 template <typename QT, typename KVT>
 static int launch_generic(const DecodeParams& p, int64_t n_units, cudaStream_t st) {
@@ -522,14 +538,20 @@ static bool fast_ok(const DecodeParams& p, int q_dtype, int kv_dtype) {
 static int run_stage1(DecodeParams& p, int q_dtype, int kv_dtype, cudaStream_t st) {
     const int64_t n_units = max_units(p.B, p.n_tokens, p.chunk);
     if (fast_ok(p, q_dtype, kv_dtype)) {
+        if (kv_dtype == ATTN_B200_E4M3) {
+            // e4m3 rows are short (D bytes): give each row group of a warp its own head so that a
+            // warp-wide load is one contiguous 512-byte piece of a token
+            const int hpw = heads_per_warp(p.D, 1);
+            int warps = (p.H + hpw - 1) / hpw;
+            if (warps > 8) warps = 8;
+            p.head_groups = (p.H + warps * hpw - 1) / (warps * hpw);
+            return q_dtype == ATTN_B200_F16 ? launch_fast<__half, __nv_fp8_e4m3, true>(p, warps, n_units, st)
+                                            : launch_fast<__nv_bfloat16, __nv_fp8_e4m3, true>(p, warps, n_units, st);
+        }
         const int warps = p.H >= 8 ? 8 : p.H;
         p.head_groups = (p.H + warps - 1) / warps;
-        if (q_dtype == ATTN_B200_F16) {
-            return kv_dtype == ATTN_B200_E4M3 ? launch_fast<__half, __nv_fp8_e4m3>(p, warps, n_units, st)
-                                              : launch_fast<__half, __half>(p, warps, n_units, st);
-        }
-        return kv_dtype == ATTN_B200_E4M3 ? launch_fast<__nv_bfloat16, __nv_fp8_e4m3>(p, warps, n_units, st)
-                                          : launch_fast<__nv_bfloat16, __nv_bfloat16>(p, warps, n_units, st);
+        return q_dtype == ATTN_B200_F16 ? launch_fast<__half, __half, false>(p, warps, n_units, st)
+                                        : launch_fast<__nv_bfloat16, __nv_bfloat16, false>(p, warps, n_units, st);
     }
     p.head_groups = p.H;
     if (kv_dtype == ATTN_B200_E4M3) {
