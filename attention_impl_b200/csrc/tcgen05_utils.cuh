@@ -49,6 +49,29 @@ __device__ __forceinline__ bool mbar_wait(void* bar, uint32_t parity, volatile i
     return true;
 }
 
+// Same contract, but polls with the non-suspending test_wait: for the single MMA-issuing thread,
+// which has nothing else to do and whose reaction time is on the critical path.
+__device__ __forceinline__ bool mbar_wait_spin(void* bar, uint32_t parity, volatile int* cta_abort, int32_t* err_flag) {
+    const uint32_t addr = smem_u32(bar);
+    long long t0 = 0;
+    for (int spins = 0;; ++spins) {
+        uint32_t ok;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
+        if (ok) return true;
+        if ((spins & 255) == 255) {
+            if (*cta_abort) return false;
+            if (t0 == 0) t0 = clock64();
+            else if (clock64() - t0 > WAIT_CYCLES) {
+                *cta_abort = 1;
+                atomicExch(&g_abort, 1);
+                if (err_flag) atomicOr(err_flag, ATTN_B200_FLAG_TIMEOUT);
+                return false;
+            }
+        }
+    }
+}
+
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, void* bar) {
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
@@ -124,6 +147,22 @@ __device__ __forceinline__ uint32_t ex2_f16x2(uint32_t x) {
     return y;
 }
 
+// Packed fp32 pairs (one instruction for two lanes' worth of fp32 FMA / ADD on sm_100).
+__device__ __forceinline__ void fma2(float& d0, float& d1, float a0, float a1, float b0, float b1, float c0, float c1) {
+    asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmov.b64 rc, {%6, %7};\n\t"
+        "fma.rn.f32x2 rd, ra, rb, rc;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+        : "=f"(d0), "=f"(d1) : "f"(a0), "f"(a1), "f"(b0), "f"(b1), "f"(c0), "f"(c1));
+}
+__device__ __forceinline__ void add2(float& d0, float& d1, float a0, float a1, float b0, float b1) {
+    asm("{\n\t.reg .b64 ra, rb, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+        "add.rn.f32x2 rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+        : "=f"(d0), "=f"(d1) : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
 // Shared-memory matrix descriptor, 128-byte swizzle, sm_100 version field.
 __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
     return (uint64_t)((addr >> 4) & 0x3FFF) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16) |
