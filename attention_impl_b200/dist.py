@@ -85,3 +85,63 @@ def kv_split_decode(Q, K, V, K_cache_local, V_cache_local, local_indices, local_
                                     scale=scale, chunk=chunk, k_scale=k_scale, v_scale=v_scale)
     parts = gather_partials(part, group)
     return ops.lse_combine(parts, Q, K, V, num_heads=num_heads, scale=scale)
+
+
+class KvSplitExchange:
+    """KV-split decode whose partial rows travel by plain stores into the peers' memory (NVLink)
+    instead of an NCCL all-gather.
+
+    Set-up (collective over ``group``): a symmetric buffer ``[2, G, B, H, D+2]`` fp32 (two halves used
+    on alternate steps, so a rank that is one step ahead never overwrites rows a slower peer is
+    still combining) and ``G`` arrival counters per rank, mapped into every process with
+    ``torch.distributed._symmetric_memory``.  Per step: local partial rows (two kernels), one push
+    kernel (stores into every rank's slot ``[parity, my_rank]`` + one system-scope atomic per CTA on
+    that rank's counter for me), one wait kernel (bounded; raises ``FLAG_TIMEOUT`` in ``err_flag``),
+    then the usual LSE combine over the gathered rows.  No host synchronisation, no NCCL call.
+    """
+
+    def __init__(self, batch: int, num_heads: int, head_dim: int, device, group=None):
+        import ctypes
+        import torch.distributed._symmetric_memory as symm
+        from . import _lib
+        self._lib, self._ct = _lib, ctypes
+        self.group = group if group is not None else dist.group.WORLD
+        self.G, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        self.B, self.H, self.D = batch, num_heads, head_dim
+        G = self.G
+        self.row_elems = batch * num_heads * (head_dim + 2)
+        self.row_bytes = self.row_elems * 4
+        if self.row_bytes % 16:
+            raise ValueError("B*H*(D+2)*4 must be a multiple of 16 bytes")
+        self.parts = symm.empty((2, G, batch, num_heads, head_dim + 2), dtype=torch.float32, device=device)
+        self.flags = symm.empty((32,), dtype=torch.int32, device=device)
+        self.parts.zero_()
+        self.flags.zero_()
+        torch.cuda.synchronize(device)
+        self._h_parts = symm.rendezvous(self.parts, self.group)
+        self._h_flags = symm.rendezvous(self.flags, self.group)
+        dist.barrier(self.group)
+        part_ptrs, flag_ptrs = list(self._h_parts.buffer_ptrs), list(self._h_flags.buffer_ptrs)
+        PtrArr = ctypes.c_void_p * G
+        self._dst = []
+        for parity in range(2):     # my slot [parity, rank] in every rank's buffer
+            self._dst.append(PtrArr(*[part_ptrs[g] + (parity * G + self.rank) * self.row_bytes for g in range(G)]))
+        self._flag = PtrArr(*[flag_ptrs[g] + 4 * self.rank for g in range(G)])
+        self.ctas_per_push = _lib.lib.attn_b200_peer_push_ctas(self.row_bytes)
+        self.step = 0
+        self.err_flag = torch.zeros(1, dtype=torch.int32, device=device)
+
+    def decode(self, Q, K, V, K_cache_local, V_cache_local, local_indices, local_offsets, *, scale=None,
+               k_scale=None, v_scale=None, chunk=None) -> torch.Tensor:
+        from . import ops
+        lib, check = self._lib.lib, self._lib.check
+        part = ops.paged_decode_partial(Q, K_cache_local, V_cache_local, local_indices, local_offsets, self.H,
+                                        scale=scale, chunk=chunk, k_scale=k_scale, v_scale=v_scale)
+        parity = self.step & 1
+        self.step += 1
+        stream = torch.cuda.current_stream().cuda_stream
+        check(lib.attn_b200_peer_push(part.data_ptr(), self.row_bytes, self._dst[parity], self._flag, self.G, stream),
+              "peer_push")
+        check(lib.attn_b200_wait_flags(self.flags.data_ptr(), self.G, self.step * self.ctas_per_push,
+                                       self.err_flag.data_ptr(), stream), "wait_flags")
+        return ops.lse_combine(self.parts[parity], Q, K, V, num_heads=self.H, scale=scale)

@@ -553,8 +553,25 @@ class Fp8Split(Workload):
         self.Q, self.K, self.V = (torch.randn(self.Bn, dim, device=dev, dtype=torch.float16, generator=g)
                                   for _ in range(3))
         self.chunk = A.ops.pick_chunk(self.Bn, self.H, self.D, self.T, dev)
+        self.xchg = None
+        if self.args.exchange == "peer" and G > 1:
+            self.xchg = adist.KvSplitExchange(self.Bn, self.H, self.D, dev)
+            ref = adist.kv_split_decode(self.Q, self.K, self.V, self.Kc, self.Vc, self.ci, self.off, self.H,
+                                        k_scale=self.ks, v_scale=self.vs, chunk=self.chunk)
+            for _ in range(3):      # both buffer halves and the counter arithmetic
+                got = self.xchg.decode(self.Q, self.K, self.V, self.Kc, self.Vc, self.ci, self.off,
+                                       k_scale=self.ks, v_scale=self.vs, chunk=self.chunk)
+            torch.cuda.synchronize()
+            if int(self.xchg.err_flag.item()) != 0 or not torch.equal(got, ref):
+                raise SystemExit(f"rank {r}: peer exchange differs from the NCCL path "
+                                 f"(flag {int(self.xchg.err_flag.item())}, "
+                                 f"max diff {(got.float() - ref.float()).abs().max().item()})")
 
     def step(self):
+        if self.xchg is not None:
+            self.out = self.xchg.decode(self.Q, self.K, self.V, self.Kc, self.Vc, self.ci, self.off,
+                                        k_scale=self.ks, v_scale=self.vs, chunk=self.chunk)
+            return
         self.out = self.adist.kv_split_decode(self.Q, self.K, self.V, self.Kc, self.Vc, self.ci, self.off, self.H,
                                               k_scale=self.ks, v_scale=self.vs, chunk=self.chunk)
 
@@ -587,8 +604,9 @@ class Fp8Split(Workload):
         return {"workload": "long_context_fp8_kv_paged_decode", "batch": self.Bn, "heads": self.H,
                 "head_dim": self.D, "ctx_range": [self.LO, self.HI], "context_tokens": self.T_all,
                 "kv_bytes_total": 2.0 * self.T_all * self.H * self.D, "kv_bytes_per_gpu": per,
-                "sharding": f"each sequence's KV split {self.world} ways; all-gather of [B,H,D+2] fp32 partials "
-                            f"over NCCL + LSE combine", "chunk": self.chunk,
+                "sharding": f"each sequence's KV split {self.world} ways; [B,H,D+2] fp32 partials exchanged by "
+                            + ("peer stores over NVLink" if self.xchg is not None else "NCCL all-gather")
+                            + " + LSE combine", "chunk": self.chunk,
                 "l2": f"inputs larger than L2 ({per / 1e9:.1f} GB of KV per GPU per step)"}
 
     def reference_run(self, steps, warmup):
@@ -745,6 +763,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="large_decode", choices=sorted(WORKLOADS))
     ap.add_argument("--batch", type=int, default=None, help="override the batch size (profiling a small case)")
+    ap.add_argument("--exchange", default="nccl", choices=["nccl", "peer"],
+                    help="fp8_split: how the partial rows travel between ranks")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (profiling runs)")
     args = ap.parse_args()
     W = WORKLOADS[args.workload]

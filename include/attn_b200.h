@@ -144,6 +144,22 @@ ATTN_B200_API int attn_b200_lse_combine(const float* parts, int n_parts, const v
                           const void* v_new, void* out, int B, int H, int D, float scale, int q_dtype,
                           void* stream);
 
+/* Peer-memory exchange for the KV-split path (no counterpart in the reference).  Replaces the NCCL
+ * all-gather of the partial rows: attn_b200_peer_push stores `n_bytes` (multiple of 16) from `src`
+ * into peer_dst[g] for every g < n_peers (host arrays of device pointers that are valid in this
+ * process: peer allocations mapped by CUDA IPC / symmetric memory, or local memory for g = self),
+ * then adds 1 per CTA to each *peer_flag[g] (int32, system-scope atomic).  One push adds
+ * attn_b200_peer_push_ctas(n_bytes) to each counter; counters are never reset.
+ * attn_b200_wait_flags enqueues a kernel that waits until every flags[i] (i < n_flags <= 32, local
+ * memory written by the peers) has reached `expected`; the wait is bounded (about one second) and
+ * sets ATTN_B200_FLAG_TIMEOUT in *err_flag when it gives up.  Work enqueued after it on the same
+ * stream sees the pushed data. */
+ATTN_B200_API int attn_b200_peer_push_ctas(size_t n_bytes);
+ATTN_B200_API int attn_b200_peer_push(const void* src, size_t n_bytes, void* const* peer_dst,
+                                      int32_t* const* peer_flag, int n_peers, void* stream);
+ATTN_B200_API int attn_b200_wait_flags(const int32_t* flags, int n_flags, int32_t expected, int32_t* err_flag,
+                                       void* stream);
+
 /* Paged decode that allocates nothing and needs no scratch from the caller.
  * (No counterpart in the reference: its launcher allocates S, P and O itself with torch::zeros.)
  * For hosts that cannot call cudaMalloc — an engine that gave all free HBM to its own KV pool, or
