@@ -198,3 +198,29 @@ def test_decode_graph_replays_with_changing_lengths():
         assert (O.float() - O_ref.float()).abs().max() < 1e-3
         _, _, O32 = orc.paged_decode(Q, K, V, Kc.cpu(), Vc.cpu(), ci, off, H, compute_dtype=torch.float32)
         assert (O.cpu().float() - O32.float()).abs().max() <= TOL16
+
+
+def test_paged_decode_pool_beyond_int32_element_offsets():
+    """600 000 slots x 4096 elements: element offsets exceed 2^31 (the reference's int index
+    overflows past 524 288 slots, paged_attention_kernel.cu:132).  Only the rows that are used are
+    non-zero; the oracle runs on the gathered rows."""
+    import lm_ops
+    B, H, D = 3, 32, 128
+    n_slots = 600_000
+    lens = [700, 1, 333]
+    g = torch.Generator().manual_seed(123)
+    T = sum(lens)
+    Kc = torch.zeros(n_slots, H * D, dtype=torch.float16, device="cuda")
+    Vc = torch.zeros(n_slots, H * D, dtype=torch.float16, device="cuda")
+    # all slots in the upper part of the pool, beyond the 32-bit element range
+    ci = (torch.randperm(60_000, generator=g)[:T] + 530_000).int()
+    rows_k = torch.randn(T, H * D, generator=g).half()
+    rows_v = torch.randn(T, H * D, generator=g).half()
+    Kc[ci.long().cuda()] = rows_k.cuda()
+    Vc[ci.long().cuda()] = rows_v.cuda()
+    Q, K, V = (torch.randn(B, H * D, generator=g).half() for _ in range(3))
+    off = torch.tensor(lens).cumsum(0).int()
+    _, _, O = lm_ops.paged_kv_attention_forward(Q.cuda(), K.cuda(), V.cuda(), Kc, Vc, ci.cuda(), off.cuda(), H,
+                                                return_sp=False)
+    _, _, O32 = orc.paged_decode(Q, K, V, rows_k, rows_v, torch.arange(T).int(), off, H, compute_dtype=torch.float32)
+    assert (O.cpu().float() - O32.float()).abs().max() <= TOL16

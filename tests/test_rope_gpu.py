@@ -87,3 +87,31 @@ def test_rope_empty_input():
     q = torch.empty(0, 64, dtype=torch.float16, device="cuda")
     lm_ops.rotary_embedding_inplace(q, q.clone(), torch.empty(0, dtype=torch.int32, device="cuda"),
                                     cos.cuda(), sin.cuda(), 64)
+
+
+@pytest.mark.parametrize("num_heads,head_dim,rot_dim", [(1, 16, 16), (1, 32, 32), (1, 64, 64), (1, 16, 8), (4, 32, 4), (8, 64, 32)])
+def test_rope_reference_suite_shapes(num_heads, head_dim, rot_dim):
+    """The reference's own cases (tests/test_rotary_embedding.py:79-142): 4 tokens, positions
+    arange(4), a 32-position table, std 0.1, atol 1e-3 against the torch module that rounds the angles
+    to fp16 before cos/sin (its own table, :27-30) -- and, unlike the reference, k is checked as well."""
+    import lm_ops
+    gen = torch.Generator().manual_seed(head_dim + rot_dim)
+    n, max_pos = 4, 32
+    q = (torch.randn(n, num_heads * head_dim, generator=gen) * 0.1).half()
+    k = (torch.randn(n, num_heads * head_dim, generator=gen) * 0.1).half()
+    pos = torch.arange(n).int()
+    cos, sin = orc.rope_tables(rot_dim, max_pos)                       # the kernel-side table (:65-71)
+    inv_freq = 1.0 / (10000 ** (torch.arange(0, rot_dim, 2).float() / rot_dim))
+    emb = torch.cat((torch.outer(torch.arange(max_pos).float(), inv_freq),) * 2, dim=-1).half()
+    ref_cos, ref_sin = emb.cos().half(), emb.sin().half()                # the torch module's table (:27-30)
+
+    def ref(x):
+        xh = x.reshape(n, num_heads, head_dim)
+        xr = xh[..., :rot_dim]
+        c, s_ = ref_cos[pos.long()].unsqueeze(1), ref_sin[pos.long()].unsqueeze(1)
+        xr = xr * c + orc.rotate_half(xr) * s_
+        return torch.cat((xr, xh[..., rot_dim:]), dim=-1).reshape(n, -1)
+    qd, kd = q.cuda(), k.cuda()
+    lm_ops.rotary_embedding_inplace(qd, kd, pos.cuda(), cos.cuda(), sin.cuda(), head_dim)
+    assert torch.allclose(ref(q).float(), qd.cpu().float(), atol=1e-3)
+    assert torch.allclose(ref(k).float(), kd.cpu().float(), atol=1e-3)
