@@ -625,6 +625,18 @@ prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     }
 }
 
+// Rows of the packed buffer past the last sequence belong to no query tile; zero them so that the
+// output never carries uninitialised memory (the reference returns zeros there, zeros_like(V)).
+__global__ void zero_tail_kernel(void* out, const int32_t* offsets, int B, int64_t n_tokens, int64_t row_bytes) {
+    int64_t beg = offsets[B - 1];
+    if (beg < 0) beg = 0;
+    if (beg >= n_tokens) return;
+    const int64_t n_vec = (n_tokens - beg) * row_bytes / 16;
+    uint4* base = reinterpret_cast<uint4*>((char*)out + beg * row_bytes);
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_vec; i += (int64_t)gridDim.x * blockDim.x)
+        base[i] = make_uint4(0, 0, 0, 0);
+}
+
 // ---------------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------------
@@ -694,6 +706,7 @@ int prefill_tc_launch(const void* q, const void* k, const void* v, const int32_t
     cudaError_t e = cudaGetSymbolAddress(&abort_addr, g_abort);
     if (e != cudaSuccess) return (int)e;
     if ((e = cudaMemsetAsync(abort_addr, 0, sizeof(int), st)) != cudaSuccess) return (int)e;
+    zero_tail_kernel<<<64, 256, 0, st>>>(out, offsets, B, n_tokens, (int64_t)H * HD * (out_f32 ? 4 : 2));
     if (!use_v1) {
         if (dtype == ATTN_B200_BF16) {
             if ((e = cudaFuncSetAttribute(prefill_tc2_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) != cudaSuccess)

@@ -383,8 +383,7 @@ def paged_attention_forward(Q, K, V, offsets, num_heads: int, *, scale: Optional
 
     ``offsets`` int32 ``[B]`` are inclusive cumulative lengths.  Returns ``[S, P, O]``; S, P are
     ``[B, H, maxL, maxL]`` in the input dtype as in the reference unless ``return_sp=False``
-    (empty placeholders; required for the tensor-core path and for any large input; O is then not
-    zero-filled first, so rows beyond ``offsets[-1]``, which belong to no sequence, are undefined).
+    (empty placeholders; required for the tensor-core path and for any large input).
     ``out_dtype=torch.float32`` makes the tensor-core path store fp32 output.  ``err_flag`` (int32
     device scalar) receives ATTN_B200_FLAG_* bits (bad offsets, an in-kernel wait that ran out).
     """
@@ -407,10 +406,11 @@ def paged_attention_forward(Q, K, V, offsets, num_heads: int, *, scale: Optional
             lens = torch.diff(offsets, prepend=offsets.new_zeros(1))
             max_seqlen = int(lens.max().item()) if B > 0 else 0
         out_f32 = out_dtype == torch.float32 and Q.dtype != torch.float32
-        # the reference zero-fills O (zeros_like, :209); every row that belongs to a sequence is
-        # overwritten, so the fast form skips the 1 GB memset and leaves rows past offsets[-1] undefined
-        O = (torch.zeros if return_sp else torch.empty)(Q.shape, dtype=torch.float32 if out_f32 else Q.dtype,
-                                                        device=dev)
+        # the reference zero-fills O (zeros_like, :209).  The tensor-core path writes every row itself
+        # (rows past offsets[-1] are zeroed by a small kernel), so it skips the up-front memset
+        tc_path = (not return_sp and not force_generic and D == 128 and Q.dtype in (torch.float16, torch.bfloat16))
+        O = (torch.empty if tc_path else torch.zeros)(Q.shape, dtype=torch.float32 if out_f32 else Q.dtype,
+                                                      device=dev)
         if return_sp:
             S = torch.zeros(B, H, max_seqlen, max_seqlen, dtype=Q.dtype, device=dev)
             P = torch.zeros_like(S)

@@ -86,3 +86,13 @@ def test_prefill_tc_rows_sum_property_at_workload_lengths():
     begs = [0] + off.tolist()[:-1]
     for b in begs:
         assert torch.allclose(O2[b], V2[b].float(), atol=4e-3 * 4)
+
+
+def test_prefill_tc_rows_past_the_last_sequence_are_zero():
+    import lm_ops
+    lens = [200, 100]
+    Q, K, V, off = prefill_inputs(lens + [77], 2, 128, torch.bfloat16, seed=2)     # 77 tokens belong to no sequence
+    off = off[:2]
+    _, _, O = lm_ops.packed_attention(Q.cuda(), K.cuda(), V.cuda(), off.cuda(), 2, return_sp=False)
+    assert O[300:].abs().sum().item() == 0
+    assert O[:300].abs().sum().item() > 0
