@@ -46,7 +46,14 @@ struct DecodeParams {
     const float* v_scale;
     int32_t* err_flag;
     int head_groups;
+    int Hkv;          // KV heads; H (query heads) = Hkv * G
+    int G;            // query heads per KV head
+    int block_size;   // tokens per KV block; 1 = `slots` is a per-token table
+    int max_blocks;   // block_size > 1: `slots` is a [B, max_blocks] block table
 };
+
+// Pool row of token `t` (absolute index in the token stream) of the unit's sequence, or -1.
+__device__ __forceinline__ int token_slot(const DecodeParams& p, const struct Unit& un, int64_t t);
 
 struct Unit {
     int b;
@@ -65,6 +72,26 @@ struct SeqBounds {
         return v < 0 ? 0 : (v > n_tokens ? n_tokens : v);
     }
 };
+
+__device__ __forceinline__ int token_slot(const DecodeParams& p, const Unit& un, int64_t t) {
+    int64_t v;
+    if (!p.slots) {
+        v = t;
+    } else if (p.block_size <= 1) {
+        v = p.slots[t];
+    } else {
+        const int64_t rel = t - un.seq_beg;
+        const int64_t blk = rel / p.block_size;
+        if (blk >= p.max_blocks) v = -1;
+        else {
+            const int64_t id = p.slots[(int64_t)un.b * p.max_blocks + blk];
+            v = id < 0 ? -1 : id * p.block_size + (rel - blk * p.block_size);
+        }
+    }
+    if (v >= 0 && v < p.n_slots) return (int)v;
+    if (p.err_flag) atomicOr(p.err_flag, ATTN_B200_FLAG_BAD_SLOT);
+    return -1;
+}
 
 __device__ __forceinline__ bool resolve_unit(int64_t u, int B, int chunk, const SeqBounds& sb, Unit& out) {
     int lo = 0, hi = B - 1;
@@ -113,13 +140,17 @@ template <> struct RowChunk<__nv_fp8_e4m3, 16> {
     }
 };
 
-// MH = false: the 32/LPR row groups of a warp take different TOKENS of one head.
-// MH = true:  they take adjacent HEADS of one token, so a warp-wide load is one contiguous 512-byte
-//             piece of a token's row and a CTA of 8 warps streams 4 KB per token; each group then
-//             keeps its own softmax state and nothing is merged across groups.
+// Multi-head attention with a per-token slot table (the reference's case and the benchmarked one).
+// The general kernel below (grouped-query heads, block tables) computes the same thing with G = 1,
+// block_size = 1, but measured 7 % slower on this path (6.40 vs 6.91 TB/s on a 15 GB fp16 case), so
+// the specialised form is kept.
+// MH = true (the form that is launched): the 32/LPR row groups of a warp take adjacent HEADS of one
+// token, so a warp-wide load is one contiguous 512-byte piece of a token's row and a CTA of 8 warps
+// streams 4 KB per token; each group keeps its own softmax state and nothing is merged across
+// groups.  MH = false: the groups take different TOKENS of one head (kept for A/B measurements).
 template <typename QT, typename KVT, int D, bool MH>
 __global__ void __launch_bounds__(256)
-paged_decode_fast_kernel(const DecodeParams p) {
+paged_decode_mha_kernel(const DecodeParams p) {
     constexpr int EPL = 16 / (int)sizeof(KVT);   // elements per lane (one 16-byte slice)
     constexpr int LPR = D / EPL;                 // lanes per row
     constexpr int TPI = 32 / LPR;                // rows per warp-wide load
@@ -309,6 +340,199 @@ paged_decode_fast_kernel(const DecodeParams p) {
     }
 }
 
+// The 32/LPR row groups of a warp take ADJACENT KV HEADS of one token, so a warp-wide load is one
+// contiguous 512-byte piece of the token's row and a CTA of 8 warps streams 4 KB per token; each
+// group keeps its own softmax state.  G > 1 (grouped-query attention): the G query heads that share
+// a KV head are all served from the one copy of the row held in registers.
+template <typename QT, typename KVT, int D, int G>
+__global__ void __launch_bounds__(256, G == 1 ? 2 : 1)     // G = 1: 128 registers, two CTAs (16 warps) per SM
+paged_decode_fast_kernel(const DecodeParams p) {
+    constexpr int EPL = 16 / (int)sizeof(KVT);   // elements per lane (one 16-byte slice)
+    constexpr int LPR = D / EPL;                 // lanes per row
+    constexpr int HPW = 32 / LPR;                // KV heads per warp
+    constexpr int U = G >= 8 ? 2 : (G >= 4 ? 4 : 8);   // row loads in flight per lane and tensor = tokens per tile
+    constexpr bool kFp8 = sizeof(KVT) == 1;
+    static_assert(LPR >= 1 && LPR <= 32, "unsupported head_dim");
+
+    __shared__ int32_t s_off[kMaxStagedB];
+    SeqBounds sb{stage_offsets(p, s_off), p.uniform_ctx, p.n_tokens};
+
+    const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t u = blockIdx.x / p.head_groups;
+    const int sub = lane % LPR, grp = lane / LPR;
+    const int hk_raw = ((blockIdx.x % p.head_groups) * warps + warp) * HPW + grp;
+    Unit un;
+    if (!resolve_unit(u, p.B, p.chunk, sb, un) || hk_raw - grp >= p.Hkv) return;
+    const bool h_ok = hk_raw < p.Hkv;            // trailing groups of the last warp may have no head
+    const int hk = h_ok ? hk_raw : p.Hkv - 1;
+    const int64_t row_bytes = (int64_t)p.Hkv * D * sizeof(KVT);
+    const char* kbase = (const char*)p.k_cache + ((int64_t)hk * D + sub * EPL) * sizeof(KVT);
+    const char* vbase = (const char*)p.v_cache + ((int64_t)hk * D + sub * EPL) * sizeof(KVT);
+
+    // 16-bit KV: q in fp32, pre-multiplied by scale*log2(e).  e4m3 KV: q stays unscaled in packed
+    // fp16 (products with the 4-significant-bit e4m3 values are formed by HFMA2 and the 16
+    // products of a lane are summed in fp16 before widening: the error, ~1e-3 of a score's
+    // standard deviation, is far below the e4m3 quantisation it rides on); the combined factor
+    // scale*log2(e)*k_scale[hk] is applied to the reduced fp32 score.
+    float qf[G][kFp8 ? 1 : EPL];
+    __half2 q2[G][kFp8 ? EPL / 2 : 1];
+    const float qs = p.scale_log2 * (p.k_scale ? p.k_scale[hk] : 1.f);
+#pragma unroll
+    for (int gi = 0; gi < G; ++gi) {
+        const QT* qp = (const QT*)p.q + ((int64_t)un.b * p.H + hk * G + gi) * D + sub * EPL;
+        if constexpr (kFp8) {
+#pragma unroll
+            for (int i = 0; i < EPL / 2; ++i)
+                q2[gi][i] = __floats2half2_rn(to_f32<QT>(qp[2 * i]), to_f32<QT>(qp[2 * i + 1]));
+        } else {
+#pragma unroll
+            for (int i = 0; i < EPL; ++i) qf[gi][i] = to_f32<QT>(qp[i]) * qs;
+        }
+    }
+    float m[G], l[G], o[G][EPL];
+#pragma unroll
+    for (int gi = 0; gi < G; ++gi) {
+        m[gi] = -INFINITY;
+        l[gi] = 0.f;
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) o[gi][i] = 0.f;
+    }
+
+    auto load_slot = [&](int64_t t0) -> int {
+        const int64_t t = t0 + lane;
+        return (lane < U && t < un.tend) ? token_slot(p, un, t) : -1;
+    };
+
+    int next_slot = load_slot(un.tbeg);
+    for (int64_t t0 = un.tbeg; t0 < un.tend; t0 += U) {
+        const int my_slot = next_slot;
+        uint4 kr[U], vr[U];
+        int sl[U];
+#pragma unroll
+        for (int j = 0; j < U; ++j) {
+            sl[j] = __shfl_sync(0xffffffffu, my_slot, j);
+            kr[j] = sl[j] >= 0 ? ldg_stream128(kbase + (int64_t)sl[j] * row_bytes) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int j = 0; j < U; ++j)
+            vr[j] = sl[j] >= 0 ? ldg_stream128(vbase + (int64_t)sl[j] * row_bytes) : make_uint4(0, 0, 0, 0);
+        if (t0 + U < un.tend) next_slot = load_slot(t0 + U);
+
+        float s[G][U];
+#pragma unroll
+        for (int j = 0; j < U; ++j) {
+            if constexpr (kFp8) {
+                const uint32_t w4[4] = {kr[j].x, kr[j].y, kr[j].z, kr[j].w};
+#pragma unroll
+                for (int gi = 0; gi < G; ++gi) {
+                    __half2 a0 = __float2half2_rn(0.f), a1 = a0;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        __half2 lo, hi;
+                        e4m3x4_to_half2x2(w4[i], lo, hi);    // 2 conversions: cheaper to redo per query head than to hold
+                        a0 = __hfma2(q2[gi][2 * i], lo, a0);
+                        a1 = __hfma2(q2[gi][2 * i + 1], hi, a1);
+                    }
+                    const float2 f = __half22float2(__hadd2(a0, a1));
+                    const float acc = group_sum<LPR>(f.x + f.y) * qs;
+                    s[gi][j] = sl[j] >= 0 ? acc : -INFINITY;
+                }
+            } else {
+                float kf[EPL];
+                RowChunk<KVT, EPL>::unpack(kr[j], kf);
+#pragma unroll
+                for (int gi = 0; gi < G; ++gi) {
+                    float acc = 0.f;
+#pragma unroll
+                    for (int i = 0; i < EPL; ++i) acc = fmaf(qf[gi][i], kf[i], acc);
+                    acc = group_sum<LPR>(acc);
+                    s[gi][j] = sl[j] >= 0 ? acc : -INFINITY;
+                }
+            }
+        }
+        if (p.S && sub == 0 && h_ok) {
+#pragma unroll
+            for (int gi = 0; gi < G; ++gi)
+#pragma unroll
+                for (int j = 0; j < U; ++j)
+                    if (sl[j] >= 0)
+                        p.S[((int64_t)un.b * p.H + hk * G + gi) * p.sp_stride + (t0 + j - un.seq_beg)] =
+                            (double)(s[gi][j] * kLn2);
+        }
+        float msub[G];      // maximum to subtract (0 while a head has seen no valid row: exp2(-inf - 0) = 0)
+#pragma unroll
+        for (int gi = 0; gi < G; ++gi) {
+            float tmax = s[gi][0];
+#pragma unroll
+            for (int j = 1; j < U; ++j) tmax = fmaxf(tmax, s[gi][j]);
+            const float m_new = fmaxf(m[gi], tmax);
+            const bool live = m_new > -INFINITY;
+            const float alpha = live ? fast_exp2(m[gi] - m_new) : 1.f;
+            l[gi] *= alpha;
+#pragma unroll
+            for (int i = 0; i < EPL; ++i) o[gi][i] *= alpha;
+            m[gi] = m_new;
+            msub[gi] = live ? m_new : 0.f;
+        }
+        if constexpr (kFp8) {
+            // p*v summed over the tile's rows in fp16x2 (p <= 1, |v| <= 448), widened once per tile
+            __half2 oa[G][EPL / 2];
+#pragma unroll
+            for (int gi = 0; gi < G; ++gi)
+#pragma unroll
+                for (int i = 0; i < EPL / 2; ++i) oa[gi][i] = __float2half2_rn(0.f);
+#pragma unroll
+            for (int j = 0; j < U; ++j) {
+                const uint32_t w4[4] = {vr[j].x, vr[j].y, vr[j].z, vr[j].w};
+#pragma unroll
+                for (int gi = 0; gi < G; ++gi) {
+                    const float pj = fast_exp2(s[gi][j] - msub[gi]);
+                    l[gi] += pj;
+                    const __half2 p2 = __float2half2_rn(pj);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        __half2 lo, hi;
+                        e4m3x4_to_half2x2(w4[i], lo, hi);
+                        oa[gi][2 * i] = __hfma2(p2, lo, oa[gi][2 * i]);
+                        oa[gi][2 * i + 1] = __hfma2(p2, hi, oa[gi][2 * i + 1]);
+                    }
+                }
+            }
+#pragma unroll
+            for (int gi = 0; gi < G; ++gi)
+#pragma unroll
+                for (int i = 0; i < EPL / 2; ++i) {
+                    const float2 f = __half22float2(oa[gi][i]);
+                    o[gi][2 * i] += f.x;
+                    o[gi][2 * i + 1] += f.y;
+                }
+        } else {
+#pragma unroll
+            for (int j = 0; j < U; ++j) {
+                float vf[EPL];
+                RowChunk<KVT, EPL>::unpack(vr[j], vf);
+#pragma unroll
+                for (int gi = 0; gi < G; ++gi) {
+                    const float pj = fast_exp2(s[gi][j] - msub[gi]);
+                    l[gi] += pj;
+#pragma unroll
+                    for (int i = 0; i < EPL; ++i) o[gi][i] = fmaf(pj, vf[i], o[gi][i]);
+                }
+            }
+        }
+    }
+    if (!h_ok) return;
+    const float vs = p.v_scale ? p.v_scale[hk] : 1.f;
+#pragma unroll
+    for (int gi = 0; gi < G; ++gi) {
+        float* row = p.part + ((int64_t)u * p.H + hk * G + gi) * (D + 2);
+        float2* dst = reinterpret_cast<float2*>(row + sub * EPL);
+#pragma unroll
+        for (int i = 0; i < EPL / 2; ++i) dst[i] = make_float2(o[gi][2 * i] * vs, o[gi][2 * i + 1] * vs);
+        if (sub == 0) *reinterpret_cast<float2*>(row + D) = make_float2(m[gi], l[gi]);
+    }
+}
+
 // ---------------------------------------------------------------------------------------------
 // generic kernel: any dtype / head_dim, one CTA per (unit, head)
 // ---------------------------------------------------------------------------------------------
@@ -331,23 +555,17 @@ paged_decode_generic_kernel(const DecodeParams p) {
     const int D = p.D;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
-    const float qs = p.scale_log2 * (p.k_scale ? p.k_scale[h] : 1.f);
+    const int hk = h / p.G;                               // KV head of this query head
+    const float qs = p.scale_log2 * (p.k_scale ? p.k_scale[hk] : 1.f);
     for (int d = tid; d < D; d += blockDim.x)
         s_q[d] = to_f32<QT>(((const QT*)p.q)[((int64_t)un.b * p.H + h) * D + d]) * qs;
-    for (int i = tid; i < n; i += blockDim.x) {
-        const int64_t t = un.tbeg + i;
-        const int64_t v = p.slots ? (int64_t)p.slots[t] : t;
-        int s = -1;
-        if (v >= 0 && v < p.n_slots) s = (int)v;
-        else if (p.err_flag) atomicOr(p.err_flag, ATTN_B200_FLAG_BAD_SLOT);
-        s_slot[i] = s;
-    }
+    for (int i = tid; i < n; i += blockDim.x) s_slot[i] = token_slot(p, un, un.tbeg + i);
     __syncthreads();
     float lmax = -INFINITY;
     for (int i = tid; i < n; i += blockDim.x) {
         float acc = -INFINITY;
         if (s_slot[i] >= 0) {
-            const KVT* kr = (const KVT*)p.k_cache + ((int64_t)s_slot[i] * p.H + h) * D;
+            const KVT* kr = (const KVT*)p.k_cache + ((int64_t)s_slot[i] * p.Hkv + hk) * D;
             acc = 0.f;
             for (int d = 0; d < D; ++d) acc = fmaf(s_q[d], to_f32<KVT>(kr[d]), acc);
             if (p.S)
@@ -372,12 +590,12 @@ paged_decode_generic_kernel(const DecodeParams p) {
     __syncthreads();
     const float l = s_red[0] + s_red[1] + s_red[2] + s_red[3];
     float* row = p.part + ((int64_t)u * p.H + h) * (D + 2);
-    const float vs = p.v_scale ? p.v_scale[h] : 1.f;
+    const float vs = p.v_scale ? p.v_scale[hk] : 1.f;
     for (int d = tid; d < D; d += blockDim.x) {
         float acc = 0.f;
         for (int i = 0; i < n; ++i)
             if (s_slot[i] >= 0)
-                acc = fmaf(s_sc[i], to_f32<KVT>(((const KVT*)p.v_cache)[((int64_t)s_slot[i] * p.H + h) * D + d]), acc);
+                acc = fmaf(s_sc[i], to_f32<KVT>(((const KVT*)p.v_cache)[((int64_t)s_slot[i] * p.Hkv + hk) * D + d]), acc);
         row[d] = acc * vs;
     }
     if (tid == 0) { row[D] = m; row[D + 1] = l; }
@@ -401,6 +619,7 @@ struct CombineParams {
     int64_t uniform_ctx, n_tokens;
     int B, H, D, chunk;
     float scale_log2;
+    int G;                // query heads per KV head: k_new / v_new are [B, (H/G)*D]
 };
 
 template <typename QT>
@@ -434,7 +653,7 @@ lse_combine_kernel(const CombineParams p) {
     float s_new = -INFINITY;
     if (p.k_new) {
         const QT* qp = (const QT*)p.q + ((int64_t)b * p.H + h) * D;
-        const QT* kp = (const QT*)p.k_new + ((int64_t)b * p.H + h) * D;
+        const QT* kp = (const QT*)p.k_new + ((int64_t)b * (p.H / p.G) + h / p.G) * D;
         float acc = 0.f;
         for (int d = lane; d < D; d += 32) acc = fmaf(to_f32<QT>(qp[d]), to_f32<QT>(kp[d]), acc);
         s_new = group_sum<32>(acc) * p.scale_log2;
@@ -474,7 +693,7 @@ lse_combine_kernel(const CombineParams p) {
             const int d = dbase + k * 32 + lane;
             if (d >= D) continue;
             float a = acc[k];
-            if (p.k_new) a = fmaf(w_new, to_f32<QT>(((const QT*)p.v_new)[((int64_t)b * p.H + h) * D + d]), a);
+            if (p.k_new) a = fmaf(w_new, to_f32<QT>(((const QT*)p.v_new)[((int64_t)b * (p.H / p.G) + h / p.G) * D + d]), a);
             if (p.out) ((QT*)p.out)[((int64_t)b * p.H + h) * D + d] = from_f32<QT>(a * inv);
             else p.part_out[((int64_t)b * p.H + h) * RS + d] = a;
         }
@@ -501,20 +720,44 @@ lse_combine_kernel(const CombineParams p) {
 // ---------------------------------------------------------------------------------------------
 static inline int64_t max_units(int B, int64_t n_tokens, int chunk) { return n_tokens / chunk + B + 1; }
 
-template <typename QT, typename KVT, bool MH>
-static int launch_fast(const DecodeParams& p, int warps, int64_t n_units, cudaStream_t st) {
+template <typename QT, typename KVT>
+static int launch_mha(const DecodeParams& p, int warps, int64_t n_units, cudaStream_t st) {
     const int64_t blocks = n_units * p.head_groups;
     if (blocks > 0x7fffffffLL) return ATTN_B200_ETOOLARGE;
     switch (p.D) {
-        case 64: paged_decode_fast_kernel<QT, KVT, 64, MH><<<(unsigned)blocks, warps * 32, 0, st>>>(p); break;
-        case 128: paged_decode_fast_kernel<QT, KVT, 128, MH><<<(unsigned)blocks, warps * 32, 0, st>>>(p); break;
-        case 256: paged_decode_fast_kernel<QT, KVT, 256, MH><<<(unsigned)blocks, warps * 32, 0, st>>>(p); break;
+        case 64: paged_decode_mha_kernel<QT, KVT, 64, true><<<(unsigned)blocks, warps * 32, 0, st>>>(p); break;
+        case 128: paged_decode_mha_kernel<QT, KVT, 128, true><<<(unsigned)blocks, warps * 32, 0, st>>>(p); break;
+        case 256: paged_decode_mha_kernel<QT, KVT, 256, true><<<(unsigned)blocks, warps * 32, 0, st>>>(p); break;
         default: return ATTN_B200_ESHAPE;
     }
     return (int)cudaGetLastError();
 }
 
-// rows per warp-wide load = heads per warp in the multi-head mapping
+template <typename QT, typename KVT, int G>
+static int launch_fast_g(const DecodeParams& p, int warps, int64_t n_units, cudaStream_t st) {
+    const int64_t blocks = n_units * p.head_groups;
+    if (blocks > 0x7fffffffLL) return ATTN_B200_ETOOLARGE;
+    switch (p.D) {
+        case 64: paged_decode_fast_kernel<QT, KVT, 64, G><<<(unsigned)blocks, warps * 32, 0, st>>>(p); break;
+        case 128: paged_decode_fast_kernel<QT, KVT, 128, G><<<(unsigned)blocks, warps * 32, 0, st>>>(p); break;
+        case 256: paged_decode_fast_kernel<QT, KVT, 256, G><<<(unsigned)blocks, warps * 32, 0, st>>>(p); break;
+        default: return ATTN_B200_ESHAPE;
+    }
+    return (int)cudaGetLastError();
+}
+
+template <typename QT, typename KVT>
+static int launch_fast(const DecodeParams& p, int warps, int64_t n_units, cudaStream_t st) {
+    switch (p.G) {
+        case 1: return launch_fast_g<QT, KVT, 1>(p, warps, n_units, st);
+        case 2: return launch_fast_g<QT, KVT, 2>(p, warps, n_units, st);
+        case 4: return launch_fast_g<QT, KVT, 4>(p, warps, n_units, st);
+        case 8: return launch_fast_g<QT, KVT, 8>(p, warps, n_units, st);
+        default: return ATTN_B200_ESHAPE;
+    }
+}
+
+// rows per warp-wide load = KV heads per warp
 static int heads_per_warp(int D, int kv_bytes) { return 32 / (D * kv_bytes / 16); }
 
 template <typename QT, typename KVT>
@@ -529,6 +772,7 @@ static int launch_generic(const DecodeParams& p, int64_t n_units, cudaStream_t s
 
 static bool fast_ok(const DecodeParams& p, int q_dtype, int kv_dtype) {
     if (!(p.D == 64 || p.D == 128 || p.D == 256)) return false;
+    if (!(p.G == 1 || p.G == 2 || p.G == 4 || p.G == 8)) return false;
     if (!(q_dtype == ATTN_B200_F16 || q_dtype == ATTN_B200_BF16)) return false;
     if (!(kv_dtype == q_dtype || kv_dtype == ATTN_B200_E4M3)) return false;
     if (((uintptr_t)p.k_cache | (uintptr_t)p.v_cache) % 16) return false;
@@ -538,19 +782,26 @@ static bool fast_ok(const DecodeParams& p, int q_dtype, int kv_dtype) {
 static int run_stage1(DecodeParams& p, int q_dtype, int kv_dtype, cudaStream_t st) {
     const int64_t n_units = max_units(p.B, p.n_tokens, p.chunk);
     if (fast_ok(p, q_dtype, kv_dtype)) {
-        // every row group of a warp takes its own head, so that a warp-wide load is one contiguous
+        // every row group of a warp takes its own KV head, so that a warp-wide load is one contiguous
         // 512-byte piece of a token's row (2 heads of 16-bit rows, 4 heads of e4m3 rows at head_dim
-        // 128) and a CTA of 8 warps streams 4 KB per token.  Measured against the tokens-per-warp
+        // 128) and a CTA of 8 warps streams 4 KB per token.  Measured against a tokens-per-warp
         // mapping on B200: +17 % for e4m3 KV (0.89 -> 1.04 of the copy peak), +3 % for fp16 KV.
         const int hpw = heads_per_warp(p.D, kv_dtype == ATTN_B200_E4M3 ? 1 : 2);
-        int warps = (p.H + hpw - 1) / hpw;
+        int warps = (p.Hkv + hpw - 1) / hpw;
         if (warps > 8) warps = 8;
-        p.head_groups = (p.H + warps * hpw - 1) / (warps * hpw);
+        p.head_groups = (p.Hkv + warps * hpw - 1) / (warps * hpw);
+        if (p.G == 1 && p.block_size <= 1) {      // multi-head, per-token slot table: specialised kernel
+            if (kv_dtype == ATTN_B200_E4M3)
+                return q_dtype == ATTN_B200_F16 ? launch_mha<__half, __nv_fp8_e4m3>(p, warps, n_units, st)
+                                                : launch_mha<__nv_bfloat16, __nv_fp8_e4m3>(p, warps, n_units, st);
+            return q_dtype == ATTN_B200_F16 ? launch_mha<__half, __half>(p, warps, n_units, st)
+                                            : launch_mha<__nv_bfloat16, __nv_bfloat16>(p, warps, n_units, st);
+        }
         if (kv_dtype == ATTN_B200_E4M3)
-            return q_dtype == ATTN_B200_F16 ? launch_fast<__half, __nv_fp8_e4m3, true>(p, warps, n_units, st)
-                                            : launch_fast<__nv_bfloat16, __nv_fp8_e4m3, true>(p, warps, n_units, st);
-        return q_dtype == ATTN_B200_F16 ? launch_fast<__half, __half, true>(p, warps, n_units, st)
-                                        : launch_fast<__nv_bfloat16, __nv_bfloat16, true>(p, warps, n_units, st);
+            return q_dtype == ATTN_B200_F16 ? launch_fast<__half, __nv_fp8_e4m3>(p, warps, n_units, st)
+                                            : launch_fast<__nv_bfloat16, __nv_fp8_e4m3>(p, warps, n_units, st);
+        return q_dtype == ATTN_B200_F16 ? launch_fast<__half, __half>(p, warps, n_units, st)
+                                        : launch_fast<__nv_bfloat16, __nv_bfloat16>(p, warps, n_units, st);
     }
     p.head_groups = p.H;
     if (kv_dtype == ATTN_B200_E4M3) {
@@ -579,9 +830,12 @@ static int run_combine(const CombineParams& c, int q_dtype, cudaStream_t st) {
     return (int)cudaGetLastError();
 }
 
-static int check_common(const void* q, const void* kc, const void* vc, int B, int H, int D, int64_t n_tokens,
-                        int64_t n_slots, int chunk, int kv_dtype, const float* ks, const float* vs) {
+static int check_common(const void* q, const void* kc, const void* vc, int B, int H, int Hkv, int D, int64_t n_tokens,
+                        int64_t n_slots, int block_size, int max_blocks, int chunk, int kv_dtype, const float* ks,
+                        const float* vs) {
     if (!q || !kc || !vc || B <= 0 || H <= 0 || D <= 0 || n_tokens < 0 || n_slots <= 0) return ATTN_B200_EINVAL;
+    if (Hkv <= 0 || H % Hkv) return ATTN_B200_ESHAPE;
+    if (block_size < 1 || (block_size > 1 && max_blocks <= 0)) return ATTN_B200_EINVAL;
     if (chunk < 32 || chunk > 2048 || chunk % 32) return ATTN_B200_ESHAPE;
     if (D > 1024) return ATTN_B200_ESHAPE;
     if (n_tokens > 0x7fffffffLL) return ATTN_B200_ETOOLARGE;
@@ -614,11 +868,12 @@ extern "C" int attn_b200_paged_decode_pick_chunk(int B, int H, int D, int64_t n_
 extern "C" int attn_b200_paged_decode(const void* q, const void* k_new, const void* v_new, const void* k_cache,
                                       const void* v_cache, const int32_t* slots, const int32_t* offsets, void* out,
                                       void* workspace, size_t workspace_bytes, double* S, double* P,
-                                      int64_t sp_stride, int B, int H, int D, int64_t n_tokens, int64_t n_slots,
-                                      int uniform_ctx, int chunk, float scale, const float* k_scale,
-                                      const float* v_scale, int q_dtype, int kv_dtype, int stages,
-                                      int32_t* err_flag, void* stream) {
-    int rc = check_common(q, k_cache, v_cache, B, H, D, n_tokens, n_slots, chunk, kv_dtype, k_scale, v_scale);
+                                      int64_t sp_stride, int B, int H, int n_kv_heads, int D, int64_t n_tokens,
+                                      int64_t n_slots, int uniform_ctx, int block_size, int max_blocks, int chunk,
+                                      float scale, const float* k_scale, const float* v_scale, int q_dtype,
+                                      int kv_dtype, int stages, int32_t* err_flag, void* stream) {
+    int rc = check_common(q, k_cache, v_cache, B, H, n_kv_heads, D, n_tokens, n_slots, block_size, max_blocks, chunk,
+                          kv_dtype, k_scale, v_scale);
     if (rc) return rc;
     if (!out || !workspace || !k_new || !v_new) return ATTN_B200_EINVAL;
     if ((S == nullptr) != (P == nullptr)) return ATTN_B200_EINVAL;
@@ -627,9 +882,11 @@ extern "C" int attn_b200_paged_decode(const void* q, const void* k_new, const vo
         (uintptr_t)workspace % 16)
         return ATTN_B200_EWORKSPACE;
     cudaStream_t st = (cudaStream_t)stream;
+    const int G = H / n_kv_heads;
     DecodeParams p{q, k_cache, v_cache, slots, offsets, (float*)workspace, S, sp_stride, B, H, D, n_tokens, n_slots,
                    uniform_ctx, chunk, scale * kLog2e, kv_dtype == ATTN_B200_E4M3 ? k_scale : nullptr,
-                   kv_dtype == ATTN_B200_E4M3 ? v_scale : nullptr, err_flag, 1};
+                   kv_dtype == ATTN_B200_E4M3 ? v_scale : nullptr, err_flag, 1, n_kv_heads, G, block_size,
+                   max_blocks};
     if (stages < 1 || stages > 3) return ATTN_B200_EINVAL;
     if (stages & 1) {
         rc = run_stage1(p, q_dtype, kv_dtype, st);
@@ -637,40 +894,45 @@ extern "C" int attn_b200_paged_decode(const void* q, const void* k_new, const vo
     }
     if (!(stages & 2)) return 0;
     CombineParams c{(const float*)workspace, 0, q, k_new, v_new, out, nullptr, S, P, sp_stride, offsets,
-                    uniform_ctx, n_tokens, B, H, D, chunk, scale * kLog2e};
+                    uniform_ctx, n_tokens, B, H, D, chunk, scale * kLog2e, G};
     return run_combine(c, q_dtype, st);
 }
 
 extern "C" int attn_b200_paged_decode_partial(const void* q, const void* k_cache, const void* v_cache,
                                               const int32_t* slots, const int32_t* offsets, float* part_out,
-                                              void* workspace, size_t workspace_bytes, int B, int H, int D,
-                                              int64_t n_tokens, int64_t n_slots, int chunk, float scale,
-                                              const float* k_scale, const float* v_scale, int q_dtype,
-                                              int kv_dtype, int32_t* err_flag, void* stream) {
-    int rc = check_common(q, k_cache, v_cache, B, H, D, n_tokens, n_slots, chunk, kv_dtype, k_scale, v_scale);
+                                              void* workspace, size_t workspace_bytes, int B, int H, int n_kv_heads,
+                                              int D, int64_t n_tokens, int64_t n_slots, int block_size,
+                                              int max_blocks, int chunk, float scale, const float* k_scale,
+                                              const float* v_scale, int q_dtype, int kv_dtype, int32_t* err_flag,
+                                              void* stream) {
+    int rc = check_common(q, k_cache, v_cache, B, H, n_kv_heads, D, n_tokens, n_slots, block_size, max_blocks, chunk,
+                          kv_dtype, k_scale, v_scale);
     if (rc) return rc;
     if (!part_out || !workspace || !offsets) return ATTN_B200_EINVAL;
     if (workspace_bytes < attn_b200_paged_decode_workspace_bytes(B, H, D, n_tokens, chunk) ||
         (uintptr_t)workspace % 16)
         return ATTN_B200_EWORKSPACE;
     cudaStream_t st = (cudaStream_t)stream;
+    const int G = H / n_kv_heads;
     DecodeParams p{q, k_cache, v_cache, slots, offsets, (float*)workspace, nullptr, 0, B, H, D, n_tokens, n_slots,
                    0, chunk, scale * kLog2e, kv_dtype == ATTN_B200_E4M3 ? k_scale : nullptr,
-                   kv_dtype == ATTN_B200_E4M3 ? v_scale : nullptr, err_flag, 1};
+                   kv_dtype == ATTN_B200_E4M3 ? v_scale : nullptr, err_flag, 1, n_kv_heads, G, block_size,
+                   max_blocks};
     rc = run_stage1(p, q_dtype, kv_dtype, st);
     if (rc) return rc;
     CombineParams c{(const float*)workspace, 0, q, nullptr, nullptr, nullptr, part_out, nullptr, nullptr, 0,
-                    offsets, 0, n_tokens, B, H, D, chunk, scale * kLog2e};
+                    offsets, 0, n_tokens, B, H, D, chunk, scale * kLog2e, G};
     return run_combine(c, q_dtype, st);
 }
 
 extern "C" int attn_b200_lse_combine(const float* parts, int n_parts, const void* q, const void* k_new,
-                                     const void* v_new, void* out, int B, int H, int D, float scale, int q_dtype,
-                                     void* stream) {
+                                     const void* v_new, void* out, int B, int H, int n_kv_heads, int D, float scale,
+                                     int q_dtype, void* stream) {
     if (!parts || n_parts <= 0 || !out || B <= 0 || H <= 0 || D <= 0) return ATTN_B200_EINVAL;
+    if (n_kv_heads <= 0 || H % n_kv_heads) return ATTN_B200_ESHAPE;
     if ((k_new == nullptr) != (v_new == nullptr)) return ATTN_B200_EINVAL;
     if (k_new && !q) return ATTN_B200_EINVAL;
     CombineParams c{parts, n_parts, q, k_new, v_new, out, nullptr, nullptr, nullptr, 0, nullptr, 0, 0,
-                    B, H, D, 32, scale * kLog2e};
+                    B, H, D, 32, scale * kLog2e, H / n_kv_heads};
     return run_combine(c, q_dtype, (cudaStream_t)stream);
 }

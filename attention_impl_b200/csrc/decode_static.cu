@@ -52,6 +52,7 @@ extern "C" int attn_b200_paged_decode_static_scratch(
     const int rc = scratch_for_current_device(&scratch);
     if (rc) return rc;
     return attn_b200_paged_decode(q, k_new, v_new, k_cache, v_cache, slots, offsets, out, scratch,
-                                  (size_t)ATTN_B200_STATIC_SCRATCH_BYTES, nullptr, nullptr, 0, B, H, D, n_tokens,
-                                  n_slots, 0, chunk, scale, k_scale, v_scale, q_dtype, kv_dtype, 3, err_flag, stream);
+                                  (size_t)ATTN_B200_STATIC_SCRATCH_BYTES, nullptr, nullptr, 0, B, H, /*n_kv_heads=*/H,
+                                  D, n_tokens, n_slots, 0, /*block_size=*/1, /*max_blocks=*/0, chunk, scale, k_scale,
+                                  v_scale, q_dtype, kv_dtype, 3, err_flag, stream);
 }

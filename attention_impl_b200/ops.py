@@ -135,7 +135,8 @@ def paged_kv_attention_forward(Q, K, V, K_cache, V_cache, cache_indices, offsets
                                chunk: Optional[int] = None, k_scale=None, v_scale=None,
                                max_context_len: Optional[int] = None, workspace: Optional[torch.Tensor] = None,
                                out: Optional[torch.Tensor] = None,
-                               err_flag: Optional[torch.Tensor] = None, stages: int = 3) -> List[torch.Tensor]:
+                               err_flag: Optional[torch.Tensor] = None, stages: int = 3,
+                               block_size: int = 1) -> List[torch.Tensor]:
     """KV-paged single-query attention, block_size = 1 (paged_attention_kernel.cu:237-294).
 
     Q, K, V ``[B, H*D]`` (the current token); K_cache, V_cache ``[slots, H*D]``; cache_indices
@@ -148,6 +149,10 @@ def paged_kv_attention_forward(Q, K, V, K_cache, V_cache, cache_indices, offsets
     ``k_scale``/``v_scale`` float32 ``[H]`` select the FP8-e4m3 KV path; ``chunk`` overrides the
     split-KV chunk length; ``workspace``/``out`` let a caller reuse buffers; ``stages`` (1 = partial
     kernel only, 2 = combine only, 3 = both) exists so a benchmark can time the two kernels apart.
+    Grouped-query attention: K, V and the pools may have fewer heads than Q (``Hkv = K_cache.size(1) //
+    D`` must divide ``num_heads``); query head h reads KV head ``h // (num_heads // Hkv)``.
+    ``block_size > 1``: ``cache_indices`` is a block table int32 ``[B, max_blocks]`` and token t of
+    sequence b lives in pool row ``cache_indices[b, t // block_size] * block_size + t % block_size``.
     """
     for t, n in ((Q, "Q"), (K, "K"), (V, "V"), (K_cache, "K_cache"), (V_cache, "V_cache")):
         _check_input(t, n)
@@ -163,9 +168,19 @@ def paged_kv_attention_forward(Q, K, V, K_cache, V_cache, cache_indices, offsets
     H, D = num_heads, dim // num_heads
     if offsets.numel() != B:
         raise RuntimeError("offsets must have one entry per sequence")
-    if K_cache.size(1) != dim or V_cache.shape != K_cache.shape:
-        raise RuntimeError("K_cache/V_cache must be [slots, H*D]")
-    T = cache_indices.numel()
+    if K_cache.size(1) % D or V_cache.shape != K_cache.shape:
+        raise RuntimeError("K_cache/V_cache must be [slots, Hkv*D]")
+    Hkv = K_cache.size(1) // D
+    if H % Hkv or K.size(1) != Hkv * D or V.size(1) != Hkv * D:
+        raise RuntimeError("K, V and the pools must have Hkv*D columns with Hkv dividing num_heads")
+    if block_size > 1:
+        if cache_indices.dim() != 2 or cache_indices.size(0) != B:
+            raise RuntimeError("block_size > 1 needs a block table [B, max_blocks]")
+        max_blocks = cache_indices.size(1)
+        T = B * max_blocks * block_size          # token capacity; the lengths come from offsets
+    else:
+        max_blocks = 0
+        T = cache_indices.numel()
     if scale is None:
         scale = 1.0 / math.sqrt(D)
     if kvd == _lib.E4M3:
@@ -173,12 +188,12 @@ def paged_kv_attention_forward(Q, K, V, K_cache, V_cache, cache_indices, offsets
             raise RuntimeError("FP8 KV needs k_scale and v_scale (float32 [H])")
         for t, n in ((k_scale, "k_scale"), (v_scale, "v_scale")):
             _check_input(t, n)
-            if t.dtype != torch.float32 or t.numel() != H:
-                raise RuntimeError(f"{n} must be float32 [H]")
+            if t.dtype != torch.float32 or t.numel() != Hkv:
+                raise RuntimeError(f"{n} must be float32 [Hkv]")
     dev = Q.device
     with torch.cuda.device(dev):
         if chunk is None:
-            chunk = pick_chunk(B, H, D, T, dev)
+            chunk = pick_chunk(B, Hkv, D, T, dev)
         need = decode_workspace_bytes(B, H, D, T, chunk)
         if workspace is None:
             workspace = torch.empty(need, dtype=torch.uint8, device=dev)
@@ -201,8 +216,8 @@ def paged_kv_attention_forward(Q, K, V, K_cache, V_cache, cache_indices, offsets
             cache_indices.data_ptr(), offsets.data_ptr(), O.data_ptr(), workspace.data_ptr(),
             workspace.numel() * workspace.element_size(),
             S.data_ptr() if return_sp else None, P.data_ptr() if return_sp else None, stride,
-            B, H, D, T, K_cache.size(0), 0, chunk, float(scale), _ptr(k_scale), _ptr(v_scale), qd, kvd, stages,
-            _ptr(err_flag), _stream()), "paged_kv_attention_forward")
+            B, H, Hkv, D, T, K_cache.size(0), 0, block_size, max_blocks, chunk, float(scale), _ptr(k_scale),
+            _ptr(v_scale), qd, kvd, stages, _ptr(err_flag), _stream()), "paged_kv_attention_forward")
     return [S, P, O]
 
 
@@ -296,21 +311,22 @@ def paged_decode_partial(Q, K_cache, V_cache, cache_indices, offsets, num_heads:
     kvd = _kv_code(K_cache, Q)
     B, dim = Q.shape
     H, D = num_heads, dim // num_heads
+    Hkv = K_cache.size(1) // D
     T = cache_indices.numel()
     if scale is None:
         scale = 1.0 / math.sqrt(D)
     dev = Q.device
     with torch.cuda.device(dev):
         if chunk is None:
-            chunk = pick_chunk(B, H, D, T, dev)
+            chunk = pick_chunk(B, Hkv, D, T, dev)
         need = decode_workspace_bytes(B, H, D, T, chunk)
         if workspace is None:
             workspace = torch.empty(need, dtype=torch.uint8, device=dev)
         part = torch.empty(B, H, D + 2, dtype=torch.float32, device=dev)
         check(lib.attn_b200_paged_decode_partial(
             Q.data_ptr(), K_cache.data_ptr(), V_cache.data_ptr(), cache_indices.data_ptr(), offsets.data_ptr(),
-            part.data_ptr(), workspace.data_ptr(), workspace.numel() * workspace.element_size(), B, H, D, T,
-            K_cache.size(0), chunk, float(scale), _ptr(k_scale), _ptr(v_scale), qd, kvd, None, _stream()),
+            part.data_ptr(), workspace.data_ptr(), workspace.numel() * workspace.element_size(), B, H, Hkv, D, T,
+            K_cache.size(0), 1, 0, chunk, float(scale), _ptr(k_scale), _ptr(v_scale), qd, kvd, None, _stream()),
             "paged_decode_partial")
     return part
 
@@ -327,9 +343,10 @@ def lse_combine(parts, Q, K=None, V=None, *, num_heads: int, scale: Optional[flo
     if scale is None:
         scale = 1.0 / math.sqrt(D)
     O = torch.empty_like(Q)
+    Hkv = K.size(1) // D if K is not None else H
     with torch.cuda.device(Q.device):
         check(lib.attn_b200_lse_combine(parts.data_ptr(), n_parts, Q.data_ptr(), _ptr(K), _ptr(V), O.data_ptr(),
-                                        B, H, D, float(scale), _dtype_code(Q, "Q"), _stream()), "lse_combine")
+                                        B, H, Hkv, D, float(scale), _dtype_code(Q, "Q"), _stream()), "lse_combine")
     return O
 
 
@@ -364,8 +381,8 @@ def kv_attention_forward(Q, K, V, K_cache, V_cache, num_heads: int, *, scale: fl
         check(lib.attn_b200_paged_decode(
             Q.data_ptr(), K.data_ptr(), V.data_ptr(), K_cache.data_ptr(), V_cache.data_ptr(), None, None,
             O.data_ptr(), ws.data_ptr(), need, S64.data_ptr() if return_sp else None,
-            P64.data_ptr() if return_sp else None, ctx + 1 if return_sp else 0, B, H, D, T, max(T, 1), ctx, chunk,
-            float(scale), None, None, qd, qd, 3, None, _stream()), "kv_attention_forward")
+            P64.data_ptr() if return_sp else None, ctx + 1 if return_sp else 0, B, H, H, D, T, max(T, 1), ctx, 1, 0,
+            chunk, float(scale), None, None, qd, qd, 3, None, _stream()), "kv_attention_forward")
     if return_sp:
         return [S64.to(Q.dtype), P64.to(Q.dtype), O]
     e = torch.empty(0, dtype=Q.dtype, device=dev)

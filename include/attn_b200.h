@@ -113,13 +113,20 @@ ATTN_B200_API int attn_b200_rope_write_kv(void* q, void* k, const void* v, const
  * no initialisation and holds nothing between calls.
  * `stages`: 3 runs both kernels (the normal call); 1 runs only the partial kernel, 2 only the
  * combine kernel (same arguments) so that a profiler or benchmark can put events between them.
+ * Extensions beyond the reference (which is multi-head, block_size = 1):
+ *   n_kv_heads  KV heads (H % n_kv_heads == 0); k_new, v_new, k_cache, v_cache then have n_kv_heads*D
+ *               columns and query head h reads KV head h / (H / n_kv_heads).  Pass H for MHA.
+ *   block_size  tokens per KV block.  1: `slots` is the per-token table above.  > 1: `slots` is a
+ *               block table int32 [B, max_blocks]; token t of sequence b lives in pool row
+ *               slots[b*max_blocks + t/block_size]*block_size + t%block_size.
  */
 ATTN_B200_API int attn_b200_paged_decode(const void* q, const void* k_new, const void* v_new, const void* k_cache,
                            const void* v_cache, const int32_t* slots, const int32_t* offsets, void* out,
                            void* workspace, size_t workspace_bytes, double* S, double* P, int64_t sp_stride,
-                           int B, int H, int D, int64_t n_tokens, int64_t n_slots, int uniform_ctx, int chunk,
-                           float scale, const float* k_scale, const float* v_scale, int q_dtype, int kv_dtype,
-                           int stages, int32_t* err_flag, void* stream);
+                           int B, int H, int n_kv_heads, int D, int64_t n_tokens, int64_t n_slots,
+                           int uniform_ctx, int block_size, int max_blocks, int chunk, float scale,
+                           const float* k_scale, const float* v_scale, int q_dtype, int kv_dtype, int stages,
+                           int32_t* err_flag, void* stream);
 
 ATTN_B200_API size_t attn_b200_paged_decode_workspace_bytes(int B, int H, int D, int64_t n_tokens, int chunk);
 /* Heuristic chunk length: enough (chunk, head-group) work items to fill `sm_count` SMs. */
@@ -132,17 +139,17 @@ ATTN_B200_API int attn_b200_paged_decode_pick_chunk(int B, int H, int D, int64_t
  * No counterpart in the reference (it has no split-KV). */
 ATTN_B200_API int attn_b200_paged_decode_partial(const void* q, const void* k_cache, const void* v_cache,
                                    const int32_t* slots, const int32_t* offsets, float* part_out,
-                                   void* workspace, size_t workspace_bytes, int B, int H, int D,
-                                   int64_t n_tokens, int64_t n_slots, int chunk, float scale,
-                                   const float* k_scale, const float* v_scale, int q_dtype, int kv_dtype,
-                                   int32_t* err_flag, void* stream);
+                                   void* workspace, size_t workspace_bytes, int B, int H, int n_kv_heads, int D,
+                                   int64_t n_tokens, int64_t n_slots, int block_size, int max_blocks, int chunk,
+                                   float scale, const float* k_scale, const float* v_scale, int q_dtype,
+                                   int kv_dtype, int32_t* err_flag, void* stream);
 
 /* Log-sum-exp combine of n_parts partial sets  parts [n_parts, B, H, D+2]  (layout above) plus
  * the new token (k_new, v_new; may both be NULL to skip it) into out [B, H*D] (q_dtype).
  * No counterpart in the reference. */
 ATTN_B200_API int attn_b200_lse_combine(const float* parts, int n_parts, const void* q, const void* k_new,
-                          const void* v_new, void* out, int B, int H, int D, float scale, int q_dtype,
-                          void* stream);
+                          const void* v_new, void* out, int B, int H, int n_kv_heads, int D, float scale,
+                          int q_dtype, void* stream);
 
 /* Peer-memory exchange for the KV-split path (no counterpart in the reference).  Replaces the NCCL
  * all-gather of the partial rows: attn_b200_peer_push stores `n_bytes` (multiple of 16) from `src`

@@ -60,6 +60,7 @@ def paged_decode(
     num_heads: int,
     scale: Optional[float] = None,
     compute_dtype: Optional[torch.dtype] = None,
+    block_size: int = 1,
 ):
     """Single-query attention over slot-addressed KV rows plus the new token.
 
@@ -73,10 +74,17 @@ def paged_decode(
     Returns ``S, P`` as float64 ``[B, H, max_ctx + 1]`` (new token's entry at
     index ``ctx_b``, zero tail; paged_attention_kernel.cu:261-262) and ``O``
     ``[B, H*D]`` in Q's dtype.
+
+    Two generalisations the reference does not have (it is multi-head with one slot per token):
+    the pools and K, V may carry ``Hkv < H`` heads (query head h uses KV head ``h // (H // Hkv)``),
+    and with ``block_size > 1`` ``cache_indices`` is a block table ``[B, max_blocks]``, token t of
+    sequence b living in row ``table[b, t // block_size] * block_size + t % block_size``.
     """
     B, dim = Q.shape
     H = num_heads
     D = dim // H
+    Hkv = K_cache.shape[1] // D
+    g = H // Hkv
     if scale is None:
         scale = 1.0 / math.sqrt(D)
     cd = compute_dtype or Q.dtype
@@ -88,12 +96,16 @@ def paged_decode(
     idx = cache_indices.long()
     for b in range(B):
         n = ends[b] - begs[b]
-        rows = idx[begs[b]:ends[b]]
+        if block_size > 1:
+            t = torch.arange(n)
+            rows = idx[b, t // block_size] * block_size + t % block_size
+        else:
+            rows = idx[begs[b]:ends[b]]
         q = Q[b].to(cd).reshape(H, D)
-        k_all = torch.cat([K_cache[rows].to(cd).reshape(n, H, D), K[b].to(cd).reshape(1, H, D)], 0)
-        v_all = torch.cat([V_cache[rows].to(cd).reshape(n, H, D), V[b].to(cd).reshape(1, H, D)], 0)
-        k_all = k_all.permute(1, 0, 2)  # [H, n+1, D]
-        v_all = v_all.permute(1, 0, 2)
+        k_all = torch.cat([K_cache[rows].to(cd).reshape(n, Hkv, D), K[b].to(cd).reshape(1, Hkv, D)], 0)
+        v_all = torch.cat([V_cache[rows].to(cd).reshape(n, Hkv, D), V[b].to(cd).reshape(1, Hkv, D)], 0)
+        k_all = k_all.permute(1, 0, 2).repeat_interleave(g, dim=0)  # [H, n+1, D]
+        v_all = v_all.permute(1, 0, 2).repeat_interleave(g, dim=0)
         s = torch.matmul(k_all, q.unsqueeze(-1)).squeeze(-1) * scale  # [H, n+1]
         p = s.softmax(dim=-1)
         o = torch.matmul(p.unsqueeze(1), v_all).squeeze(1)  # [H, D]

@@ -41,8 +41,8 @@ def test_argument_errors_are_reported_without_a_gpu():
     assert lib.attn_b200_rope_inplace(None, None, None, None, None, 4, 1, 1, 16, 8, 32, 0, None, None) == -1
     assert lib.attn_b200_rope_inplace(None, None, None, None, None, 0, 1, 1, 16, 8, 32, 0, None, None) == 0
     assert lib.attn_b200_paged_decode(None, None, None, None, None, None, None, None, None, 0, None, None, 0,
-                                      1, 1, 128, 0, 1, 0, 32, 1.0, None, None, 0, 0, 3, None, None) == -1
-    assert lib.attn_b200_lse_combine(None, 1, None, None, None, None, 1, 1, 128, 1.0, 0, None) == -1
+                                      1, 1, 1, 128, 0, 1, 0, 1, 0, 32, 1.0, None, None, 0, 0, 3, None, None) == -1
+    assert lib.attn_b200_lse_combine(None, 1, None, None, None, None, 1, 1, 1, 128, 1.0, 0, None) == -1
     assert lib.attn_b200_varlen_prefill(None, None, None, None, None, None, None, 1, 1, 1, 1, 128, 1.0, 0, 0, 0,
                                         None, None) == -1
     assert lib.attn_b200_dense_attention(None, None, None, None, None, None, None, 1, 1, 1, 1, 1.0, 1.0, 0,

@@ -224,3 +224,71 @@ def test_paged_decode_pool_beyond_int32_element_offsets():
                                                 return_sp=False)
     _, _, O32 = orc.paged_decode(Q, K, V, rows_k, rows_v, torch.arange(T).int(), off, H, compute_dtype=torch.float32)
     assert (O.cpu().float() - O32.float()).abs().max() <= TOL16
+
+
+def _gqa_inputs(B, Hq, Hkv, D, lens, n_slots, dtype, seed):
+    g = torch.Generator().manual_seed(seed)
+    Q = torch.randn(B, Hq * D, generator=g).to(dtype)
+    K, V = (torch.randn(B, Hkv * D, generator=g).to(dtype) for _ in range(2))
+    Kc, Vc = (torch.randn(n_slots, Hkv * D, generator=g).to(dtype) for _ in range(2))
+    ci = torch.randperm(n_slots, generator=g)[: sum(lens)].int()
+    off = torch.tensor(lens).cumsum(0).int()
+    return Q, K, V, Kc, Vc, ci, off
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("Hq,Hkv,D", [(8, 4, 128), (32, 8, 128), (16, 2, 128), (8, 2, 64), (6, 2, 128), (12, 4, 48)])
+def test_paged_decode_grouped_query(dtype, Hq, Hkv, D):
+    """Fewer KV heads than query heads (not in the reference): group sizes 2, 4, 8 take the fast kernel,
+    3 and head_dim 48 the generic one."""
+    lens = [0, 1, 40, 129, 700]
+    inp = _gqa_inputs(len(lens), Hq, Hkv, D, lens, 2048, dtype, seed=Hq * 10 + Hkv)
+    S, P, O = _decode(*inp, Hq)
+    S32, P32, O32 = orc.paged_decode(*inp, Hq, compute_dtype=torch.float32)
+    tol = TOL16 if dtype == torch.float16 else 1.6e-2
+    assert (O.float() - O32.float()).abs().max() <= tol
+    assert (P - P32).abs().max() < 2e-4
+
+
+def test_paged_decode_grouped_query_fp8():
+    B, Hq, Hkv, D = 4, 32, 8, 128
+    lens = uniform_lens(B, 100, 1500, seed=6)
+    Q, K, V, Kc, Vc, ci, off = _gqa_inputs(B, Hq, Hkv, D, lens, 8192, torch.float16, seed=7)
+    K8, ks = orc.quantize_e4m3_per_head(Kc, Hkv)
+    V8, vs = orc.quantize_e4m3_per_head(Vc, Hkv)
+    Kd, Vd = orc.dequantize_e4m3_per_head(K8, ks, Hkv), orc.dequantize_e4m3_per_head(V8, vs, Hkv)
+    _, _, Oref = orc.paged_decode(Q.float(), K.float(), V.float(), Kd, Vd, ci, off, Hq)
+    import lm_ops
+    _, _, O = lm_ops.paged_kv_attention_forward(Q.cuda(), K.cuda(), V.cuda(), K8.cuda(), V8.cuda(), ci.cuda(),
+                                                off.cuda(), Hq, return_sp=False, k_scale=ks.cuda(), v_scale=vs.cuda())
+    assert (O.cpu().float() - Oref).norm() / Oref.norm() <= 2e-2
+
+
+@pytest.mark.parametrize("block_size", [4, 16, 64])
+@pytest.mark.parametrize("Hq,Hkv", [(8, 8), (16, 4)])
+def test_paged_decode_block_table(block_size, Hq, Hkv):
+    """KV blocks of several tokens addressed through a [B, max_blocks] block table."""
+    import lm_ops
+    B, D = 5, 128
+    lens = [1, block_size, block_size + 1, 333, 0]
+    n_blocks = 128
+    g = torch.Generator().manual_seed(block_size)
+    max_blocks = max((n + block_size - 1) // block_size for n in lens)
+    perm = torch.randperm(n_blocks, generator=g)
+    table = torch.full((B, max_blocks), -1, dtype=torch.int32)
+    nxt = 0
+    for b, n in enumerate(lens):
+        nb = (n + block_size - 1) // block_size
+        table[b, :nb] = perm[nxt:nxt + nb].int()
+        nxt += nb
+    Q = torch.randn(B, Hq * D, generator=g).half()
+    K, V = (torch.randn(B, Hkv * D, generator=g).half() for _ in range(2))
+    Kc, Vc = (torch.randn(n_blocks * block_size, Hkv * D, generator=g).half() for _ in range(2))
+    off = torch.tensor(lens).cumsum(0).int()
+    S, P, O = lm_ops.paged_kv_attention_forward(Q.cuda(), K.cuda(), V.cuda(), Kc.cuda(), Vc.cuda(), table.cuda(),
+                                                off.cuda(), Hq, block_size=block_size)
+    tbl = table.clamp(min=0)
+    S32, P32, O32 = orc.paged_decode(Q, K, V, Kc, Vc, tbl, off, Hq, compute_dtype=torch.float32,
+                                     block_size=block_size)
+    assert (O.cpu().float() - O32.float()).abs().max() <= TOL16
+    assert (P.cpu() - P32).abs().max() < 2e-4

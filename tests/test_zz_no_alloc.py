@@ -32,8 +32,8 @@ def _call_pair(seed, B, H, D, lo, hi, chunk):
     out_new = torch.full_like(Q, float("nan"))
     _lib.check(lib.attn_b200_paged_decode(
         Q.data_ptr(), K.data_ptr(), V.data_ptr(), Kc.data_ptr(), Vc.data_ptr(), ci.data_ptr(), off.data_ptr(),
-        out_ref.data_ptr(), ws.data_ptr(), need, None, None, 0, B, H, D, T, Kc.size(0), 0, chunk, scale, None, None,
-        _lib.F16, _lib.F16, 3, None, stream), "paged_decode")
+        out_ref.data_ptr(), ws.data_ptr(), need, None, None, 0, B, H, H, D, T, Kc.size(0), 0, 1, 0, chunk, scale, None,
+        None, _lib.F16, _lib.F16, 3, None, stream), "paged_decode")
     _lib.check(lib.attn_b200_paged_decode_static_scratch(
         Q.data_ptr(), K.data_ptr(), V.data_ptr(), Kc.data_ptr(), Vc.data_ptr(), ci.data_ptr(), off.data_ptr(),
         out_new.data_ptr(), B, H, D, T, Kc.size(0), chunk, scale, None, None, _lib.F16, _lib.F16, None, stream),
