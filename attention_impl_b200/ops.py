@@ -297,6 +297,84 @@ class PagedDecodeGraph:
         return self.out
 
 
+class HostStagedDecoder:
+    """Paged decode whose per-step inputs live in pinned HOST memory, with the uploads overlapped
+    with compute: the batch is cut into ``n_groups`` runs of sequences with about equal token
+    counts; while group g is decoded, group g+1's q/k/v rows, slot-table slice and offsets travel
+    on a copy stream, and each group's output rows go back as soon as they exist.  Only the first
+    group's upload and the last group's download are exposed.  (The slot table is the bulk of the
+    traffic: 4 bytes per context token per step.)
+
+    ``Q, K, V`` pinned ``[B, H*D]``, ``cache_indices`` pinned int32 ``[T]``, ``offsets`` pinned int32 ``[B]``
+    (inclusive cumulative lengths), ``out`` pinned ``[B, H*D]``.  The KV pools stay on the device.
+    """
+
+    def __init__(self, K_cache, V_cache, num_heads: int, max_batch: int, max_tokens: int, *, dtype=None,
+                 n_groups: int = 4, scale: Optional[float] = None, k_scale=None, v_scale=None):
+        dev = K_cache.device
+        self.dev, self.H, self.n_groups = dev, num_heads, n_groups
+        self.Kc, self.Vc, self.kw = K_cache, V_cache, dict(scale=scale, k_scale=k_scale, v_scale=v_scale)
+        dtype = dtype or (K_cache.dtype if K_cache.dtype in _DT else torch.float16)
+        dim_kv = K_cache.size(1)
+        self.dim_q = None
+        self.dtype = dtype
+        self.d_ci = torch.empty(max_tokens, dtype=torch.int32, device=dev)
+        self.d_off = torch.empty(max_batch, dtype=torch.int32, device=dev)
+        self.h_off = torch.empty(max_batch, dtype=torch.int32).pin_memory()     # offsets rebased per group
+        self.d_q = self.d_k = self.d_v = self.d_o = None
+        self.max_batch, self.dim_kv = max_batch, dim_kv
+        with torch.cuda.device(dev):
+            self.copy_stream = torch.cuda.Stream()
+            self.events = [torch.cuda.Event() for _ in range(n_groups)]
+
+    def _ensure(self, dim_q):
+        if self.dim_q != dim_q:
+            dev, B = self.dev, self.max_batch
+            self.dim_q = dim_q
+            self.d_q = torch.empty(B, dim_q, dtype=self.dtype, device=dev)
+            self.d_k = torch.empty(B, self.dim_kv, dtype=self.dtype, device=dev)
+            self.d_v = torch.empty(B, self.dim_kv, dtype=self.dtype, device=dev)
+            self.d_o = torch.empty(B, dim_q, dtype=self.dtype, device=dev)
+
+    def __call__(self, Q, K, V, cache_indices, offsets, out) -> None:
+        """Enqueues everything; returns after the last output row has been copied (it synchronises
+        the compute stream once, at the end)."""
+        B = Q.size(0)
+        self._ensure(Q.size(1))
+        ends = offsets[:B].tolist()
+        T = ends[-1] if B else 0
+        # group boundaries (sequence indices) at about equal token counts
+        bounds, g = [0], 1
+        for b, e in enumerate(ends):
+            if g < self.n_groups and e >= T * g / self.n_groups and b + 1 < B:
+                bounds.append(b + 1)
+                g += 1
+        bounds.append(B)
+        cur = torch.cuda.current_stream(self.dev)
+        self.copy_stream.wait_stream(cur)           # staging buffers free again
+        spans = []
+        with torch.cuda.stream(self.copy_stream):
+            for i in range(len(bounds) - 1):
+                b0, b1 = bounds[i], bounds[i + 1]
+                t0 = ends[b0 - 1] if b0 else 0
+                t1 = ends[b1 - 1]
+                self.h_off[b0:b1] = offsets[b0:b1] - t0
+                self.d_q[b0:b1].copy_(Q[b0:b1], non_blocking=True)
+                self.d_k[b0:b1].copy_(K[b0:b1], non_blocking=True)
+                self.d_v[b0:b1].copy_(V[b0:b1], non_blocking=True)
+                self.d_ci[t0:t1].copy_(cache_indices[t0:t1], non_blocking=True)
+                self.d_off[b0:b1].copy_(self.h_off[b0:b1], non_blocking=True)
+                self.events[i].record(self.copy_stream)
+                spans.append((b0, b1, t0, t1))
+        for i, (b0, b1, t0, t1) in enumerate(spans):
+            cur.wait_event(self.events[i])
+            paged_kv_attention_forward(self.d_q[b0:b1], self.d_k[b0:b1], self.d_v[b0:b1], self.Kc, self.Vc,
+                                       self.d_ci[t0:t1], self.d_off[b0:b1], self.H, return_sp=False,
+                                       out=self.d_o[b0:b1], **self.kw)
+            out[b0:b1].copy_(self.d_o[b0:b1], non_blocking=True)
+        cur.synchronize()
+
+
 def paged_decode_partial(Q, K_cache, V_cache, cache_indices, offsets, num_heads: int, *,
                          scale: Optional[float] = None, chunk: Optional[int] = None, k_scale=None, v_scale=None,
                          workspace: Optional[torch.Tensor] = None) -> torch.Tensor:

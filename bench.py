@@ -249,13 +249,12 @@ class LargeDecode(Workload):
     def e2e_setup(self):
         self.h_in = [x.cpu().pin_memory() for x in (self.Q, self.K, self.V, self.ci, self.off)]
         self.h_out = torch.empty(self.O.shape, dtype=self.O.dtype).pin_memory()
+        # the public host-input operator: uploads overlapped with compute, group by group
+        self.staged = self.A.HostStagedDecoder(self.Kc, self.Vc, self.Hl, self.Bn, self.T)
         return sum(x.numel() * x.element_size() for x in self.h_in), self.h_out.numel() * self.h_out.element_size()
 
     def e2e_step(self):
-        dQ, dK, dV, dci, doff = (x.to(self.dev, non_blocking=True) for x in self.h_in)
-        _, _, o = self.A.paged_kv_attention_forward(dQ, dK, dV, self.Kc, self.Vc, dci, doff, self.Hl, return_sp=False)
-        self.h_out.copy_(o, non_blocking=True)
-        torch.cuda.current_stream().synchronize()   # the caller reads the result every step
+        self.staged(*self.h_in, self.h_out)          # returns once the last output row is in host memory
 
     def units_per_step_rank(self):
         return 2.0 * self.T * self.Hl * self.D * self.kv_bytes_el
