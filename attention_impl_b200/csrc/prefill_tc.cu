@@ -306,6 +306,161 @@ struct SmemLayout2 {
     int abort;
 };
 
+
+// One softmax thread = one query row (TMEM lane) of a 128-row tile: walks the key tiles, turns S into
+// P in place, keeps the running maximum lazily, and writes the normalised output row at the end.
+template <typename T>
+__device__ __forceinline__ void softmax_row(unsigned long long* s_full, unsigned long long* p_full,
+                                            unsigned long long* o_full, uint32_t s_addr, uint32_t o_addr, int nk,
+                                            int tq, int r, int trace_role, const Params& p, volatile int* cta_abort,
+                                            bool row_valid, int64_t out_row, int h) {
+    {
+        float m_ref = -INFINITY, l = 0.f;
+        // P <= 2^kLazy.  On the fp16 path the exponent argument passes through fp16: keeping it
+        // below 1 keeps its rounding below the rounding of P itself.
+        constexpr float kLazy = std::is_same<T, __nv_bfloat16>::value ? 8.f : 1.f;
+        bool ok = true;
+        for (int j = 0; j < nk; ++j) {
+            if (r == 0) TRACE(trace_role, j, 0);
+            if (!(ok = mbar_wait(s_full, j & 1, cta_abort, p.err_flag))) break;
+            tc_fence_after();
+            if (r == 0) TRACE(trace_role, j, 1);
+            float sv[BN];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) tmem_ld32_nowait(s_addr + c * 32, sv + c * 32);
+            tmem_ld_wait();
+            if (r == 0) TRACE(trace_role, j, 2);
+            if (j == tq) {
+#pragma unroll
+                for (int i = 0; i < BN; ++i)
+                    if (i > r) sv[i] = -INFINITY;
+            }
+            // eight independent chains, then a tree: a single 128-long dependent chain would cost
+            // its full latency with only two softmax warps per scheduler to hide it
+            float mx8[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) mx8[i] = fmaxf(sv[i], sv[8 + i]);
+#pragma unroll
+            for (int i = 16; i < BN; i += 16)
+#pragma unroll
+                for (int k = 0; k < 8; ++k) mx8[k] = max3(mx8[k], sv[i + k], sv[i + 8 + k]);
+            const float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
+                                   fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
+            const float m_new = fmaxf(m_ref, mx * p.scale_log2);
+            // advance the reference maximum only when some row of the warp outgrew it by 2^8
+            if (__any_sync(0xffffffffu, m_new > m_ref + kLazy)) {
+                if (j > 0) {
+                    const float alpha = fast_exp2(m_ref - m_new);
+                    l *= alpha;
+                    if (!(ok = mbar_wait(o_full, (j - 1) & 1, cta_abort, p.err_flag))) break;
+                    tc_fence_after();
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        float ov[32];
+                        tmem_ld32(o_addr + c * 32, ov);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) ov[i] *= alpha;
+                        tmem_st32(o_addr + c * 32, reinterpret_cast<const uint32_t*>(ov));
+                    }
+                    tmem_st_wait();
+                }
+                m_ref = m_new;
+            }
+            if (r == 0) TRACE(trace_role, j, 3);
+            // P = 2^(s*scale - m_ref): the exponent argument is formed in fp32, packed to f16x2 and
+            // passed through the packed ex2 of the special-function unit (two results per
+            // operation).  fp16 inputs: that result is P itself and row sums run over eight short
+            // fp16x2 chains before widening.  bf16 inputs: A and B of one MMA must share a type, and
+            // widening + re-packing the f16x2 result costs more issue slots than it saves, so that
+            // path uses the fp32 ex2.
+            float rs = 0.f;
+            if constexpr (std::is_same<T, __half>::value) {
+                __half2 hs[8];
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {           // 64 keys -> 32 packed columns per store
+                    uint32_t pk[32];
+#pragma unroll
+                    for (int i = 0; i < 64; i += 2) {
+                        const float x0 = fmaf(sv[c * 64 + i], p.scale_log2, -m_ref);
+                        const float x1 = fmaf(sv[c * 64 + i + 1], p.scale_log2, -m_ref);
+                        const uint32_t e = ex2_f16x2(pack2<__half>(x0, x1));
+                        pk[i >> 1] = e;
+                        const __half2 eh = *reinterpret_cast<const __half2*>(&e);
+                        const int g = (i >> 1) & 7;
+                        hs[g] = (c == 0 && i < 16) ? eh : __hadd2(hs[g], eh);
+                    }
+                    tmem_st32(s_addr + c * 32, pk);
+                }
+#pragma unroll
+                for (int g = 0; g < 8; g += 2) {
+                    const float2 a = __half22float2(hs[g]), b2 = __half22float2(hs[g + 1]);
+                    rs += (a.x + a.y) + (b2.x + b2.y);
+                }
+            } else {
+                // bf16 inputs: fp32 ex2, the remaining fp32 arithmetic as packed pairs (f32x2).
+                // Moving a share of the exponentials to a polynomial on the FMA pipe was measured
+                // (50 %, 25 %, 12.5 % of the elements): slower each time, the softmax warp is bound
+                // by instruction issue, not by the special-function unit.
+                float rs4[4] = {0.f, 0.f, 0.f, 0.f};
+                const float nm = -m_ref;
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    uint32_t pk[32];
+#pragma unroll
+                    for (int i = 0; i < 64; i += 4) {
+                        float x0, x1, x2, x3, p0, p1, p2, p3;
+                        fma2(x0, x1, sv[c * 64 + i], sv[c * 64 + i + 1], p.scale_log2, p.scale_log2, nm, nm);
+                        fma2(x2, x3, sv[c * 64 + i + 2], sv[c * 64 + i + 3], p.scale_log2, p.scale_log2, nm, nm);
+                        p0 = fast_exp2(x0);
+                        p1 = fast_exp2(x1);
+                        p2 = fast_exp2(x2);
+                        p3 = fast_exp2(x3);
+                        add2(rs4[0], rs4[1], rs4[0], rs4[1], p0, p1);
+                        add2(rs4[2], rs4[3], rs4[2], rs4[3], p2, p3);
+                        pk[i >> 1] = pack2<T>(p0, p1);
+                        pk[(i >> 1) + 1] = pack2<T>(p2, p3);
+                    }
+                    tmem_st32(s_addr + c * 32, pk);
+                }
+                rs = (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
+            }
+            l += rs;
+            if (r == 0) TRACE(trace_role, j, 4);
+            tmem_st_wait();
+            tc_fence_before();
+            mbar_arrive(p_full);
+            if (r == 0) TRACE(trace_role, j, 5);
+        }
+        if (ok && nk > 0) ok = mbar_wait(o_full, (nk - 1) & 1, cta_abort, p.err_flag);
+        if (ok && nk > 0) {
+            tc_fence_after();
+            const bool valid = row_valid;
+            const float inv = 1.f / l;
+            const int64_t row = out_row;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                float ov[32];
+                tmem_ld32(o_addr + c * 32, ov);
+                if (!valid) continue;
+                if (p.out_f32) {
+                    float4* dst = reinterpret_cast<float4*>((float*)p.out + (row * p.H + h) * HD + c * 32);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i)
+                        dst[i] = make_float4(ov[4 * i] * inv, ov[4 * i + 1] * inv, ov[4 * i + 2] * inv, ov[4 * i + 3] * inv);
+                } else {
+                    uint4* dst = reinterpret_cast<uint4*>((T*)p.out + (row * p.H + h) * HD + c * 32);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        dst[i] = make_uint4(pack2<T>(ov[8 * i] * inv, ov[8 * i + 1] * inv),
+                                            pack2<T>(ov[8 * i + 2] * inv, ov[8 * i + 3] * inv),
+                                            pack2<T>(ov[8 * i + 4] * inv, ov[8 * i + 5] * inv),
+                                            pack2<T>(ov[8 * i + 6] * inv, ov[8 * i + 7] * inv));
+                }
+            }
+        }
+        }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(THREADS2, 1)
 prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -464,149 +619,8 @@ prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         const int tq = 2 * tp + w;                        // query tile index == index of its diagonal key tile
         const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
         const uint32_t s_addr = lane_base + w * 128, o_addr = lane_base + 256 + w * 128;
-        float m_ref = -INFINITY, l = 0.f;
-        // P <= 2^kLazy.  On the fp16 path the exponent argument passes through fp16: keeping it
-        // below 1 keeps its rounding below the rounding of P itself.
-        constexpr float kLazy = std::is_same<T, __nv_bfloat16>::value ? 8.f : 1.f;
-        bool ok = true;
-        for (int j = 0; j < nk; ++j) {
-            if (r == 0) TRACE(w, j, 0);
-            if (!(ok = mbar_wait(&sm.s_full[w], j & 1, cta_abort, p.err_flag))) break;
-            tc_fence_after();
-            if (r == 0) TRACE(w, j, 1);
-            float sv[BN];
-#pragma unroll
-            for (int c = 0; c < 4; ++c) tmem_ld32_nowait(s_addr + c * 32, sv + c * 32);
-            tmem_ld_wait();
-            if (r == 0) TRACE(w, j, 2);
-            if (j == tq) {
-#pragma unroll
-                for (int i = 0; i < BN; ++i)
-                    if (i > r) sv[i] = -INFINITY;
-            }
-            // eight independent chains, then a tree: a single 128-long dependent chain would cost
-            // its full latency with only two softmax warps per scheduler to hide it
-            float mx8[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) mx8[i] = fmaxf(sv[i], sv[8 + i]);
-#pragma unroll
-            for (int i = 16; i < BN; i += 16)
-#pragma unroll
-                for (int k = 0; k < 8; ++k) mx8[k] = max3(mx8[k], sv[i + k], sv[i + 8 + k]);
-            const float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
-                                   fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
-            const float m_new = fmaxf(m_ref, mx * p.scale_log2);
-            // advance the reference maximum only when some row of the warp outgrew it by 2^8
-            if (__any_sync(0xffffffffu, m_new > m_ref + kLazy)) {
-                if (j > 0) {
-                    const float alpha = fast_exp2(m_ref - m_new);
-                    l *= alpha;
-                    if (!(ok = mbar_wait(&sm.o_full[w], (j - 1) & 1, cta_abort, p.err_flag))) break;
-                    tc_fence_after();
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        float ov[32];
-                        tmem_ld32(o_addr + c * 32, ov);
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) ov[i] *= alpha;
-                        tmem_st32(o_addr + c * 32, reinterpret_cast<const uint32_t*>(ov));
-                    }
-                    tmem_st_wait();
-                }
-                m_ref = m_new;
-            }
-            if (r == 0) TRACE(w, j, 3);
-            // P = 2^(s*scale - m_ref): the exponent argument is formed in fp32, packed to f16x2 and
-            // passed through the packed ex2 of the special-function unit (two results per
-            // operation).  fp16 inputs: that result is P itself and row sums run over eight short
-            // fp16x2 chains before widening.  bf16 inputs: A and B of one MMA must share a type, and
-            // widening + re-packing the f16x2 result costs more issue slots than it saves, so that
-            // path uses the fp32 ex2.
-            float rs = 0.f;
-            if constexpr (std::is_same<T, __half>::value) {
-                __half2 hs[8];
-#pragma unroll
-                for (int c = 0; c < 2; ++c) {           // 64 keys -> 32 packed columns per store
-                    uint32_t pk[32];
-#pragma unroll
-                    for (int i = 0; i < 64; i += 2) {
-                        const float x0 = fmaf(sv[c * 64 + i], p.scale_log2, -m_ref);
-                        const float x1 = fmaf(sv[c * 64 + i + 1], p.scale_log2, -m_ref);
-                        const uint32_t e = ex2_f16x2(pack2<__half>(x0, x1));
-                        pk[i >> 1] = e;
-                        const __half2 eh = *reinterpret_cast<const __half2*>(&e);
-                        const int g = (i >> 1) & 7;
-                        hs[g] = (c == 0 && i < 16) ? eh : __hadd2(hs[g], eh);
-                    }
-                    tmem_st32(s_addr + c * 32, pk);
-                }
-#pragma unroll
-                for (int g = 0; g < 8; g += 2) {
-                    const float2 a = __half22float2(hs[g]), b2 = __half22float2(hs[g + 1]);
-                    rs += (a.x + a.y) + (b2.x + b2.y);
-                }
-            } else {
-                // bf16 inputs: fp32 ex2, the remaining fp32 arithmetic as packed pairs (f32x2).
-                // Moving a share of the exponentials to a polynomial on the FMA pipe was measured
-                // (50 %, 25 %, 12.5 % of the elements): slower each time, the softmax warp is bound
-                // by instruction issue, not by the special-function unit.
-                float rs4[4] = {0.f, 0.f, 0.f, 0.f};
-                const float nm = -m_ref;
-#pragma unroll
-                for (int c = 0; c < 2; ++c) {
-                    uint32_t pk[32];
-#pragma unroll
-                    for (int i = 0; i < 64; i += 4) {
-                        float x0, x1, x2, x3, p0, p1, p2, p3;
-                        fma2(x0, x1, sv[c * 64 + i], sv[c * 64 + i + 1], p.scale_log2, p.scale_log2, nm, nm);
-                        fma2(x2, x3, sv[c * 64 + i + 2], sv[c * 64 + i + 3], p.scale_log2, p.scale_log2, nm, nm);
-                        p0 = fast_exp2(x0);
-                        p1 = fast_exp2(x1);
-                        p2 = fast_exp2(x2);
-                        p3 = fast_exp2(x3);
-                        add2(rs4[0], rs4[1], rs4[0], rs4[1], p0, p1);
-                        add2(rs4[2], rs4[3], rs4[2], rs4[3], p2, p3);
-                        pk[i >> 1] = pack2<T>(p0, p1);
-                        pk[(i >> 1) + 1] = pack2<T>(p2, p3);
-                    }
-                    tmem_st32(s_addr + c * 32, pk);
-                }
-                rs = (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
-            }
-            l += rs;
-            if (r == 0) TRACE(w, j, 4);
-            tmem_st_wait();
-            tc_fence_before();
-            mbar_arrive(&sm.p_full[w]);
-            if (r == 0) TRACE(w, j, 5);
-        }
-        if (ok && nk > 0) ok = mbar_wait(&sm.o_full[w], (nk - 1) & 1, cta_abort, p.err_flag);
-        if (ok && nk > 0) {
-            tc_fence_after();
-            const bool valid = q0 + w * BM + r < L;
-            const float inv = 1.f / l;
-            const int64_t row = seq_beg + q0 + w * BM + r;
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                float ov[32];
-                tmem_ld32(o_addr + c * 32, ov);
-                if (!valid) continue;
-                if (p.out_f32) {
-                    float4* dst = reinterpret_cast<float4*>((float*)p.out + (row * p.H + h) * HD + c * 32);
-#pragma unroll
-                    for (int i = 0; i < 8; ++i)
-                        dst[i] = make_float4(ov[4 * i] * inv, ov[4 * i + 1] * inv, ov[4 * i + 2] * inv, ov[4 * i + 3] * inv);
-                } else {
-                    uint4* dst = reinterpret_cast<uint4*>((T*)p.out + (row * p.H + h) * HD + c * 32);
-#pragma unroll
-                    for (int i = 0; i < 4; ++i)
-                        dst[i] = make_uint4(pack2<T>(ov[8 * i] * inv, ov[8 * i + 1] * inv),
-                                            pack2<T>(ov[8 * i + 2] * inv, ov[8 * i + 3] * inv),
-                                            pack2<T>(ov[8 * i + 4] * inv, ov[8 * i + 5] * inv),
-                                            pack2<T>(ov[8 * i + 6] * inv, ov[8 * i + 7] * inv));
-                }
-            }
-        }
+        softmax_row<T>(&sm.s_full[w], &sm.p_full[w], &sm.o_full[w], s_addr, o_addr, nk, tq, r, w, p, cta_abort,
+                       q0 + w * BM + r < L, seq_beg + q0 + w * BM + r, h);
     }
     // ---------------------------------------------------------------------- teardown
     if (warp == 8 && lane == 0 && sm.abort) {
@@ -622,6 +636,166 @@ prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     if (warp == 9) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512));
+    }
+}
+
+
+// =============================================================================================
+// Version 3: one 128-row query tile per CTA, TWO CTAs per SM.
+//
+// Same tensor-memory pipeline as version 2 (S -> P in place, O accumulated by the MMA, lazy
+// maximum) but each CTA owns a single query tile: 96 KB of shared memory (Q, one K tile, one V
+// tile), 256 TMEM columns (S, O), 256 threads.  Two such CTAs share an SM, so the second
+// warpgroup of version 2 becomes a second, independent CTA: one CTA's softmax overlaps the other's
+// MMAs as before, and in addition one CTA's prologue (TMEM allocation, first TMA loads) and
+// epilogue (O read-back and store) overlap the other's main loop, and a CTA never idles half of
+// its warps on the last key tile.  The price: K and V tiles are fetched from L2 once per query
+// tile instead of once per pair.
+//   warps 0-3  softmax (thread = query row)      warp 4  TMA: Q, then K_j / V_j as their tile frees
+//   warp 5     MMA issue (one spinning thread)   warps 6-7  idle (complete the register-donor warpgroup)
+// Registers: launched with 128 per thread (2 CTAs x 256 threads); 4 x 200 + 4 x 56 = 8 x 128.
+// =============================================================================================
+constexpr int THREADS3 = 256;
+
+struct SmemLayout3 {
+    alignas(1024) unsigned char q[TILE_BYTES];
+    alignas(1024) unsigned char k[TILE_BYTES];
+    alignas(1024) unsigned char v[TILE_BYTES];
+    alignas(8) unsigned long long q_full, s_full, p_full, o_full, k_full, k_empty, v_full, v_empty;
+    unsigned int tmem_base;
+    int abort;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(THREADS3, 2)
+prefill_tc3_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                   const __grid_constant__ CUtensorMap map_v, const Params p) {
+    extern __shared__ unsigned char smem_raw[];
+    SmemLayout3& sm = *reinterpret_cast<SmemLayout3*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int b = blockIdx.z, h = blockIdx.y;
+    const int t = p.n_qtiles - 1 - (int)blockIdx.x;        // heavy (late) tiles first
+    const int64_t seq_beg = b ? p.offsets[b - 1] : 0;
+    const int64_t seq_end = p.offsets[b];
+    if (seq_beg < 0 || seq_end < seq_beg || seq_end > p.n_tokens) {
+        if (p.err_flag && threadIdx.x == 0) atomicOr(p.err_flag, ATTN_B200_FLAG_BAD_OFFSETS);
+        return;
+    }
+    const int L = (int)(seq_end - seq_beg);
+    const int q0 = t * BM;
+    if (q0 >= L) return;
+    if (*(volatile int*)&g_abort) return;
+    const int n_kv = t + 1;
+    volatile int* cta_abort = &sm.abort;
+
+    if (threadIdx.x == 0) {
+        mbar_init(&sm.q_full, 1);
+        mbar_init(&sm.s_full, 1);
+        mbar_init(&sm.p_full, 128);
+        mbar_init(&sm.o_full, 1);
+        mbar_init(&sm.k_full, 1);
+        mbar_init(&sm.k_empty, 1);
+        mbar_init(&sm.v_full, 1);
+        mbar_init(&sm.v_empty, 1);
+        sm.abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 5) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(256));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = sm.tmem_base;
+    const int col0 = h * HD;
+
+    int issued = 0;
+    if (warp >= 4) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+        if (warp == 4) {
+            // -------------------------------------------------------------- TMA producer
+            if (lane == 0) {
+                mbar_expect_tx(&sm.q_full, TILE_BYTES);
+                tma_load_2d(sm.q, &map_q, col0, (int)(seq_beg + q0), &sm.q_full);
+                tma_load_2d(sm.q + SUB_BYTES, &map_q, col0 + 64, (int)(seq_beg + q0), &sm.q_full);
+                for (int j = 0; j < n_kv; ++j) {
+                    const int row = (int)(seq_beg + (int64_t)j * BN);
+                    if (j > 0 && !mbar_wait(&sm.k_empty, (j - 1) & 1, cta_abort, p.err_flag)) break;
+                    mbar_expect_tx(&sm.k_full, TILE_BYTES);
+                    tma_load_2d(sm.k, &map_k, col0, row, &sm.k_full);
+                    tma_load_2d(sm.k + SUB_BYTES, &map_k, col0 + 64, row, &sm.k_full);
+                    if (j > 0 && !mbar_wait(&sm.v_empty, (j - 1) & 1, cta_abort, p.err_flag)) { issued = 2 * j + 1; break; }
+                    mbar_expect_tx(&sm.v_full, TILE_BYTES);
+                    tma_load_2d(sm.v, &map_v, col0, row, &sm.v_full);
+                    tma_load_2d(sm.v + SUB_BYTES, &map_v, col0 + 64, row, &sm.v_full);
+                    issued = 2 * j + 2;          // K tiles issued = (issued+1)/2, V tiles = issued/2
+                }
+            }
+        } else if (warp == 5) {
+            // -------------------------------------------------------------- MMA issuer
+            constexpr uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
+            constexpr uint32_t idesc_qk = (1u << 4) | (fmt << 7) | (fmt << 10) | ((BN >> 3) << 17) | ((BM >> 4) << 24);
+            constexpr uint32_t idesc_pv = idesc_qk | (1u << 16);   // B (= V) is MN-major, same type as P
+            if (lane == 0) {
+                const uint64_t qd = smem_desc(smem_u32(sm.q), 16, 1024), kd = smem_desc(smem_u32(sm.k), 16, 1024);
+                const uint64_t vd = smem_desc(smem_u32(sm.v), SUB_BYTES, 1024);
+                auto issue_qk = [&]() {
+#pragma unroll
+                    for (int kk = 0; kk < HD / 16; ++kk) {
+                        const uint32_t off16 = ((kk >> 2) * SUB_BYTES + (kk & 3) * 32) >> 4;
+                        umma_f16(tmem, qd + off16, kd + off16, idesc_qk, kk > 0);
+                    }
+                    umma_commit(&sm.s_full);
+                    umma_commit(&sm.k_empty);
+                };
+                bool ok = mbar_wait_spin(&sm.q_full, 0, cta_abort, p.err_flag) &&
+                          mbar_wait_spin(&sm.k_full, 0, cta_abort, p.err_flag);
+                if (ok) {
+                    tc_fence_after();
+                    issue_qk();
+                }
+                for (int j = 0; ok && j < n_kv; ++j) {
+                    if (!(ok = mbar_wait_spin(&sm.p_full, j & 1, cta_abort, p.err_flag))) break;
+                    if (!(ok = mbar_wait_spin(&sm.v_full, j & 1, cta_abort, p.err_flag))) break;
+                    tc_fence_after();
+                    umma_f16_ts(tmem + 128, tmem, vd, idesc_pv, j > 0 ? 1u : 0u);
+#pragma unroll
+                    for (int kk = 1; kk < BN / 16; ++kk)
+                        umma_f16_ts(tmem + 128, tmem + kk * 8, vd + ((kk * 2048) >> 4), idesc_pv, 1u);
+                    umma_commit(&sm.o_full);
+                    umma_commit(&sm.v_empty);
+                    if (j + 1 < n_kv) {
+                        if (!(ok = mbar_wait_spin(&sm.k_full, (j + 1) & 1, cta_abort, p.err_flag))) break;
+                        tc_fence_after();
+                        issue_qk();
+                    }
+                }
+            }
+            __syncwarp();
+        }
+    } else {
+        // ------------------------------------------------------------------ softmax
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 200;");
+        const int r = threadIdx.x;
+        const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
+        softmax_row<T>(&sm.s_full, &sm.p_full, &sm.o_full, lane_base, lane_base + 128, n_kv, t, r, 0, p, cta_abort,
+                       q0 + r < L, seq_beg + q0 + r, h);
+    }
+    // ---------------------------------------------------------------------- teardown
+    if (warp == 4 && lane == 0 && sm.abort) {
+        const long long t0 = clock64();
+        while (!mbar_try(&sm.q_full, 0) && clock64() - t0 < WAIT_CYCLES) {}
+        const int nk_issued = (issued + 1) / 2, nv_issued = issued / 2;
+        if (nk_issued > 0) while (!mbar_try(&sm.k_full, (nk_issued - 1) & 1) && clock64() - t0 < WAIT_CYCLES) {}
+        if (nv_issued > 0) while (!mbar_try(&sm.v_full, (nv_issued - 1) & 1) && clock64() - t0 < WAIT_CYCLES) {}
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 5) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(256));
     }
 }
 
@@ -696,9 +870,10 @@ int prefill_tc_launch(const void* q, const void* k, const void* v, const int32_t
     if ((rc = make_map(&mq, q, n_tokens, H, dtype)) || (rc = make_map(&mk, k, n_tokens, H, dtype)) ||
         (rc = make_map(&mv, v, n_tokens, H, dtype)))
         return rc;
-    static const bool use_v1 = [] { const char* e = getenv("ATTN_B200_PREFILL_V1"); return e && e[0] == '1'; }();
-    const int rows_per_cta = use_v1 ? BM : 2 * BM;
-    const int smem = (int)(use_v1 ? sizeof(SmemLayout) : sizeof(SmemLayout2)) + 1024;
+    static const int version = [] { const char* e = getenv("ATTN_B200_PREFILL_VERSION"); return e ? atoi(e) : 2; }();
+    const bool use_v1 = version == 1, use_v3 = version == 3;
+    const int rows_per_cta = (use_v1 || use_v3) ? BM : 2 * BM;
+    const int smem = (int)(use_v1 ? sizeof(SmemLayout) : use_v3 ? sizeof(SmemLayout3) : sizeof(SmemLayout2)) + 1024;
     Params p{offsets, out, B, H, n_tokens, (max_len + rows_per_cta - 1) / rows_per_cta, scale * kLog2e, out_f32,
              err_flag};
     dim3 grid(p.n_qtiles, H, B);
@@ -707,6 +882,18 @@ int prefill_tc_launch(const void* q, const void* k, const void* v, const int32_t
     if (e != cudaSuccess) return (int)e;
     if ((e = cudaMemsetAsync(abort_addr, 0, sizeof(int), st)) != cudaSuccess) return (int)e;
     zero_tail_kernel<<<64, 256, 0, st>>>(out, offsets, B, n_tokens, (int64_t)H * HD * (out_f32 ? 4 : 2));
+    if (use_v3) {
+        if (dtype == ATTN_B200_BF16) {
+            if ((e = cudaFuncSetAttribute(prefill_tc3_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) != cudaSuccess)
+                return (int)e;
+            prefill_tc3_kernel<__nv_bfloat16><<<grid, THREADS3, smem, st>>>(mq, mk, mv, p);
+        } else {
+            if ((e = cudaFuncSetAttribute(prefill_tc3_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) != cudaSuccess)
+                return (int)e;
+            prefill_tc3_kernel<__half><<<grid, THREADS3, smem, st>>>(mq, mk, mv, p);
+        }
+        return (int)cudaGetLastError();
+    }
     if (!use_v1) {
         if (dtype == ATTN_B200_BF16) {
             if ((e = cudaFuncSetAttribute(prefill_tc2_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) != cudaSuccess)
