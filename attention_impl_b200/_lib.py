@@ -41,6 +41,8 @@ PROTOTYPES = {
     "attn_b200_lse_combine": (_i32, [_vp, _i32, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _f32, _i32, _vp]),
     "attn_b200_varlen_prefill": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i64, _i32, _i32, _i32, _f32,
                                         _i32, _i32, _i32, _vp, _vp]),
+    "attn_b200_paged_prefill": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i64, _i64, _i32, _i32, _i32, _i32, _i32,
+                                       _i64, _f32, _i32, _i32, _vp, _vp]),
     "attn_b200_dense_attention": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _f32, _f32,
                                          _i32, _vp]),
 }

@@ -519,6 +519,51 @@ def paged_attention_forward(Q, K, V, offsets, num_heads: int, *, scale: Optional
     return [S, P, O]
 
 
+def paged_prefill_attention(Q, K_cache, V_cache, cache_indices, kv_offsets, q_offsets, num_heads: int, *,
+                            scale: Optional[float] = None, max_q_len: Optional[int] = None,
+                            max_kv_len: Optional[int] = None, force_generic: bool = False,
+                            err_flag: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Chunked / prefix-cached prefill through the slot table (not in the reference).
+
+    Q ``[sum q_len, H*D]`` holds, per sequence, the query rows of its LAST ``q_len_b`` tokens
+    (``q_offsets`` int32 ``[B]``, inclusive cumulative); ``cache_indices`` int32 ``[sum kv_len]`` /
+    ``kv_offsets`` address ALL of the sequence's tokens in the pools (prefix and chunk, e.g. appended
+    with :func:`rope_and_cache_write`).  Query i of a chunk sees key j iff ``j <= kv_len - q_len + i``.
+    With ``q_len == kv_len`` this is the packed causal prefill, with ``q_len == 1`` the paged decode
+    without a separate current token.  Returns O ``[sum q_len, H*D]``.
+    """
+    for t, n in ((Q, "Q"), (K_cache, "K_cache"), (V_cache, "V_cache")):
+        _check_input(t, n)
+    for t, n in ((cache_indices, "cache_indices"), (kv_offsets, "kv_offsets"), (q_offsets, "q_offsets")):
+        _int32(t, n)
+    dt = _dtype_code(Q, "Q")
+    if K_cache.dtype != Q.dtype or V_cache.dtype != Q.dtype or V_cache.shape != K_cache.shape:
+        raise RuntimeError("K_cache and V_cache must share Q's dtype and each other's shape")
+    nq, dim = Q.shape
+    if dim % num_heads:
+        raise RuntimeError("Q.size(1) must be a multiple of num_heads")
+    H, D = num_heads, dim // num_heads
+    Hkv = K_cache.size(1) // D
+    B = q_offsets.numel()
+    if K_cache.size(1) % D or H % Hkv or kv_offsets.numel() != B:
+        raise RuntimeError("pools must be [slots, Hkv*D] with Hkv dividing num_heads; one offset per sequence")
+    if scale is None:
+        scale = 1.0 / math.sqrt(D)
+    dev = Q.device
+    with torch.cuda.device(dev):
+        if max_q_len is None:
+            max_q_len = int(torch.diff(q_offsets, prepend=q_offsets.new_zeros(1)).max().item()) if B else 0
+        if max_kv_len is None:
+            max_kv_len = int(torch.diff(kv_offsets, prepend=kv_offsets.new_zeros(1)).max().item()) if B else 0
+        O = torch.zeros_like(Q)
+        check(lib.attn_b200_paged_prefill(Q.data_ptr(), K_cache.data_ptr(), V_cache.data_ptr(),
+                                          cache_indices.data_ptr(), kv_offsets.data_ptr(), q_offsets.data_ptr(),
+                                          O.data_ptr(), B, nq, cache_indices.numel(), max_q_len, max_kv_len, H, Hkv, D,
+                                          K_cache.size(0), float(scale), dt, int(force_generic), _ptr(err_flag),
+                                          _stream()), "paged_prefill_attention")
+    return O
+
+
 def naive_attention_forward(Q, K, V, mask, num_heads: int, *, scale: Optional[float] = None,
                             fill: float = 100000.0, return_sp: bool = True) -> List[torch.Tensor]:
     """Dense masked MHA (attention_kernel.cu:187-229): Q, K, V ``[B, L, H*D]``, mask ``[B, L, L]``

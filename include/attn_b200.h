@@ -204,6 +204,20 @@ ATTN_B200_API int attn_b200_varlen_prefill(const void* q, const void* k, const v
                              float scale, int dtype, int out_f32, int force_generic, int32_t* err_flag,
                              void* stream);
 
+/* Chunked / prefix-cached prefill through the slot table (no counterpart in the reference: it is
+ * its packed prefill and its paged single-query operator unified).  Sequence b contributes the
+ * query rows [q_offsets[b-1], q_offsets[b]) of q [n_q_tokens, H*D] — the LAST tokens of the sequence —
+ * and the keys slots[kv_offsets[b-1] .. kv_offsets[b]) (all of its tokens, the chunk's own included,
+ * already in the pools k_cache, v_cache [n_slots, n_kv_heads*D]).  Query i of a chunk of q_len rows
+ * over kv_len keys sees key j iff j <= kv_len - q_len + i.  max_q_len / max_kv_len bound the
+ * per-sequence lengths (grid and shared-memory sizing; max_kv_len <= 12288 on the generic path).
+ * dtype F16 / BF16 / F32; out [n_q_tokens, H*D] in dtype. */
+ATTN_B200_API int attn_b200_paged_prefill(const void* q, const void* k_cache, const void* v_cache,
+                                          const int32_t* slots, const int32_t* kv_offsets, const int32_t* q_offsets,
+                                          void* out, int B, int64_t n_q_tokens, int64_t n_kv_tokens, int max_q_len,
+                                          int max_kv_len, int H, int n_kv_heads, int D, int64_t n_slots, float scale,
+                                          int dtype, int force_generic, int32_t* err_flag, void* stream);
+
 /* Dense masked attention.  Replaces naive_attention_forward (attention_kernel.cu:187-229,
  * kernel :15-94).  q, k, v, out [B, L, H*D]; mask [B, L, L] (dtype) or NULL; scores are
  * scale*<q,k> + (mask-1)*fill;  S, P optional [B, H, L, L] (dtype). */

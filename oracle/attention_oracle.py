@@ -258,6 +258,38 @@ def packed_prefill(Q, K, V, offsets, num_heads: int, compute_dtype=None, out_dty
     return O
 
 
+def paged_prefill(Q, K_cache, V_cache, cache_indices, kv_offsets, q_offsets, num_heads, scale=None,
+                  compute_dtype=None, out_dtype=None):
+    """Chunked prefill through the slot table (not in the reference; the packed-prefill math of
+    tests/test_packed_attention.py:9-22 applied to gathered rows): per sequence, the query rows are
+    its last ``q_len`` tokens and see key j iff ``j <= kv_len - q_len + i``."""
+    nq, dim = Q.shape
+    H, D = num_heads, dim // num_heads
+    Hkv = K_cache.shape[1] // D
+    g = H // Hkv
+    if scale is None:
+        scale = 1.0 / math.sqrt(D)
+    cd = compute_dtype or Q.dtype
+    qb, qe = _starts(q_offsets)
+    kb, ke = _starts(kv_offsets)
+    O = torch.zeros(Q.shape, dtype=out_dtype or Q.dtype)
+    idx = cache_indices.long()
+    for b in range(len(qe)):
+        lq, lk = qe[b] - qb[b], ke[b] - kb[b]
+        if lq == 0:
+            continue
+        rows = idx[kb[b]:ke[b]]
+        q = Q[qb[b]:qe[b]].to(cd).reshape(lq, H, D).permute(1, 0, 2)
+        k = K_cache[rows].to(cd).reshape(lk, Hkv, D).permute(1, 0, 2).repeat_interleave(g, dim=0)
+        v = V_cache[rows].to(cd).reshape(lk, Hkv, D).permute(1, 0, 2).repeat_interleave(g, dim=0)
+        S = torch.matmul(q, k.transpose(-1, -2)) * scale
+        vis = torch.arange(lk).unsqueeze(0) <= (lk - lq + torch.arange(lq)).unsqueeze(1)
+        S = S.masked_fill(~vis.unsqueeze(0), float("-inf"))
+        P = S.softmax(dim=-1)
+        O[qb[b]:qe[b]] = torch.matmul(P, v).permute(1, 0, 2).reshape(lq, dim).to(O.dtype)
+    return O
+
+
 # --------------------------------------------------------------------------------------
 # a3: rotary embedding
 # --------------------------------------------------------------------------------------
