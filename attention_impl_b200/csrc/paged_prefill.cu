@@ -137,8 +137,18 @@ extern "C" int attn_b200_paged_prefill(const void* q, const void* k_cache, const
     }
 }
 
-// Tensor-core form: not built yet; everything takes the generic kernel.
+// Tensor-core form (tcgen05, K/V gathered into shared memory by cp.async): prefill_tc.cu
 namespace attn {
-bool paged_prefill_tc_supported(const PagedPrefillParams&, int) { return false; }
-int paged_prefill_tc_launch(const PagedPrefillParams&, int, cudaStream_t) { return ATTN_B200_ESHAPE; }
+int paged_prefill_tc_launch_impl(const void* q, const void* k_cache, const void* v_cache, const int32_t* slots,
+                                 const int32_t* kv_offsets, const int32_t* q_offsets, void* out, int B,
+                                 int64_t n_q_tokens, int64_t n_kv_tokens, int max_q_len, int H, int Hkv, int D,
+                                 int64_t n_slots, float scale, int dtype, int32_t* err_flag, cudaStream_t st);
+bool paged_prefill_tc_supported(const PagedPrefillParams& p, int dtype) {
+    return p.D == 128 && (dtype == ATTN_B200_F16 || dtype == ATTN_B200_BF16);
+}
+int paged_prefill_tc_launch(const PagedPrefillParams& p, int dtype, cudaStream_t st) {
+    return paged_prefill_tc_launch_impl(p.q, p.k_cache, p.v_cache, p.slots, p.kv_offsets, p.q_offsets, p.out, p.B,
+                                        p.n_q_tokens, p.n_kv_tokens, p.max_q_len, p.H, p.Hkv, p.D, p.n_slots, p.scale,
+                                        dtype, p.err_flag, st);
+}
 }  // namespace attn

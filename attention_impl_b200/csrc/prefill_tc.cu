@@ -309,10 +309,12 @@ struct SmemLayout2 {
 
 // One softmax thread = one query row (TMEM lane) of a 128-row tile: walks the key tiles, turns S into
 // P in place, keeps the running maximum lazily, and writes the normalised output row at the end.
+// `qpos` is the row's position in key coordinates (keys 0..qpos are visible): its index within the
+// sequence for the packed prefill, kv_len - q_len + index for a chunk over a cached prefix.
 template <typename T>
 __device__ __forceinline__ void softmax_row(unsigned long long* s_full, unsigned long long* p_full,
                                             unsigned long long* o_full, uint32_t s_addr, uint32_t o_addr, int nk,
-                                            int tq, int r, int trace_role, const Params& p, volatile int* cta_abort,
+                                            int qpos, int r, int trace_role, const Params& p, volatile int* cta_abort,
                                             bool row_valid, int64_t out_row, int h) {
     {
         float m_ref = -INFINITY, l = 0.f;
@@ -330,10 +332,12 @@ __device__ __forceinline__ void softmax_row(unsigned long long* s_full, unsigned
             for (int c = 0; c < 4; ++c) tmem_ld32_nowait(s_addr + c * 32, sv + c * 32);
             tmem_ld_wait();
             if (r == 0) TRACE(trace_role, j, 2);
-            if (j == tq) {
+            // key (j*BN + i) is visible to this row iff it is <= qpos (the row's position among the keys)
+            const int lim = qpos - j * BN;
+            if (lim < BN - 1) {
 #pragma unroll
                 for (int i = 0; i < BN; ++i)
-                    if (i > r) sv[i] = -INFINITY;
+                    if (i > lim) sv[i] = -INFINITY;
             }
             // eight independent chains, then a tree: a single 128-long dependent chain would cost
             // its full latency with only two softmax warps per scheduler to hide it
@@ -619,7 +623,7 @@ prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         const int tq = 2 * tp + w;                        // query tile index == index of its diagonal key tile
         const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
         const uint32_t s_addr = lane_base + w * 128, o_addr = lane_base + 256 + w * 128;
-        softmax_row<T>(&sm.s_full[w], &sm.p_full[w], &sm.o_full[w], s_addr, o_addr, nk, tq, r, w, p, cta_abort,
+        softmax_row<T>(&sm.s_full[w], &sm.p_full[w], &sm.o_full[w], s_addr, o_addr, nk, tq * BM + r, r, w, p, cta_abort,
                        q0 + w * BM + r < L, seq_beg + q0 + w * BM + r, h);
     }
     // ---------------------------------------------------------------------- teardown
@@ -780,7 +784,7 @@ prefill_tc3_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         asm volatile("setmaxnreg.inc.sync.aligned.u32 200;");
         const int r = threadIdx.x;
         const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
-        softmax_row<T>(&sm.s_full, &sm.p_full, &sm.o_full, lane_base, lane_base + 128, n_kv, t, r, 0, p, cta_abort,
+        softmax_row<T>(&sm.s_full, &sm.p_full, &sm.o_full, lane_base, lane_base + 128, n_kv, t * BM + r, r, 0, p, cta_abort,
                        q0 + r < L, seq_beg + q0 + r, h);
     }
     // ---------------------------------------------------------------------- teardown
@@ -796,6 +800,255 @@ prefill_tc3_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     if (warp == 5) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(256));
+    }
+}
+
+
+// =============================================================================================
+// Paged form of version 2: the K and V tiles are GATHERED through the slot table.
+//
+// Chunked / prefix-cached prefill: sequence b's query rows are its last q_len tokens (packed in q),
+// its keys are the pool rows slots[kv_beg .. kv_beg + kv_len) (prefix and chunk); query i sees key
+// j iff j <= kv_len - q_len + i.  Everything downstream of shared memory is version 2 (two query
+// tiles per CTA, S -> P in tensor memory, O accumulated by the MMA).  What changes is the producer
+// of K/V: a fourth warpgroup (warps 12-15) copies the 128 rows of a tile with 16-byte cp.async
+// (16 consecutive lanes = one 256-byte row, so a warp instruction reads two whole rows) into the
+// same 128-byte-swizzled layout TMA would have produced; rows past the end of the sequence are
+// zero-filled.  A copy group is published (fence.proxy.async + mbarrier arrive by all 128 producer
+// threads) once it has landed.  Grouped-query heads: query head h reads KV head h / (H / Hkv).
+// =============================================================================================
+constexpr int THREADS_PG = 512;
+
+struct PagedTcParams {
+    const int32_t* slots;
+    const int32_t* kv_offsets;
+    const int32_t* q_offsets;
+    const void* k_cache;
+    const void* v_cache;
+    int Hkv;
+    int64_t n_kv_tokens, n_slots;
+};
+
+struct SmemLayoutPg {
+    alignas(1024) unsigned char q[2][TILE_BYTES];
+    alignas(1024) unsigned char k[STAGES][TILE_BYTES];
+    alignas(1024) unsigned char v[STAGES][TILE_BYTES];
+    alignas(8) unsigned long long q_full;
+    unsigned long long s_full[2], p_full[2], o_full[2];
+    unsigned long long k_full[STAGES], k_empty[STAGES], v_full[STAGES], v_empty[STAGES];
+    unsigned int tmem_base;
+    int abort;
+};
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+
+template <typename T>
+__global__ void __launch_bounds__(THREADS_PG, 1)
+paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const Params p, const PagedTcParams pg) {
+    extern __shared__ unsigned char smem_raw[];
+    SmemLayoutPg& sm = *reinterpret_cast<SmemLayoutPg*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int b = blockIdx.z, h = blockIdx.y;
+    const int tp = p.n_qtiles - 1 - (int)blockIdx.x;       // pair of query tiles, late pairs first
+    const int64_t q_beg = b ? pg.q_offsets[b - 1] : 0, q_end = pg.q_offsets[b];
+    const int64_t kv_beg = b ? pg.kv_offsets[b - 1] : 0, kv_end = pg.kv_offsets[b];
+    if (q_beg < 0 || q_end < q_beg || q_end > p.n_tokens || kv_beg < 0 || kv_end < kv_beg ||
+        kv_end > pg.n_kv_tokens || (kv_end - kv_beg) < (q_end - q_beg)) {
+        if (p.err_flag && threadIdx.x == 0) atomicOr(p.err_flag, ATTN_B200_FLAG_BAD_OFFSETS);
+        return;
+    }
+    const int q_len = (int)(q_end - q_beg), kv_len = (int)(kv_end - kv_beg);
+    const int q0 = tp * 2 * BM;
+    if (q0 >= q_len) return;
+    if (*(volatile int*)&g_abort) return;
+    const int shift = kv_len - q_len;
+    // key tiles per warpgroup: up to the tile that holds its last row's last visible key
+    auto tiles_for = [&](int w) {
+        const int first = q0 + w * BM;
+        if (first >= q_len) return 0;
+        const int last = first + BM - 1 < q_len - 1 ? first + BM - 1 : q_len - 1;
+        return (shift + last) / BN + 1;
+    };
+    const int n0 = tiles_for(0), n1 = tiles_for(1);
+    const int nmax = n1 > n0 ? n1 : n0;
+    volatile int* cta_abort = &sm.abort;
+
+    if (threadIdx.x == 0) {
+        mbar_init(&sm.q_full, 1);
+        for (int w = 0; w < 2; ++w) {
+            mbar_init(&sm.s_full[w], 1);
+            mbar_init(&sm.p_full[w], 128);
+            mbar_init(&sm.o_full[w], 1);
+        }
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&sm.k_full[s], 128);
+            mbar_init(&sm.k_empty[s], 1);
+            mbar_init(&sm.v_full[s], 128);
+            mbar_init(&sm.v_empty[s], 1);
+        }
+        sm.abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 9) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(512));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = sm.tmem_base;
+
+    // Registers: launched with 128 per thread (16 warps); 8 * 200 + 8 * 56 = 16 * 128.
+    if (warp >= 12) {
+        // ------------------------------------------------------------------ gather producers
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+        const int tid = threadIdx.x - 384;
+        const int c = tid & 15, rsub = tid >> 4;              // 16-byte chunk of a row, row within a pass
+        const int hk = h / (p.H / pg.Hkv);
+        const int64_t row_bytes = (int64_t)pg.Hkv * HD * 2;
+        const char* kbase = (const char*)pg.k_cache + (int64_t)hk * HD * 2 + c * 16;
+        const char* vbase = (const char*)pg.v_cache + (int64_t)hk * HD * 2 + c * 16;
+        const uint32_t dst_off = (c >> 3) * SUB_BYTES;
+        auto gather = [&](const char* base, unsigned char* stage, int j) {
+            const uint32_t sbase = smem_u32(stage) + dst_off;
+#pragma unroll 4
+            for (int pass = 0; pass < BN / 8; ++pass) {
+                const int row = pass * 8 + rsub;
+                const int kvpos = j * BN + row;
+                int64_t slot = -1;
+                if (kvpos < kv_len) {
+                    slot = pg.slots[kv_beg + kvpos];
+                    if (slot < 0 || slot >= pg.n_slots) {
+                        if (p.err_flag) atomicOr(p.err_flag, ATTN_B200_FLAG_BAD_SLOT);
+                        slot = -1;
+                    }
+                }
+                const uint32_t dst = sbase + row * 128 + (((c & 7) ^ (row & 7)) << 4);
+                cp_async16(dst, slot >= 0 ? base + slot * row_bytes : base, slot >= 0 ? 16 : 0);
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        };
+        bool ok = true;
+        int published = 0;
+        for (int j = 0; j < nmax && ok; ++j) {
+            const int s = j & 1;
+            if (j >= 1) {     // publish tile j-1: both of its groups have to land first
+                asm volatile("cp.async.wait_group 0;" ::: "memory");
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                mbar_arrive(&sm.k_full[(j - 1) & 1]);
+                mbar_arrive(&sm.v_full[(j - 1) & 1]);
+                published = j;
+            }
+            if (j >= STAGES) {
+                const uint32_t ph = ((j - STAGES) >> 1) & 1;
+                if (!(ok = mbar_wait(&sm.k_empty[s], ph, cta_abort, p.err_flag))) break;
+                if (!(ok = mbar_wait(&sm.v_empty[s], ph, cta_abort, p.err_flag))) break;
+            }
+            gather(kbase, sm.k[s], j);
+            gather(vbase, sm.v[s], j);
+        }
+        asm volatile("cp.async.wait_group 0;" ::: "memory");     // also the drain when aborting
+        if (ok && published < nmax) {
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_arrive(&sm.k_full[(nmax - 1) & 1]);
+            mbar_arrive(&sm.v_full[(nmax - 1) & 1]);
+        }
+    } else if (warp >= 8) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+        if (warp == 8) {
+            // -------------------------------------------------------------- TMA: the two Q tiles
+            if (lane == 0) {
+                const int col0 = h * HD;
+                mbar_expect_tx(&sm.q_full, 2 * TILE_BYTES);
+                for (int w = 0; w < 2; ++w) {
+                    tma_load_2d(sm.q[w], &map_q, col0, (int)(q_beg + q0 + w * BM), &sm.q_full);
+                    tma_load_2d(sm.q[w] + SUB_BYTES, &map_q, col0 + 64, (int)(q_beg + q0 + w * BM), &sm.q_full);
+                }
+            }
+        } else if (warp == 9) {
+            // -------------------------------------------------------------- MMA issuer (as version 2)
+            constexpr uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
+            constexpr uint32_t idesc_qk = (1u << 4) | (fmt << 7) | (fmt << 10) | ((BN >> 3) << 17) | ((BM >> 4) << 24);
+            constexpr uint32_t idesc_pv = idesc_qk | (1u << 16);
+            const int nw[2] = {n0, n1};
+            if (lane == 0) {
+                const uint64_t qd[2] = {smem_desc(smem_u32(sm.q[0]), 16, 1024), smem_desc(smem_u32(sm.q[1]), 16, 1024)};
+                const uint64_t kd[2] = {smem_desc(smem_u32(sm.k[0]), 16, 1024), smem_desc(smem_u32(sm.k[1]), 16, 1024)};
+                const uint64_t vd[2] = {smem_desc(smem_u32(sm.v[0]), SUB_BYTES, 1024), smem_desc(smem_u32(sm.v[1]), SUB_BYTES, 1024)};
+                auto issue_qk = [&](int w, int j) {
+                    const uint64_t a = qd[w], b2 = kd[j & 1];
+#pragma unroll
+                    for (int kk = 0; kk < HD / 16; ++kk) {
+                        const uint32_t off16 = ((kk >> 2) * SUB_BYTES + (kk & 3) * 32) >> 4;
+                        umma_f16(tmem + w * 128, a + off16, b2 + off16, idesc_qk, kk > 0);
+                    }
+                    umma_commit(&sm.s_full[w]);
+                };
+                auto issue_pv = [&](int w, int j) {
+                    const uint64_t b2 = vd[j & 1];
+                    const uint32_t d = tmem + 256 + w * 128, a = tmem + w * 128;
+                    umma_f16_ts(d, a, b2, idesc_pv, j > 0 ? 1u : 0u);
+#pragma unroll
+                    for (int kk = 1; kk < BN / 16; ++kk)
+                        umma_f16_ts(d, a + kk * 8, b2 + ((kk * 2048) >> 4), idesc_pv, 1u);
+                    umma_commit(&sm.o_full[w]);
+                };
+                bool ok = mbar_wait_spin(&sm.q_full, 0, cta_abort, p.err_flag) &&
+                          mbar_wait_spin(&sm.k_full[0], 0, cta_abort, p.err_flag);
+                if (ok) {
+                    tc_fence_after();
+                    issue_qk(0, 0);
+                    if (n1 > 0) issue_qk(1, 0);
+                    umma_commit(&sm.k_empty[0]);
+                }
+                for (int j = 0; ok && j < nmax; ++j) {
+                    const int s = j & 1;
+                    const uint32_t ph = (j >> 1) & 1;
+                    for (int w = 0; w < 2 && ok; ++w) {
+                        if (j < nw[w]) {
+                            if (!(ok = mbar_wait_spin(&sm.p_full[w], j & 1, cta_abort, p.err_flag))) break;
+                            if (w == 0 || j >= n0) { if (!(ok = mbar_wait_spin(&sm.v_full[s], ph, cta_abort, p.err_flag))) break; }
+                            tc_fence_after();
+                            issue_pv(w, j);
+                        }
+                        if (w == 1) umma_commit(&sm.v_empty[s]);
+                        if (j + 1 < nw[w]) {
+                            if (w == 0 || j + 1 >= n0) {
+                                if (!(ok = mbar_wait_spin(&sm.k_full[(j + 1) & 1], ((j + 1) >> 1) & 1, cta_abort, p.err_flag))) break;
+                            }
+                            tc_fence_after();
+                            issue_qk(w, j + 1);
+                        }
+                        if (w == 1 && j + 1 < nmax) umma_commit(&sm.k_empty[(j + 1) & 1]);
+                    }
+                }
+            }
+            __syncwarp();
+        }
+    } else {
+        // ------------------------------------------------------------------ softmax warpgroups
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 200;");
+        const int w = warp >> 2;
+        const int r = threadIdx.x & 127;
+        const int nk = w ? n1 : n0;
+        const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+        const int qi = q0 + w * BM + r;                    // row within the chunk
+        softmax_row<T>(&sm.s_full[w], &sm.p_full[w], &sm.o_full[w], lane_base + w * 128, lane_base + 256 + w * 128,
+                       nk, shift + qi, r, w, p, cta_abort, qi < q_len, q_beg + qi, h);
+    }
+    // ---------------------------------------------------------------------- teardown
+    if (warp == 8 && lane == 0 && sm.abort) {
+        const long long t0 = clock64();
+        while (!mbar_try(&sm.q_full, 0) && clock64() - t0 < WAIT_CYCLES) {}
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 9) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512));
     }
 }
 
@@ -914,6 +1167,39 @@ int prefill_tc_launch(const void* q, const void* k, const void* v, const int32_t
         if ((e = cudaFuncSetAttribute(prefill_tc_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) != cudaSuccess)
             return (int)e;
         prefill_tc_kernel<__half><<<grid, THREADS, smem, st>>>(mq, mk, mv, p);
+    }
+    return (int)cudaGetLastError();
+}
+
+
+// ---- paged (chunked) prefill launcher, called from paged_prefill.cu
+int paged_prefill_tc_launch_impl(const void* q, const void* k_cache, const void* v_cache, const int32_t* slots,
+                                 const int32_t* kv_offsets, const int32_t* q_offsets, void* out, int B,
+                                 int64_t n_q_tokens, int64_t n_kv_tokens, int max_q_len, int H, int Hkv, int D,
+                                 int64_t n_slots, float scale, int dtype, int32_t* err_flag, cudaStream_t st) {
+    using namespace tc;
+    if (D != HD || (dtype != ATTN_B200_F16 && dtype != ATTN_B200_BF16)) return ATTN_B200_ESHAPE;
+    if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)out) % 16) return ATTN_B200_EINVAL;
+    if (n_q_tokens > 0x7fffffffLL || B > 65535 || H > 65535) return ATTN_B200_ETOOLARGE;
+    CUtensorMap mq;
+    int rc = make_map(&mq, q, n_q_tokens, H, dtype);
+    if (rc) return rc;
+    const int smem = (int)sizeof(SmemLayoutPg) + 1024;
+    Params p{q_offsets, out, B, H, n_q_tokens, (max_q_len + 2 * BM - 1) / (2 * BM), scale * kLog2e, 0, err_flag};
+    PagedTcParams pg{slots, kv_offsets, q_offsets, k_cache, v_cache, Hkv, n_kv_tokens, n_slots};
+    dim3 grid(p.n_qtiles, H, B);
+    void* abort_addr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&abort_addr, g_abort);
+    if (e != cudaSuccess) return (int)e;
+    if ((e = cudaMemsetAsync(abort_addr, 0, sizeof(int), st)) != cudaSuccess) return (int)e;
+    if (dtype == ATTN_B200_BF16) {
+        if ((e = cudaFuncSetAttribute(paged_prefill_tc_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) != cudaSuccess)
+            return (int)e;
+        paged_prefill_tc_kernel<__nv_bfloat16><<<grid, THREADS_PG, smem, st>>>(mq, p, pg);
+    } else {
+        if ((e = cudaFuncSetAttribute(paged_prefill_tc_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) != cudaSuccess)
+            return (int)e;
+        paged_prefill_tc_kernel<__half><<<grid, THREADS_PG, smem, st>>>(mq, p, pg);
     }
     return (int)cudaGetLastError();
 }

@@ -50,3 +50,23 @@ def test_paged_prefill_limits_equal_packed_prefill_and_decode():
     _, _, Od = A.paged_kv_attention_forward(Q1.cuda(), Kc[last].cuda(), Vc[last].cuda(), Kc.cuda(), Vc.cuda(),
                                             ci_ctx.cuda(), off_ctx.cuda(), H, return_sp=False)
     assert (O1.float() - Od.float()).abs().max() <= 2e-3
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("H,Hkv", [(4, 4), (8, 2)])
+def test_paged_prefill_tensor_core_path(dtype, H, Hkv):
+    """head_dim 128, 16-bit: tcgen05 kernel with gathered K/V; also against the generic kernel."""
+    import attention_impl_b200 as A
+    q_lens = [256, 1, 300, 128, 513, 77]
+    kv_lens = [256, 700, 300, 1500, 513, 2048]
+    Q, Kc, Vc, ci, kvo, qo = _inputs(q_lens, kv_lens, H, Hkv, 128, dtype, 8192, seed=H + Hkv)
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    args = (Q.cuda(), Kc.cuda(), Vc.cuda(), ci.cuda(), kvo.cuda(), qo.cuda(), H)
+    O = A.paged_prefill_attention(*args, err_flag=flag)
+    torch.cuda.synchronize()
+    assert int(flag.item()) == 0
+    O32 = orc.paged_prefill(Q, Kc, Vc, ci, kvo, qo, H, compute_dtype=torch.float32, out_dtype=torch.float32)
+    tol = 2e-3 if dtype == torch.float16 else 1.6e-2
+    assert (O.cpu().float() - O32).abs().max() <= tol
+    Og = A.paged_prefill_attention(*args, force_generic=True)
+    assert (O.float() - Og.float()).abs().max() <= tol
