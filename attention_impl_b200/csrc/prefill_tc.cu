@@ -811,13 +811,14 @@ prefill_tc3_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 // its keys are the pool rows slots[kv_beg .. kv_beg + kv_len) (prefix and chunk); query i sees key
 // j iff j <= kv_len - q_len + i.  Everything downstream of shared memory is version 2 (two query
 // tiles per CTA, S -> P in tensor memory, O accumulated by the MMA).  What changes is the producer
-// of K/V: a fourth warpgroup (warps 12-15) copies the 128 rows of a tile with 16-byte cp.async
-// (16 consecutive lanes = one 256-byte row, so a warp instruction reads two whole rows) into the
-// same 128-byte-swizzled layout TMA would have produced; rows past the end of the sequence are
-// zero-filled.  A copy group is published (fence.proxy.async + mbarrier arrive by all 128 producer
-// threads) once it has landed.  Grouped-query heads: query head h reads KV head h / (H / Hkv).
+// of K/V: a fourth warpgroup (warps 12-13 for K, 14-15 for V) copies the 128 rows of a tile with
+// 16-byte cp.async (16 consecutive lanes = one 256-byte row, so a warp instruction reads two whole
+// rows) into the same 128-byte-swizzled layout TMA would have produced; rows past the end of the
+// sequence are zero-filled.  A tile is published (fence.proxy.async + mbarrier arrive by the
+// stream's 64 threads) once it has landed.  Grouped-query heads: query head h reads KV head h / (H / Hkv).
 // =============================================================================================
 constexpr int THREADS_PG = 512;
+constexpr int KSTAGES_PG = 2;    // K tiles in flight (3 fit in shared memory and were measured: no gain)
 
 struct PagedTcParams {
     const int32_t* slots;
@@ -831,11 +832,11 @@ struct PagedTcParams {
 
 struct SmemLayoutPg {
     alignas(1024) unsigned char q[2][TILE_BYTES];
-    alignas(1024) unsigned char k[STAGES][TILE_BYTES];
+    alignas(1024) unsigned char k[KSTAGES_PG][TILE_BYTES];
     alignas(1024) unsigned char v[STAGES][TILE_BYTES];
     alignas(8) unsigned long long q_full;
     unsigned long long s_full[2], p_full[2], o_full[2];
-    unsigned long long k_full[STAGES], k_empty[STAGES], v_full[STAGES], v_empty[STAGES];
+    unsigned long long k_full[KSTAGES_PG], k_empty[KSTAGES_PG], v_full[STAGES], v_empty[STAGES];
     unsigned int tmem_base;
     int abort;
 };
@@ -883,10 +884,12 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const Params 
             mbar_init(&sm.p_full[w], 128);
             mbar_init(&sm.o_full[w], 1);
         }
-        for (int s = 0; s < STAGES; ++s) {
-            mbar_init(&sm.k_full[s], 128);
+        for (int s = 0; s < KSTAGES_PG; ++s) {
+            mbar_init(&sm.k_full[s], 64);
             mbar_init(&sm.k_empty[s], 1);
-            mbar_init(&sm.v_full[s], 128);
+        }
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&sm.v_full[s], 64);
             mbar_init(&sm.v_empty[s], 1);
         }
         sm.abort = 0;
@@ -905,57 +908,67 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const Params 
     if (warp >= 12) {
         // ------------------------------------------------------------------ gather producers
         asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+        // Two independent streams: warps 12-13 copy the K tiles, warps 14-15 the V tiles.  Each
+        // stream loops  wait for its stage -> issue the tile's copies -> wait for them -> publish
+        // (fence.proxy.async + arrive by its 64 threads), so K_j is on its way as soon as
+        // Q*K(j-2) has finished and never waits behind a V stage.
         const int tid = threadIdx.x - 384;
-        const int c = tid & 15, rsub = tid >> 4;              // 16-byte chunk of a row, row within a pass
+        const bool v_stream = tid >= 64;
+        const int t64 = tid & 63;
+        const int c = t64 & 15, rsub = t64 >> 4;              // 16-byte chunk of a row, row within a pass (4 rows)
         const int hk = h / (p.H / pg.Hkv);
         const int64_t row_bytes = (int64_t)pg.Hkv * HD * 2;
-        const char* kbase = (const char*)pg.k_cache + (int64_t)hk * HD * 2 + c * 16;
-        const char* vbase = (const char*)pg.v_cache + (int64_t)hk * HD * 2 + c * 16;
+        const char* base = (const char*)(v_stream ? pg.v_cache : pg.k_cache) + (int64_t)hk * HD * 2 + c * 16;
         const uint32_t dst_off = (c >> 3) * SUB_BYTES;
-        auto gather = [&](const char* base, unsigned char* stage, int j) {
-            const uint32_t sbase = smem_u32(stage) + dst_off;
-#pragma unroll 4
-            for (int pass = 0; pass < BN / 8; ++pass) {
-                const int row = pass * 8 + rsub;
-                const int kvpos = j * BN + row;
-                int64_t slot = -1;
-                if (kvpos < kv_len) {
-                    slot = pg.slots[kv_beg + kvpos];
-                    if (slot < 0 || slot >= pg.n_slots) {
-                        if (p.err_flag) atomicOr(p.err_flag, ATTN_B200_FLAG_BAD_SLOT);
-                        slot = -1;
-                    }
-                }
-                const uint32_t dst = sbase + row * 128 + (((c & 7) ^ (row & 7)) << 4);
-                cp_async16(dst, slot >= 0 ? base + slot * row_bytes : base, slot >= 0 ? 16 : 0);
+        unsigned long long* full = v_stream ? sm.v_full : sm.k_full;
+        unsigned long long* empty = v_stream ? sm.v_empty : sm.k_empty;
+        unsigned char (*stage)[TILE_BYTES] = v_stream ? sm.v : sm.k;
+        const int n_stages = v_stream ? STAGES : KSTAGES_PG;
+        // slots of a half tile (16 of this thread's 32 rows), fetched as 16 independent loads: no
+        // atomic (a memory side effect the compiler may not move loads across) inside the loop
+        auto load_slots = [&](int j, int half, int* sl) {
+            bool bad = false;
+#pragma unroll
+            for (int q = 0; q < 16; ++q) {
+                const int kvpos = j * BN + (half * 16 + q) * 4 + rsub;
+                const bool live = j < nmax && kvpos < kv_len;
+                const int v = live ? __ldg(pg.slots + kv_beg + kvpos) : -1;
+                const bool in_range = v >= 0 && v < pg.n_slots;
+                bad |= live && !in_range;
+                sl[q] = in_range ? v : -1;
             }
-            asm volatile("cp.async.commit_group;" ::: "memory");
+            if (bad && p.err_flag) atomicOr(p.err_flag, ATTN_B200_FLAG_BAD_SLOT);
+        };
+        // destination of row (half*16+q)*4 + rsub, chunk c, in the 128-byte-swizzled tile: the row's
+        // low three bits are (q&1)*4 + rsub, so there are only two swizzle terms per thread and
+        // everything else is a compile-time offset: one add per copy on top of the source address
+        const uint32_t swz_even = rsub * 128 + ((((uint32_t)c & 7) ^ (uint32_t)rsub) << 4);
+        const uint32_t swz_odd = rsub * 128 + ((((uint32_t)c & 7) ^ (uint32_t)(4 + rsub)) << 4);
+        auto copy_rows = [&](uint32_t sbase, int half, const int* sl) {
+            const uint32_t be = sbase + swz_even, bo = sbase + swz_odd;
+#pragma unroll
+            for (int q = 0; q < 16; ++q) {
+                const uint32_t dst = ((q & 1) ? bo : be) + (uint32_t)(half * 16 + q) * 512u;
+                cp_async16(dst, base + (int64_t)(sl[q] >= 0 ? sl[q] : 0) * row_bytes, sl[q] >= 0 ? 16 : 0);
+            }
         };
         bool ok = true;
-        int published = 0;
-        for (int j = 0; j < nmax && ok; ++j) {
-            const int s = j & 1;
-            if (j >= 1) {     // publish tile j-1: both of its groups have to land first
-                asm volatile("cp.async.wait_group 0;" ::: "memory");
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                mbar_arrive(&sm.k_full[(j - 1) & 1]);
-                mbar_arrive(&sm.v_full[(j - 1) & 1]);
-                published = j;
+        for (int j = 0; j < nmax; ++j) {
+            const int s = j % n_stages;
+            if (j >= n_stages && !(ok = mbar_wait(&empty[s], ((j - n_stages) / n_stages) & 1, cta_abort, p.err_flag))) break;
+            const uint32_t sbase = smem_u32(stage[s]) + dst_off;
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                int sl[16];
+                load_slots(j, half, sl);
+                copy_rows(sbase, half, sl);
             }
-            if (j >= STAGES) {
-                const uint32_t ph = ((j - STAGES) >> 1) & 1;
-                if (!(ok = mbar_wait(&sm.k_empty[s], ph, cta_abort, p.err_flag))) break;
-                if (!(ok = mbar_wait(&sm.v_empty[s], ph, cta_abort, p.err_flag))) break;
-            }
-            gather(kbase, sm.k[s], j);
-            gather(vbase, sm.v[s], j);
-        }
-        asm volatile("cp.async.wait_group 0;" ::: "memory");     // also the drain when aborting
-        if (ok && published < nmax) {
+            asm volatile("cp.async.commit_group;" ::: "memory");
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            mbar_arrive(&sm.k_full[(nmax - 1) & 1]);
-            mbar_arrive(&sm.v_full[(nmax - 1) & 1]);
+            mbar_arrive(&full[s]);
         }
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
     } else if (warp >= 8) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
         if (warp == 8) {
@@ -976,10 +989,10 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const Params 
             const int nw[2] = {n0, n1};
             if (lane == 0) {
                 const uint64_t qd[2] = {smem_desc(smem_u32(sm.q[0]), 16, 1024), smem_desc(smem_u32(sm.q[1]), 16, 1024)};
-                const uint64_t kd[2] = {smem_desc(smem_u32(sm.k[0]), 16, 1024), smem_desc(smem_u32(sm.k[1]), 16, 1024)};
+                const uint64_t kd[KSTAGES_PG] = {smem_desc(smem_u32(sm.k[0]), 16, 1024), smem_desc(smem_u32(sm.k[1]), 16, 1024)};
                 const uint64_t vd[2] = {smem_desc(smem_u32(sm.v[0]), SUB_BYTES, 1024), smem_desc(smem_u32(sm.v[1]), SUB_BYTES, 1024)};
                 auto issue_qk = [&](int w, int j) {
-                    const uint64_t a = qd[w], b2 = kd[j & 1];
+                    const uint64_t a = qd[w], b2 = kd[j % KSTAGES_PG];
 #pragma unroll
                     for (int kk = 0; kk < HD / 16; ++kk) {
                         const uint32_t off16 = ((kk >> 2) * SUB_BYTES + (kk & 3) * 32) >> 4;
@@ -1012,17 +1025,17 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const Params 
                             if (!(ok = mbar_wait_spin(&sm.p_full[w], j & 1, cta_abort, p.err_flag))) break;
                             if (w == 0 || j >= n0) { if (!(ok = mbar_wait_spin(&sm.v_full[s], ph, cta_abort, p.err_flag))) break; }
                             tc_fence_after();
-                            issue_pv(w, j);
+                            TRACE(2, j, w * 4 + 0); issue_pv(w, j); TRACE(2, j, w * 4 + 1);
                         }
                         if (w == 1) umma_commit(&sm.v_empty[s]);
                         if (j + 1 < nw[w]) {
                             if (w == 0 || j + 1 >= n0) {
-                                if (!(ok = mbar_wait_spin(&sm.k_full[(j + 1) & 1], ((j + 1) >> 1) & 1, cta_abort, p.err_flag))) break;
+                                if (!(ok = mbar_wait_spin(&sm.k_full[(j + 1) % KSTAGES_PG], ((j + 1) / KSTAGES_PG) & 1, cta_abort, p.err_flag))) break;
                             }
                             tc_fence_after();
-                            issue_qk(w, j + 1);
+                            TRACE(2, j, w * 4 + 2); issue_qk(w, j + 1); TRACE(2, j, w * 4 + 3);
                         }
-                        if (w == 1 && j + 1 < nmax) umma_commit(&sm.k_empty[(j + 1) & 1]);
+                        if (w == 1 && j + 1 < nmax) umma_commit(&sm.k_empty[(j + 1) % KSTAGES_PG]);
                     }
                 }
             }
@@ -1192,6 +1205,7 @@ int paged_prefill_tc_launch_impl(const void* q, const void* k_cache, const void*
     cudaError_t e = cudaGetSymbolAddress(&abort_addr, g_abort);
     if (e != cudaSuccess) return (int)e;
     if ((e = cudaMemsetAsync(abort_addr, 0, sizeof(int), st)) != cudaSuccess) return (int)e;
+    zero_tail_kernel<<<64, 256, 0, st>>>(out, q_offsets, B, n_q_tokens, (int64_t)H * HD * 2);
     if (dtype == ATTN_B200_BF16) {
         if ((e = cudaFuncSetAttribute(paged_prefill_tc_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) != cudaSuccess)
             return (int)e;

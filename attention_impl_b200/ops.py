@@ -555,7 +555,8 @@ def paged_prefill_attention(Q, K_cache, V_cache, cache_indices, kv_offsets, q_of
             max_q_len = int(torch.diff(q_offsets, prepend=q_offsets.new_zeros(1)).max().item()) if B else 0
         if max_kv_len is None:
             max_kv_len = int(torch.diff(kv_offsets, prepend=kv_offsets.new_zeros(1)).max().item()) if B else 0
-        O = torch.zeros_like(Q)
+        tc_path = not force_generic and D == 128 and Q.dtype in (torch.float16, torch.bfloat16)
+        O = torch.empty_like(Q) if tc_path else torch.zeros_like(Q)     # the tensor-core path zeroes unused rows itself
         check(lib.attn_b200_paged_prefill(Q.data_ptr(), K_cache.data_ptr(), V_cache.data_ptr(),
                                           cache_indices.data_ptr(), kv_offsets.data_ptr(), q_offsets.data_ptr(),
                                           O.data_ptr(), B, nq, cache_indices.numel(), max_q_len, max_kv_len, H, Hkv, D,
