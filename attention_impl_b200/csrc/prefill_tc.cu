@@ -581,7 +581,7 @@ prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             umma_commit(&sm.o_full[w]);
         };
         // one thread issues everything; it polls without suspending so that it reacts at once
-        if (lane == 0) {
+        if (elect_one()) {
             bool ok = mbar_wait_spin(&sm.q_full, 0, cta_abort, p.err_flag) &&
                       mbar_wait_spin(&sm.k_full[0], 0, cta_abort, p.err_flag);
             if (ok) {
@@ -742,7 +742,7 @@ prefill_tc3_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             constexpr uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
             constexpr uint32_t idesc_qk = (1u << 4) | (fmt << 7) | (fmt << 10) | ((BN >> 3) << 17) | ((BM >> 4) << 24);
             constexpr uint32_t idesc_pv = idesc_qk | (1u << 16);   // B (= V) is MN-major, same type as P
-            if (lane == 0) {
+            if (elect_one()) {
                 const uint64_t qd = smem_desc(smem_u32(sm.q), 16, 1024), kd = smem_desc(smem_u32(sm.k), 16, 1024);
                 const uint64_t vd = smem_desc(smem_u32(sm.v), SUB_BYTES, 1024);
                 auto issue_qk = [&]() {
@@ -987,7 +987,7 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const Params 
             constexpr uint32_t idesc_qk = (1u << 4) | (fmt << 7) | (fmt << 10) | ((BN >> 3) << 17) | ((BM >> 4) << 24);
             constexpr uint32_t idesc_pv = idesc_qk | (1u << 16);
             const int nw[2] = {n0, n1};
-            if (lane == 0) {
+            if (elect_one()) {
                 const uint64_t qd[2] = {smem_desc(smem_u32(sm.q[0]), 16, 1024), smem_desc(smem_u32(sm.q[1]), 16, 1024)};
                 const uint64_t kd[KSTAGES_PG] = {smem_desc(smem_u32(sm.k[0]), 16, 1024), smem_desc(smem_u32(sm.k[1]), 16, 1024)};
                 const uint64_t vd[2] = {smem_desc(smem_u32(sm.v[0]), SUB_BYTES, 1024), smem_desc(smem_u32(sm.v[1]), SUB_BYTES, 1024)};
