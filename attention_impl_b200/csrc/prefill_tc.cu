@@ -300,7 +300,7 @@ struct SmemLayout2 {
     alignas(1024) unsigned char k[STAGES][TILE_BYTES];
     alignas(1024) unsigned char v[STAGES][TILE_BYTES];
     alignas(8) unsigned long long q_full;
-    unsigned long long s_full[2], p_full[2], o_full[2];
+    unsigned long long s_full[2], p_half[2], p_full[2], o_full[2];
     unsigned long long k_full[STAGES], k_empty[STAGES], v_full[STAGES], v_empty[STAGES];
     unsigned int tmem_base;
     int abort;
@@ -311,8 +311,9 @@ struct SmemLayout2 {
 // P in place, keeps the running maximum lazily, and writes the normalised output row at the end.
 // `qpos` is the row's position in key coordinates (keys 0..qpos are visible): its index within the
 // sequence for the packed prefill, kv_len - q_len + index for a chunk over a cached prefix.
-template <typename T>
-__device__ __forceinline__ void softmax_row(unsigned long long* s_full, unsigned long long* p_full,
+template <typename T, int kPolyOf8>
+__device__ __forceinline__ void softmax_row(unsigned long long* s_full, unsigned long long* p_half,
+                                            unsigned long long* p_full,
                                             unsigned long long* o_full, uint32_t s_addr, uint32_t o_addr, int nk,
                                             int qpos, int r, int trace_role, const Params& p, volatile int* cta_abort,
                                             bool row_valid, int64_t out_row, int h) {
@@ -394,6 +395,11 @@ __device__ __forceinline__ void softmax_row(unsigned long long* s_full, unsigned
                         hs[g] = (c == 0 && i < 16) ? eh : __hadd2(hs[g], eh);
                     }
                     tmem_st32(s_addr + c * 32, pk);
+                    if (c == 0 && p_half) {      // keys 0..63 of P are in place: their P.V steps may start
+                        tmem_st_wait();
+                        tc_fence_before();
+                        mbar_arrive(p_half);
+                    }
                 }
 #pragma unroll
                 for (int g = 0; g < 8; g += 2) {
@@ -401,10 +407,11 @@ __device__ __forceinline__ void softmax_row(unsigned long long* s_full, unsigned
                     rs += (a.x + a.y) + (b2.x + b2.y);
                 }
             } else {
-                // bf16 inputs: fp32 ex2, the remaining fp32 arithmetic as packed pairs (f32x2).
-                // Moving a share of the exponentials to a polynomial on the FMA pipe was measured
-                // (50 %, 25 %, 12.5 % of the elements): slower each time, the softmax warp is bound
-                // by instruction issue, not by the special-function unit.
+                // bf16 inputs: fp32 ex2, the remaining fp32 arithmetic as packed pairs (f32x2).  A
+                // warp's 128 exponentials occupy the special-function unit for 1024 clocks (4 lanes
+                // per clock per scheduler), so kPolyOf8 of every 8 elements take a cubic on the
+                // FMA pipe instead (2 where the schedulers have slots to spare, 0 in the paged kernel,
+                // whose gather warps share them).
                 float rs4[4] = {0.f, 0.f, 0.f, 0.f};
                 const float nm = -m_ref;
 #pragma unroll
@@ -417,14 +424,23 @@ __device__ __forceinline__ void softmax_row(unsigned long long* s_full, unsigned
                         fma2(x2, x3, sv[c * 64 + i + 2], sv[c * 64 + i + 3], p.scale_log2, p.scale_log2, nm, nm);
                         p0 = fast_exp2(x0);
                         p1 = fast_exp2(x1);
-                        p2 = fast_exp2(x2);
-                        p3 = fast_exp2(x3);
+                        if (kPolyOf8 == 4 || (kPolyOf8 == 2 && (i & 4)) || (kPolyOf8 == 1 && (i & 12) == 12)) {
+                            exp2_poly2(p2, p3, x2, x3);
+                        } else {
+                            p2 = fast_exp2(x2);
+                            p3 = fast_exp2(x3);
+                        }
                         add2(rs4[0], rs4[1], rs4[0], rs4[1], p0, p1);
                         add2(rs4[2], rs4[3], rs4[2], rs4[3], p2, p3);
                         pk[i >> 1] = pack2<T>(p0, p1);
                         pk[(i >> 1) + 1] = pack2<T>(p2, p3);
                     }
                     tmem_st32(s_addr + c * 32, pk);
+                    if (c == 0 && p_half) {
+                        tmem_st_wait();
+                        tc_fence_before();
+                        mbar_arrive(p_half);
+                    }
                 }
                 rs = (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
             }
@@ -495,6 +511,7 @@ prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         mbar_init(&sm.q_full, 1);
         for (int w = 0; w < 2; ++w) {
             mbar_init(&sm.s_full[w], 1);
+            mbar_init(&sm.p_half[w], 128);
             mbar_init(&sm.p_full[w], 128);
             mbar_init(&sm.o_full[w], 1);
         }
@@ -571,14 +588,17 @@ prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             }
             umma_commit(&sm.s_full[w]);
         };
-        auto issue_pv = [&](int w, int j) {      // O_w (+)= P_w V_j, P_w in the first 64 columns of S_w
+        // O_w (+)= P_w V_j, P_w in the first 64 columns of S_w; issued in two halves of 64 keys, the
+        // first as soon as the softmax threads have stored that half of P
+        auto issue_pv = [&](int w, int j, int half) {
             const uint64_t b2 = vd[j & 1];
             const uint32_t d = tmem + 256 + w * 128, a = tmem + w * 128;
-            umma_f16_ts(d, a, b2, idesc_pv, j > 0 ? 1u : 0u);
 #pragma unroll
-            for (int kk = 1; kk < BN / 16; ++kk)
-                umma_f16_ts(d, a + kk * 8, b2 + ((kk * 2048) >> 4), idesc_pv, 1u);
-            umma_commit(&sm.o_full[w]);
+            for (int k4 = 0; k4 < BN / 32; ++k4) {
+                const int kk = half * (BN / 32) + k4;
+                umma_f16_ts(d, a + kk * 8, b2 + ((kk * 2048) >> 4), idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+            }
+            if (half) umma_commit(&sm.o_full[w]);
         };
         // one thread issues everything; it polls without suspending so that it reacts at once
         if (elect_one()) {
@@ -595,10 +615,13 @@ prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 const uint32_t ph = (j >> 1) & 1;
                 for (int w = 0; w < 2 && ok; ++w) {
                     if (j < nw[w]) {
-                        if (!(ok = mbar_wait_spin(&sm.p_full[w], j & 1, cta_abort, p.err_flag))) break;
+                        if (!(ok = mbar_wait_spin(&sm.p_half[w], j & 1, cta_abort, p.err_flag))) break;
                         if (w == 0 || j >= n0) { if (!(ok = mbar_wait_spin(&sm.v_full[s], ph, cta_abort, p.err_flag))) break; }
                         tc_fence_after();
-                        TRACE(2, j, w * 4 + 0); issue_pv(w, j); TRACE(2, j, w * 4 + 1);
+                        TRACE(2, j, w * 4 + 0); issue_pv(w, j, 0);
+                        if (!(ok = mbar_wait_spin(&sm.p_full[w], j & 1, cta_abort, p.err_flag))) break;
+                        tc_fence_after();
+                        issue_pv(w, j, 1); TRACE(2, j, w * 4 + 1);
                     }
                     if (w == 1) umma_commit(&sm.v_empty[s]);
                     if (j + 1 < nw[w]) {
@@ -623,8 +646,8 @@ prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         const int tq = 2 * tp + w;                        // query tile index == index of its diagonal key tile
         const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
         const uint32_t s_addr = lane_base + w * 128, o_addr = lane_base + 256 + w * 128;
-        softmax_row<T>(&sm.s_full[w], &sm.p_full[w], &sm.o_full[w], s_addr, o_addr, nk, tq * BM + r, r, w, p, cta_abort,
-                       q0 + w * BM + r < L, seq_beg + q0 + w * BM + r, h);
+        softmax_row<T, 2>(&sm.s_full[w], &sm.p_half[w], &sm.p_full[w], &sm.o_full[w], s_addr, o_addr, nk, tq * BM + r, r, w, p,
+                       cta_abort, q0 + w * BM + r < L, seq_beg + q0 + w * BM + r, h);
     }
     // ---------------------------------------------------------------------- teardown
     if (warp == 8 && lane == 0 && sm.abort) {
@@ -784,7 +807,7 @@ prefill_tc3_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         asm volatile("setmaxnreg.inc.sync.aligned.u32 200;");
         const int r = threadIdx.x;
         const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
-        softmax_row<T>(&sm.s_full, &sm.p_full, &sm.o_full, lane_base, lane_base + 128, n_kv, t * BM + r, r, 0, p, cta_abort,
+        softmax_row<T, 2>(&sm.s_full, nullptr, &sm.p_full, &sm.o_full, lane_base, lane_base + 128, n_kv, t * BM + r, r, 0, p, cta_abort,
                        q0 + r < L, seq_beg + q0 + r, h);
     }
     // ---------------------------------------------------------------------- teardown
@@ -835,7 +858,7 @@ struct SmemLayoutPg {
     alignas(1024) unsigned char k[KSTAGES_PG][TILE_BYTES];
     alignas(1024) unsigned char v[STAGES][TILE_BYTES];
     alignas(8) unsigned long long q_full;
-    unsigned long long s_full[2], p_full[2], o_full[2];
+    unsigned long long s_full[2], p_half[2], p_full[2], o_full[2];
     unsigned long long k_full[KSTAGES_PG], k_empty[KSTAGES_PG], v_full[STAGES], v_empty[STAGES];
     unsigned int tmem_base;
     int abort;
@@ -881,6 +904,7 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const Params 
         mbar_init(&sm.q_full, 1);
         for (int w = 0; w < 2; ++w) {
             mbar_init(&sm.s_full[w], 1);
+            mbar_init(&sm.p_half[w], 128);
             mbar_init(&sm.p_full[w], 128);
             mbar_init(&sm.o_full[w], 1);
         }
@@ -1000,14 +1024,15 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const Params 
                     }
                     umma_commit(&sm.s_full[w]);
                 };
-                auto issue_pv = [&](int w, int j) {
+                auto issue_pv = [&](int w, int j, int half) {
                     const uint64_t b2 = vd[j & 1];
                     const uint32_t d = tmem + 256 + w * 128, a = tmem + w * 128;
-                    umma_f16_ts(d, a, b2, idesc_pv, j > 0 ? 1u : 0u);
 #pragma unroll
-                    for (int kk = 1; kk < BN / 16; ++kk)
-                        umma_f16_ts(d, a + kk * 8, b2 + ((kk * 2048) >> 4), idesc_pv, 1u);
-                    umma_commit(&sm.o_full[w]);
+                    for (int k4 = 0; k4 < BN / 32; ++k4) {
+                        const int kk = half * (BN / 32) + k4;
+                        umma_f16_ts(d, a + kk * 8, b2 + ((kk * 2048) >> 4), idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+                    }
+                    if (half) umma_commit(&sm.o_full[w]);
                 };
                 bool ok = mbar_wait_spin(&sm.q_full, 0, cta_abort, p.err_flag) &&
                           mbar_wait_spin(&sm.k_full[0], 0, cta_abort, p.err_flag);
@@ -1022,10 +1047,13 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const Params 
                     const uint32_t ph = (j >> 1) & 1;
                     for (int w = 0; w < 2 && ok; ++w) {
                         if (j < nw[w]) {
-                            if (!(ok = mbar_wait_spin(&sm.p_full[w], j & 1, cta_abort, p.err_flag))) break;
+                            if (!(ok = mbar_wait_spin(&sm.p_half[w], j & 1, cta_abort, p.err_flag))) break;
                             if (w == 0 || j >= n0) { if (!(ok = mbar_wait_spin(&sm.v_full[s], ph, cta_abort, p.err_flag))) break; }
                             tc_fence_after();
-                            TRACE(2, j, w * 4 + 0); issue_pv(w, j); TRACE(2, j, w * 4 + 1);
+                            TRACE(2, j, w * 4 + 0); issue_pv(w, j, 0);
+                            if (!(ok = mbar_wait_spin(&sm.p_full[w], j & 1, cta_abort, p.err_flag))) break;
+                            tc_fence_after();
+                            issue_pv(w, j, 1); TRACE(2, j, w * 4 + 1);
                         }
                         if (w == 1) umma_commit(&sm.v_empty[s]);
                         if (j + 1 < nw[w]) {
@@ -1049,7 +1077,7 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const Params 
         const int nk = w ? n1 : n0;
         const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
         const int qi = q0 + w * BM + r;                    // row within the chunk
-        softmax_row<T>(&sm.s_full[w], &sm.p_full[w], &sm.o_full[w], lane_base + w * 128, lane_base + 256 + w * 128,
+        softmax_row<T, 0>(&sm.s_full[w], &sm.p_half[w], &sm.p_full[w], &sm.o_full[w], lane_base + w * 128, lane_base + 256 + w * 128,
                        nk, shift + qi, r, w, p, cta_abort, qi < q_len, q_beg + qi, h);
     }
     // ---------------------------------------------------------------------- teardown

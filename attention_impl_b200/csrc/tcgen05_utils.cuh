@@ -167,6 +167,24 @@ __device__ __forceinline__ void add2(float& d0, float& d1, float a0, float a1, f
         "add.rn.f32x2 rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"
         : "=f"(d0), "=f"(d1) : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
 }
+// 2^x for two values on the FMA pipe (no special-function unit): round x to the nearest integer j
+// with the 1.5*2^23 trick, evaluate a cubic for 2^(x-j) on [-0.5, 0.5] (relative error 7.5e-5, far
+// below the rounding of a bf16 result) and add j to the exponent field.  x is clamped at -125 so
+// that the exponent arithmetic cannot wrap (the result there is ~2e-38 instead of 0).
+__device__ __forceinline__ void exp2_poly2(float& p0, float& p1, float x0, float x1) {
+    constexpr float kMagic = 12582912.f;
+    x0 = fmaxf(x0, -125.f);
+    x1 = fmaxf(x1, -125.f);
+    float t0, t1, j0, j1, f0, f1, q0, q1;
+    add2(t0, t1, x0, x1, kMagic, kMagic);
+    add2(j0, j1, t0, t1, -kMagic, -kMagic);
+    fma2(f0, f1, j0, j1, -1.f, -1.f, x0, x1);
+    fma2(q0, q1, f0, f1, 0.0551716648f, 0.0551716648f, 0.2426111251f, 0.2426111251f);
+    fma2(q0, q1, q0, q1, f0, f1, 0.6932609677f, 0.6932609677f);
+    fma2(q0, q1, q0, q1, f0, f1, 0.9999280572f, 0.9999280572f);
+    p0 = __int_as_float(__float_as_int(q0) + (__float_as_int(t0) << 23));
+    p1 = __int_as_float(__float_as_int(q1) + (__float_as_int(t1) << 23));
+}
 __device__ __forceinline__ float max3(float a, float b, float c) {
     float d;
     asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
