@@ -20,6 +20,7 @@
 // wait, TMEM is freed and the CTA returns.  CTAs that start after a timeout exit at once.
 #include <cuda.h>
 #include <cstdlib>
+#include <atomic>
 #include <mutex>
 #include <type_traits>
 
@@ -316,7 +317,11 @@ __device__ __forceinline__ void softmax_row(unsigned long long* s_full, unsigned
                                             unsigned long long* p_full,
                                             unsigned long long* o_full, uint32_t s_addr, uint32_t o_addr, int nk,
                                             int qpos, int r, int trace_role, const Params& p, volatile int* cta_abort,
-                                            bool row_valid, int64_t out_row, int h) {
+                                            bool row_valid, int64_t out_row, int h, int c0 = 0,
+                                            unsigned long long* o_free = nullptr) {
+    // c0: tiles this warpgroup has processed before this call (persistent kernels keep their
+    // barriers across work items, so the phase of tile j is (c0 + j) & 1); o_free, if given, is
+    // signalled once the accumulator has been read out and may be overwritten by the next item.
     {
         float m_ref = -INFINITY, l = 0.f;
         // P <= 2^kLazy.  On the fp16 path the exponent argument passes through fp16: keeping it
@@ -325,7 +330,7 @@ __device__ __forceinline__ void softmax_row(unsigned long long* s_full, unsigned
         bool ok = true;
         for (int j = 0; j < nk; ++j) {
             if (r == 0) TRACE(trace_role, j, 0);
-            if (!(ok = mbar_wait(s_full, j & 1, cta_abort, p.err_flag))) break;
+            if (!(ok = mbar_wait(s_full, (c0 + j) & 1, cta_abort, p.err_flag))) break;
             tc_fence_after();
             if (r == 0) TRACE(trace_role, j, 1);
             float sv[BN];
@@ -357,7 +362,7 @@ __device__ __forceinline__ void softmax_row(unsigned long long* s_full, unsigned
                 if (j > 0) {
                     const float alpha = fast_exp2(m_ref - m_new);
                     l *= alpha;
-                    if (!(ok = mbar_wait(o_full, (j - 1) & 1, cta_abort, p.err_flag))) break;
+                    if (!(ok = mbar_wait(o_full, (c0 + j - 1) & 1, cta_abort, p.err_flag))) break;
                     tc_fence_after();
 #pragma unroll
                     for (int c = 0; c < 4; ++c) {
@@ -451,7 +456,7 @@ __device__ __forceinline__ void softmax_row(unsigned long long* s_full, unsigned
             mbar_arrive(p_full);
             if (r == 0) TRACE(trace_role, j, 5);
         }
-        if (ok && nk > 0) ok = mbar_wait(o_full, (nk - 1) & 1, cta_abort, p.err_flag);
+        if (ok && nk > 0) ok = mbar_wait(o_full, (c0 + nk - 1) & 1, cta_abort, p.err_flag);
         if (ok && nk > 0) {
             tc_fence_after();
             const bool valid = row_valid;
@@ -461,6 +466,10 @@ __device__ __forceinline__ void softmax_row(unsigned long long* s_full, unsigned
             for (int c = 0; c < 4; ++c) {
                 float ov[32];
                 tmem_ld32(o_addr + c * 32, ov);
+                if (c == 3 && o_free) {        // the accumulator is in registers: the next item may overwrite it
+                    tc_fence_before();
+                    mbar_arrive(o_free);
+                }
                 if (!valid) continue;
                 if (p.out_f32) {
                     float4* dst = reinterpret_cast<float4*>((float*)p.out + (row * p.H + h) * HD + c * 32);
@@ -668,6 +677,297 @@ prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 
 
 // =============================================================================================
+// Persistent form of version 2.
+//
+// Version 2 spends about two of a CTA's ~ten key-tile periods outside its steady state: barrier
+// and tensor-memory set-up, the first TMA round trip and the first Q.K before any softmax can run,
+// and the read-out of O at the end.  Here the grid is one CTA per SM and every CTA walks a list of
+// work items (a pair of query tiles of one (sequence, head)), heaviest pairs first, handed out by an
+// atomic counter: the producer thread draws the next non-empty item and publishes it to the other
+// roles through a 4-deep ring in shared memory (no role can be more than two items behind the
+// producer, see the ring's comment).  Barriers, tensor memory and the K/V rings live across
+// items: each role keeps running counters for the barrier phases.  The producer fetches the next
+// item's Q tiles as soon as the last Q.K of the current item has completed (q_empty) and its first
+// K/V tiles as the ring frees, so the next item's first S tiles are computed while the softmax
+// warpgroups are still reading out O; the only new dependency is o_free (the accumulator of a
+// warpgroup has been read out before the next item's first P.V overwrites it).
+// =============================================================================================
+static __device__ unsigned long long g_work[64];   // work counters of the persistent kernel, one slot per launch in flight
+
+struct SmemLayout2p {
+    alignas(1024) unsigned char q[2][TILE_BYTES];
+    alignas(1024) unsigned char k[STAGES][TILE_BYTES];
+    alignas(1024) unsigned char v[STAGES][TILE_BYTES];
+    alignas(8) unsigned long long q_full, q_empty;
+    // item_id[n & 3] = n-th item of this CTA (-1: no more work), published by the producer.  The
+    // producer draws item n only after it has issued every K/V tile of item n-1, i.e. after the
+    // MMA thread and the softmax threads have entered item n-1; slot n & 3 was last read at the
+    // start of item n-4, so it is free.
+    unsigned long long item_full[4];
+    long long item_id[4];
+    unsigned long long s_full[2], p_half[2], p_full[2], o_full[2], o_free[2];
+    unsigned long long k_full[STAGES], k_empty[STAGES], v_full[STAGES], v_empty[STAGES];
+    unsigned int tmem_base;
+    int abort;
+};
+
+// Work item -> (pair index, head, sequence).  (sequence, head) combinations are taken in groups of
+// ITEM_GROUP; inside a group the pair index is the slowest coordinate, so the heaviest pairs of the
+// group come first while the CTAs running at any moment share the K/V of a few dozen (sequence,
+// head) combinations, which stay in L2 (with the pair index slowest over ALL combinations every CTA
+// would stream its own K/V from DRAM).
+#ifndef ATTN_B200_ITEM_GROUP
+#define ATTN_B200_ITEM_GROUP 16
+#endif
+constexpr int ITEM_GROUP = ATTN_B200_ITEM_GROUP;
+struct Item2p {
+    int tp, h, b, L, q0, n0, n1, nmax;
+    int64_t seq_beg;
+    bool valid;
+};
+__device__ __forceinline__ Item2p decode_item(const Params& p, int64_t id) {
+    Item2p it;
+    const int per_group = p.n_qtiles * ITEM_GROUP;
+    const int grp = (int)(id / per_group), r = (int)(id - (int64_t)grp * per_group);
+    const int x = r / ITEM_GROUP, hb = grp * ITEM_GROUP + (r - x * ITEM_GROUP);
+    it.tp = p.n_qtiles - 1 - x;
+    it.valid = true;
+    if (hb >= p.H * p.B) {          // padding of the last group: an empty item
+        it.L = 0; it.q0 = 1; it.b = it.h = 0; it.n0 = it.n1 = it.nmax = 0; it.seq_beg = 0;
+        return it;
+    }
+    it.b = hb / p.H;
+    it.h = hb - it.b * p.H;
+    it.seq_beg = it.b ? p.offsets[it.b - 1] : 0;
+    const int64_t seq_end = p.offsets[it.b];
+    it.valid = !(it.seq_beg < 0 || seq_end < it.seq_beg || seq_end > p.n_tokens);
+    it.L = it.valid ? (int)(seq_end - it.seq_beg) : 0;
+    it.q0 = it.tp * 2 * BM;
+    it.n0 = 2 * it.tp + 1;
+    it.n1 = (it.q0 + BM < it.L) ? 2 * it.tp + 2 : 0;
+    it.nmax = it.n1 > it.n0 ? it.n1 : it.n0;
+    return it;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(THREADS2, 1)
+prefill_tc2p_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                    const __grid_constant__ CUtensorMap map_v, const Params p, const int64_t n_items,
+                    unsigned long long* work_counter) {
+    extern __shared__ unsigned char smem_raw[];
+    SmemLayout2p& sm = *reinterpret_cast<SmemLayout2p*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (*(volatile int*)&g_abort) return;
+    volatile int* cta_abort = &sm.abort;
+
+    if (threadIdx.x == 0) {
+        mbar_init(&sm.q_full, 1);
+        mbar_init(&sm.q_empty, 1);
+        for (int i = 0; i < 4; ++i) mbar_init(&sm.item_full[i], 1);
+        for (int w = 0; w < 2; ++w) {
+            mbar_init(&sm.s_full[w], 1);
+            mbar_init(&sm.p_half[w], 128);
+            mbar_init(&sm.p_full[w], 128);
+            mbar_init(&sm.o_full[w], 1);
+            mbar_init(&sm.o_free[w], 128);
+        }
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&sm.k_full[s], 1);
+            mbar_init(&sm.k_empty[s], 1);
+            mbar_init(&sm.v_full[s], 1);
+            mbar_init(&sm.v_empty[s], 1);
+        }
+        sm.abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 9) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(512));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = sm.tmem_base;
+
+    // producer bookkeeping for the drain on abort: tiles issued in total, Q loads issued in total
+    int g_issued_k = 0, g_issued_v = 0, q_issued = 0;
+    if (warp >= 8) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+    if (warp == 8) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            int g = 0;        // key tiles issued so far (all items): ring stage g & 1, use (g >> 1)
+            int n_it = 0;     // non-empty items so far
+            bool ok = true;
+            while (ok) {
+                // draw the next non-empty item (empty ones: pairs past the end of a short sequence)
+                Item2p it;
+                long long id;
+                do {
+                    id = (long long)atomicAdd(work_counter, 1ull);
+                    if (id >= n_items) { id = -1; break; }
+                    it = decode_item(p, id);
+                    if (!it.valid && p.err_flag) atomicOr(p.err_flag, ATTN_B200_FLAG_BAD_OFFSETS);
+                } while (!it.valid || it.q0 >= it.L);
+                sm.item_id[n_it & 3] = id;
+                mbar_arrive(&sm.item_full[n_it & 3]);
+                if (id < 0) break;
+                const int col0 = it.h * HD;
+                if (n_it > 0 && !(ok = mbar_wait(&sm.q_empty, (n_it - 1) & 1, cta_abort, p.err_flag))) break;
+                mbar_expect_tx(&sm.q_full, 2 * TILE_BYTES);
+                for (int w = 0; w < 2; ++w) {
+                    tma_load_2d(sm.q[w], &map_q, col0, (int)(it.seq_beg + it.q0 + w * BM), &sm.q_full);
+                    tma_load_2d(sm.q[w] + SUB_BYTES, &map_q, col0 + 64, (int)(it.seq_beg + it.q0 + w * BM), &sm.q_full);
+                }
+                ++q_issued;
+                for (int j = 0; j < it.nmax; ++j, ++g) {
+                    const int s = g & 1;
+                    const uint32_t ph = ((g - STAGES) >> 1) & 1;
+                    const int row = (int)(it.seq_beg + (int64_t)j * BN);
+                    if (g >= STAGES && !(ok = mbar_wait(&sm.k_empty[s], ph, cta_abort, p.err_flag))) break;
+                    mbar_expect_tx(&sm.k_full[s], TILE_BYTES);
+                    tma_load_2d(sm.k[s], &map_k, col0, row, &sm.k_full[s]);
+                    tma_load_2d(sm.k[s] + SUB_BYTES, &map_k, col0 + 64, row, &sm.k_full[s]);
+                    g_issued_k = g + 1;
+                    if (g >= STAGES && !(ok = mbar_wait(&sm.v_empty[s], ph, cta_abort, p.err_flag))) break;
+                    mbar_expect_tx(&sm.v_full[s], TILE_BYTES);
+                    tma_load_2d(sm.v[s], &map_v, col0, row, &sm.v_full[s]);
+                    tma_load_2d(sm.v[s] + SUB_BYTES, &map_v, col0 + 64, row, &sm.v_full[s]);
+                    g_issued_v = g + 1;
+                }
+                ++n_it;
+            }
+        }
+    } else if (warp == 9) {
+        // ------------------------------------------------------------------ MMA issuer
+        constexpr uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
+        constexpr uint32_t idesc_qk = (1u << 4) | (fmt << 7) | (fmt << 10) | ((BN >> 3) << 17) | ((BM >> 4) << 24);
+        constexpr uint32_t idesc_pv = idesc_qk | (1u << 16);
+        if (elect_one()) {
+            const uint64_t qd[2] = {smem_desc(smem_u32(sm.q[0]), 16, 1024), smem_desc(smem_u32(sm.q[1]), 16, 1024)};
+            const uint64_t kd[2] = {smem_desc(smem_u32(sm.k[0]), 16, 1024), smem_desc(smem_u32(sm.k[1]), 16, 1024)};
+            const uint64_t vd[2] = {smem_desc(smem_u32(sm.v[0]), SUB_BYTES, 1024), smem_desc(smem_u32(sm.v[1]), SUB_BYTES, 1024)};
+            auto issue_qk = [&](int w, int stage) {      // S_w = Q_w K^T, K in ring stage `stage`
+                const uint64_t a = qd[w], b2 = kd[stage];
+                const uint32_t d = tmem + w * 128;
+#pragma unroll
+                for (int kk = 0; kk < HD / 16; ++kk) {
+                    const uint32_t off16 = ((kk >> 2) * SUB_BYTES + (kk & 3) * 32) >> 4;
+                    umma_f16(d, a + off16, b2 + off16, idesc_qk, kk > 0);
+                }
+                umma_commit(&sm.s_full[w]);
+            };
+            auto issue_pv = [&](int w, int stage, int half, bool first) {   // O_w (+)= P_w V, 64 keys per call
+                const uint64_t b2 = vd[stage];
+                const uint32_t d = tmem + 256 + w * 128, a = tmem + w * 128;
+#pragma unroll
+                for (int k4 = 0; k4 < BN / 32; ++k4) {
+                    const int kk = half * (BN / 32) + k4;
+                    umma_f16_ts(d, a + kk * 8, b2 + ((kk * 2048) >> 4), idesc_pv, (!first || kk > 0) ? 1u : 0u);
+                }
+                if (half) umma_commit(&sm.o_full[w]);
+            };
+            int g = 0, n_it = 0;
+            int c[2] = {0, 0};        // tiles processed per warpgroup (phase of s_full / p_half / p_full / o_full)
+            int uses[2] = {0, 0};     // items in which the warpgroup had work (phase of o_free)
+            bool ok = true;
+            while (ok) {
+                if (!(ok = mbar_wait_spin(&sm.item_full[n_it & 3], (n_it >> 2) & 1, cta_abort, p.err_flag))) break;
+                const long long id = sm.item_id[n_it & 3];
+                if (id < 0) break;
+                const Item2p it = decode_item(p, id);
+                const int nw[2] = {it.n0, it.n1};
+                if (!(ok = mbar_wait_spin(&sm.q_full, n_it & 1, cta_abort, p.err_flag))) break;
+                if (!(ok = mbar_wait_spin(&sm.k_full[g & 1], (g >> 1) & 1, cta_abort, p.err_flag))) break;
+                tc_fence_after();
+                issue_qk(0, g & 1);
+                if (it.n1 > 0) issue_qk(1, g & 1);
+                umma_commit(&sm.k_empty[g & 1]);
+                if (it.nmax == 1) umma_commit(&sm.q_empty);
+                for (int j = 0; ok && j < it.nmax; ++j) {
+                    const int s = (g + j) & 1;
+                    const uint32_t ph = ((g + j) >> 1) & 1;
+                    for (int w = 0; w < 2 && ok; ++w) {
+                        if (j < nw[w]) {
+                            if (j == 0 && uses[w] > 0) {     // the previous item's O must have been read out
+                                if (!(ok = mbar_wait_spin(&sm.o_free[w], (uses[w] - 1) & 1, cta_abort, p.err_flag))) break;
+                            }
+                            if (!(ok = mbar_wait_spin(&sm.p_half[w], (c[w] + j) & 1, cta_abort, p.err_flag))) break;
+                            if (w == 0 || j >= it.n0) { if (!(ok = mbar_wait_spin(&sm.v_full[s], ph, cta_abort, p.err_flag))) break; }
+                            tc_fence_after();
+                            issue_pv(w, s, 0, j == 0);
+                            if (!(ok = mbar_wait_spin(&sm.p_full[w], (c[w] + j) & 1, cta_abort, p.err_flag))) break;
+                            tc_fence_after();
+                            issue_pv(w, s, 1, j == 0);
+                        }
+                        if (w == 1) umma_commit(&sm.v_empty[s]);
+                        if (j + 1 < nw[w]) {
+                            const int s1 = (g + j + 1) & 1;
+                            if (w == 0 || j + 1 >= it.n0) {
+                                if (!(ok = mbar_wait_spin(&sm.k_full[s1], ((g + j + 1) >> 1) & 1, cta_abort, p.err_flag))) break;
+                            }
+                            tc_fence_after();
+                            issue_qk(w, s1);
+                        }
+                        if (w == 1 && j + 1 < it.nmax) {
+                            umma_commit(&sm.k_empty[(g + j + 1) & 1]);
+                            if (j + 2 == it.nmax) umma_commit(&sm.q_empty);     // last Q.K of the item issued
+                        }
+                    }
+                }
+                for (int w = 0; w < 2; ++w) {
+                    c[w] += nw[w];
+                    uses[w] += nw[w] > 0;
+                }
+                g += it.nmax;
+                ++n_it;
+            }
+        }
+        __syncwarp();
+    }
+    } else {
+        // ------------------------------------------------------------------ softmax warpgroups
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
+        const int w = warp >> 2;
+        const int r = threadIdx.x & 127;
+        const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+        const uint32_t s_addr = lane_base + w * 128, o_addr = lane_base + 256 + w * 128;
+        int c0 = 0;
+        for (int n_it = 0;; ++n_it) {
+            if (!mbar_wait(&sm.item_full[n_it & 3], (n_it >> 2) & 1, cta_abort, p.err_flag)) break;
+            const long long id = sm.item_id[n_it & 3];
+            if (id < 0) break;
+            const Item2p it = decode_item(p, id);
+            if (*cta_abort) break;
+            const int nk = w ? it.n1 : it.n0;
+            const int tq = 2 * it.tp + w;
+            softmax_row<T, 2>(&sm.s_full[w], &sm.p_half[w], &sm.p_full[w], &sm.o_full[w], s_addr, o_addr, nk, tq * BM + r, r, w, p,
+                              cta_abort, it.q0 + w * BM + r < it.L, it.seq_beg + it.q0 + w * BM + r, it.h, c0,
+                              nk > 0 ? &sm.o_free[w] : nullptr);
+            c0 += nk;
+        }
+    }
+    // ---------------------------------------------------------------------- teardown
+    if (warp == 8 && lane == 0 && sm.abort) {
+        // give the copies still in flight a bounded time to land before shared memory is released
+        const long long t0 = clock64();
+        if (q_issued > 0) while (!mbar_try(&sm.q_full, (q_issued - 1) & 1) && clock64() - t0 < WAIT_CYCLES) {}
+        for (int gg = g_issued_k > STAGES ? g_issued_k - STAGES : 0; gg < g_issued_k; ++gg)
+            while (!mbar_try(&sm.k_full[gg & 1], (gg >> 1) & 1) && clock64() - t0 < WAIT_CYCLES) {}
+        for (int gg = g_issued_v > STAGES ? g_issued_v - STAGES : 0; gg < g_issued_v; ++gg)
+            while (!mbar_try(&sm.v_full[gg & 1], (gg >> 1) & 1) && clock64() - t0 < WAIT_CYCLES) {}
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 9) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512));
+    }
+}
+
+
+// =============================================================================================
 // Version 3: one 128-row query tile per CTA, TWO CTAs per SM.
 //
 // Same tensor-memory pipeline as version 2 (S -> P in place, O accumulated by the MMA, lazy
@@ -688,7 +988,7 @@ struct SmemLayout3 {
     alignas(1024) unsigned char q[TILE_BYTES];
     alignas(1024) unsigned char k[TILE_BYTES];
     alignas(1024) unsigned char v[TILE_BYTES];
-    alignas(8) unsigned long long q_full, s_full, p_full, o_full, k_full, k_empty, v_full, v_empty;
+    alignas(8) unsigned long long q_full, s_full, p_half, p_full, o_full, k_full, k_empty, v_full, v_empty;
     unsigned int tmem_base;
     int abort;
 };
@@ -719,6 +1019,7 @@ prefill_tc3_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     if (threadIdx.x == 0) {
         mbar_init(&sm.q_full, 1);
         mbar_init(&sm.s_full, 1);
+        mbar_init(&sm.p_half, 128);
         mbar_init(&sm.p_full, 128);
         mbar_init(&sm.o_full, 1);
         mbar_init(&sm.k_full, 1);
@@ -784,12 +1085,17 @@ prefill_tc3_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                     issue_qk();
                 }
                 for (int j = 0; ok && j < n_kv; ++j) {
-                    if (!(ok = mbar_wait_spin(&sm.p_full, j & 1, cta_abort, p.err_flag))) break;
+                    if (!(ok = mbar_wait_spin(&sm.p_half, j & 1, cta_abort, p.err_flag))) break;
                     if (!(ok = mbar_wait_spin(&sm.v_full, j & 1, cta_abort, p.err_flag))) break;
                     tc_fence_after();
                     umma_f16_ts(tmem + 128, tmem, vd, idesc_pv, j > 0 ? 1u : 0u);
 #pragma unroll
-                    for (int kk = 1; kk < BN / 16; ++kk)
+                    for (int kk = 1; kk < BN / 32; ++kk)
+                        umma_f16_ts(tmem + 128, tmem + kk * 8, vd + ((kk * 2048) >> 4), idesc_pv, 1u);
+                    if (!(ok = mbar_wait_spin(&sm.p_full, j & 1, cta_abort, p.err_flag))) break;
+                    tc_fence_after();
+#pragma unroll
+                    for (int kk = BN / 32; kk < BN / 16; ++kk)
                         umma_f16_ts(tmem + 128, tmem + kk * 8, vd + ((kk * 2048) >> 4), idesc_pv, 1u);
                     umma_commit(&sm.o_full);
                     umma_commit(&sm.v_empty);
@@ -807,7 +1113,7 @@ prefill_tc3_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         asm volatile("setmaxnreg.inc.sync.aligned.u32 200;");
         const int r = threadIdx.x;
         const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
-        softmax_row<T, 2>(&sm.s_full, nullptr, &sm.p_full, &sm.o_full, lane_base, lane_base + 128, n_kv, t * BM + r, r, 0, p, cta_abort,
+        softmax_row<T, 2>(&sm.s_full, &sm.p_half, &sm.p_full, &sm.o_full, lane_base, lane_base + 128, n_kv, t * BM + r, r, 0, p, cta_abort,
                        q0 + r < L, seq_beg + q0 + r, h);
     }
     // ---------------------------------------------------------------------- teardown
@@ -1164,8 +1470,8 @@ int prefill_tc_launch(const void* q, const void* k, const void* v, const int32_t
     if ((rc = make_map(&mq, q, n_tokens, H, dtype)) || (rc = make_map(&mk, k, n_tokens, H, dtype)) ||
         (rc = make_map(&mv, v, n_tokens, H, dtype)))
         return rc;
-    static const int version = [] { const char* e = getenv("ATTN_B200_PREFILL_VERSION"); return e ? atoi(e) : 2; }();
-    const bool use_v1 = version == 1, use_v3 = version == 3;
+    static const int version = [] { const char* e = getenv("ATTN_B200_PREFILL_VERSION"); return e ? atoi(e) : 6; }();
+    const bool use_v1 = version == 1, use_v3 = version == 3, use_p = version == 6;
     const int rows_per_cta = (use_v1 || use_v3) ? BM : 2 * BM;
     const int smem = (int)(use_v1 ? sizeof(SmemLayout) : use_v3 ? sizeof(SmemLayout3) : sizeof(SmemLayout2)) + 1024;
     Params p{offsets, out, B, H, n_tokens, (max_len + rows_per_cta - 1) / rows_per_cta, scale * kLog2e, out_f32,
@@ -1176,6 +1482,31 @@ int prefill_tc_launch(const void* q, const void* k, const void* v, const int32_t
     if (e != cudaSuccess) return (int)e;
     if ((e = cudaMemsetAsync(abort_addr, 0, sizeof(int), st)) != cudaSuccess) return (int)e;
     zero_tail_kernel<<<64, 256, 0, st>>>(out, offsets, B, n_tokens, (int64_t)H * HD * (out_f32 ? 4 : 2));
+    if (use_p) {
+        int dev = 0, n_sm = 0;
+        if ((e = cudaGetDevice(&dev)) != cudaSuccess) return (int)e;
+        if ((e = cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return (int)e;
+        const int64_t n_items = (((int64_t)H * B + ITEM_GROUP - 1) / ITEM_GROUP) * ITEM_GROUP * p.n_qtiles;
+        const int smem_p = (int)sizeof(SmemLayout2p) + 1024;
+        // work counter of this launch: one of 64 slots taken in rotation, zeroed on the launch's
+        // stream (launches in flight at the same time on different streams need different slots)
+        static std::atomic<unsigned> next_slot{0};
+        void* work_base = nullptr;
+        if ((e = cudaGetSymbolAddress(&work_base, g_work)) != cudaSuccess) return (int)e;
+        unsigned long long* work_counter = (unsigned long long*)work_base + (next_slot.fetch_add(1) & 63u);
+        if ((e = cudaMemsetAsync(work_counter, 0, sizeof(unsigned long long), st)) != cudaSuccess) return (int)e;
+        const unsigned ctas = (unsigned)(n_items < n_sm ? n_items : n_sm);
+        if (dtype == ATTN_B200_BF16) {
+            if ((e = cudaFuncSetAttribute(prefill_tc2p_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_p)) != cudaSuccess)
+                return (int)e;
+            prefill_tc2p_kernel<__nv_bfloat16><<<ctas, THREADS2, smem_p, st>>>(mq, mk, mv, p, n_items, work_counter);
+        } else {
+            if ((e = cudaFuncSetAttribute(prefill_tc2p_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_p)) != cudaSuccess)
+                return (int)e;
+            prefill_tc2p_kernel<__half><<<ctas, THREADS2, smem_p, st>>>(mq, mk, mv, p, n_items, work_counter);
+        }
+        return (int)cudaGetLastError();
+    }
     if (use_v3) {
         if (dtype == ATTN_B200_BF16) {
             if ((e = cudaFuncSetAttribute(prefill_tc3_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) != cudaSuccess)

@@ -266,7 +266,7 @@ class LargeDecode(Workload):
         return 2
 
     def kernel_name(self):
-        return "paged_decode_fast_kernel<half,half,128,heads-per-warp>"
+        return "paged_decode_mha_kernel<half,half,128,heads-per-warp>"
 
     def traffic(self):
         return DECODE_TRAFFIC_RATIO * self.units_per_step_rank()
@@ -478,7 +478,7 @@ class Prefill(Workload):
         return 1
 
     def kernel_name(self):
-        return "prefill_tc2_kernel<bf16>"
+        return "prefill_tc2p_kernel<bf16>"
 
     def config(self):
         return {"workload": "packed_varlen_causal_prefill", "sequences": len(self.lens_), "heads": self.H,
@@ -596,7 +596,7 @@ class Fp8Split(Workload):
         return 3 + (1 if self.world > 1 else 0)     # partial, local combine, (all-gather), final combine
 
     def kernel_name(self):
-        return "paged_decode_fast_kernel<half,e4m3,128,heads-per-warp>"
+        return "paged_decode_mha_kernel<half,e4m3,128,heads-per-warp>"
 
     def config(self):
         per = self.units_per_step_rank()
