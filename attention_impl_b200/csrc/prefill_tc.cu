@@ -679,18 +679,22 @@ prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 // =============================================================================================
 // Persistent form of version 2.
 //
-// Version 2 spends about two of a CTA's ~ten key-tile periods outside its steady state: barrier
-// and tensor-memory set-up, the first TMA round trip and the first Q.K before any softmax can run,
-// and the read-out of O at the end.  Here the grid is one CTA per SM and every CTA walks a list of
-// work items (a pair of query tiles of one (sequence, head)), heaviest pairs first, handed out by an
-// atomic counter: the producer thread draws the next non-empty item and publishes it to the other
-// roles through a 4-deep ring in shared memory (no role can be more than two items behind the
-// producer, see the ring's comment).  Barriers, tensor memory and the K/V rings live across
-// items: each role keeps running counters for the barrier phases.  The producer fetches the next
-// item's Q tiles as soon as the last Q.K of the current item has completed (q_empty) and its first
-// K/V tiles as the ring frees, so the next item's first S tiles are computed while the softmax
-// warpgroups are still reading out O; the only new dependency is o_free (the accumulator of a
-// warpgroup has been read out before the next item's first P.V overwrites it).
+// Version 2 spends about two of a CTA's ~ten key-tile periods outside its steady state: set-up and
+// the first TMA round trip before any softmax can run, the read-out of O at the end, and the last
+// key tile of the pair, which only the upper query tile needs (the other warpgroup idles).  Here
+// the grid is one CTA per SM and every CTA walks work items (a pair of query tiles of one
+// (sequence, head)), heaviest pairs first, handed out by an atomic counter: the producer thread
+// draws the next non-empty item and publishes it to the other roles through a 4-deep ring in
+// shared memory.  Barriers, tensor memory and the K/V rings live across items; every role keeps
+// running counters for the barrier phases.
+//
+// One MMA thread serves the two warpgroups in a fixed alternating order (P.V_a, Q.K_a', P.V_b,
+// Q.K_b'), which keeps one warpgroup's softmax over the other's MMAs.  The last key tile of an
+// item is needed by the upper query tile only; the warpgroup with the lower tile has finished, and
+// the first Q.K of its tile in the NEXT item is issued at that moment (its Q tile and the first K
+// tile of the next item are fetched ahead for this), so it runs one key tile ahead.  The two query
+// tiles of a pair are given to the warpgroups in alternating order from item to item: the early
+// starter takes the upper tile, which has one key tile more, and both finish together.
 // =============================================================================================
 static __device__ unsigned long long g_work[64];   // work counters of the persistent kernel, one slot per launch in flight
 
@@ -698,11 +702,11 @@ struct SmemLayout2p {
     alignas(1024) unsigned char q[2][TILE_BYTES];
     alignas(1024) unsigned char k[STAGES][TILE_BYTES];
     alignas(1024) unsigned char v[STAGES][TILE_BYTES];
-    alignas(8) unsigned long long q_full, q_empty;
+    alignas(8) unsigned long long q_full[2], q_empty[2];
     // item_id[n & 3] = n-th item of this CTA (-1: no more work), published by the producer.  The
-    // producer draws item n only after it has issued every K/V tile of item n-1, i.e. after the
-    // MMA thread and the softmax threads have entered item n-1; slot n & 3 was last read at the
-    // start of item n-4, so it is free.
+    // producer draws item n only after it has issued every K/V tile of item n-1, which needs both
+    // streams and therefore both softmax warpgroups to be inside item n-1 or later; slot n & 3 was
+    // last read at the start of item n-4, so it is free.
     unsigned long long item_full[4];
     long long item_id[4];
     unsigned long long s_full[2], p_half[2], p_full[2], o_full[2], o_free[2];
@@ -715,7 +719,7 @@ struct SmemLayout2p {
 // ITEM_GROUP; inside a group the pair index is the slowest coordinate, so the heaviest pairs of the
 // group come first while the CTAs running at any moment share the K/V of a few dozen (sequence,
 // head) combinations, which stay in L2 (with the pair index slowest over ALL combinations every CTA
-// would stream its own K/V from DRAM).
+// would stream its own K/V from DRAM: measured 814 against 960 TFLOP/s).
 #ifndef ATTN_B200_ITEM_GROUP
 #define ATTN_B200_ITEM_GROUP 16
 #endif
@@ -743,11 +747,13 @@ __device__ __forceinline__ Item2p decode_item(const Params& p, int64_t id) {
     it.valid = !(it.seq_beg < 0 || seq_end < it.seq_beg || seq_end > p.n_tokens);
     it.L = it.valid ? (int)(seq_end - it.seq_beg) : 0;
     it.q0 = it.tp * 2 * BM;
-    it.n0 = 2 * it.tp + 1;
-    it.n1 = (it.q0 + BM < it.L) ? 2 * it.tp + 2 : 0;
+    it.n0 = 2 * it.tp + 1;                                   // key tiles of the lower query tile
+    it.n1 = (it.q0 + BM < it.L) ? 2 * it.tp + 2 : 0;         // of the upper one (0: past the end)
     it.nmax = it.n1 > it.n0 ? it.n1 : it.n0;
     return it;
 }
+// In the CTA's n-th item warpgroup w takes the upper query tile iff (w ^ n) & 1.
+__device__ __forceinline__ int upper_of(int w, int n) { return (w ^ n) & 1; }
 
 template <typename T>
 __global__ void __launch_bounds__(THREADS2, 1)
@@ -762,10 +768,10 @@ prefill_tc2p_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     volatile int* cta_abort = &sm.abort;
 
     if (threadIdx.x == 0) {
-        mbar_init(&sm.q_full, 1);
-        mbar_init(&sm.q_empty, 1);
         for (int i = 0; i < 4; ++i) mbar_init(&sm.item_full[i], 1);
         for (int w = 0; w < 2; ++w) {
+            mbar_init(&sm.q_full[w], 1);
+            mbar_init(&sm.q_empty[w], 1);
             mbar_init(&sm.s_full[w], 1);
             mbar_init(&sm.p_half[w], 128);
             mbar_init(&sm.p_full[w], 128);
@@ -790,15 +796,15 @@ prefill_tc2p_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     tc_fence_after();
     const uint32_t tmem = sm.tmem_base;
 
-    // producer bookkeeping for the drain on abort: tiles issued in total, Q loads issued in total
-    int g_issued_k = 0, g_issued_v = 0, q_issued = 0;
+    // producer bookkeeping for the drain on abort: K/V tiles and Q tiles issued in total
+    int g_issued_k = 0, g_issued_v = 0, q_issued[2] = {0, 0};
     if (warp >= 8) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
     if (warp == 8) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
             int g = 0;        // key tiles issued so far (all items): ring stage g & 1, use (g >> 1)
-            int n_it = 0;     // non-empty items so far
+            int n_it = 0;     // items published so far
             bool ok = true;
             while (ok) {
                 // draw the next non-empty item (empty ones: pairs past the end of a short sequence)
@@ -814,13 +820,22 @@ prefill_tc2p_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 mbar_arrive(&sm.item_full[n_it & 3]);
                 if (id < 0) break;
                 const int col0 = it.h * HD;
-                if (n_it > 0 && !(ok = mbar_wait(&sm.q_empty, (n_it - 1) & 1, cta_abort, p.err_flag))) break;
-                mbar_expect_tx(&sm.q_full, 2 * TILE_BYTES);
-                for (int w = 0; w < 2; ++w) {
-                    tma_load_2d(sm.q[w], &map_q, col0, (int)(it.seq_beg + it.q0 + w * BM), &sm.q_full);
-                    tma_load_2d(sm.q[w] + SUB_BYTES, &map_q, col0 + 64, (int)(it.seq_beg + it.q0 + w * BM), &sm.q_full);
-                }
-                ++q_issued;
+                auto load_q = [&](int w) -> bool {       // query tile of warpgroup w, once its buffer is free
+                    const int u = upper_of(w, n_it);
+                    if ((u ? it.n1 : it.n0) == 0) return true;
+                    if (q_issued[w] > 0 && !mbar_wait(&sm.q_empty[w], (q_issued[w] - 1) & 1, cta_abort, p.err_flag)) return false;
+                    const int row = (int)(it.seq_beg + it.q0 + u * BM);
+                    mbar_expect_tx(&sm.q_full[w], TILE_BYTES);
+                    tma_load_2d(sm.q[w], &map_q, col0, row, &sm.q_full[w]);
+                    tma_load_2d(sm.q[w] + SUB_BYTES, &map_q, col0 + 64, row, &sm.q_full[w]);
+                    ++q_issued[w];
+                    return true;
+                };
+                // The warpgroup that had the lower tile in the previous item (and takes the upper
+                // one now) finished first: its Q buffer is free first, and it starts this item
+                // first.  Order: its Q, K tile 0, the other Q, V tile 0, then the remaining tiles.
+                const int w_first = (n_it & 1) ? 0 : 1;      // upper_of(w_first, n_it) == 1
+                if (!(ok = load_q(w_first))) break;
                 for (int j = 0; j < it.nmax; ++j, ++g) {
                     const int s = g & 1;
                     const uint32_t ph = ((g - STAGES) >> 1) & 1;
@@ -830,6 +845,7 @@ prefill_tc2p_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                     tma_load_2d(sm.k[s], &map_k, col0, row, &sm.k_full[s]);
                     tma_load_2d(sm.k[s] + SUB_BYTES, &map_k, col0 + 64, row, &sm.k_full[s]);
                     g_issued_k = g + 1;
+                    if (j == 0 && !(ok = load_q(w_first ^ 1))) break;
                     if (g >= STAGES && !(ok = mbar_wait(&sm.v_empty[s], ph, cta_abort, p.err_flag))) break;
                     mbar_expect_tx(&sm.v_full[s], TILE_BYTES);
                     tma_load_2d(sm.v[s], &map_v, col0, row, &sm.v_full[s]);
@@ -868,52 +884,80 @@ prefill_tc2p_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 }
                 if (half) umma_commit(&sm.o_full[w]);
             };
-            int g = 0, n_it = 0;
+            int g = 0, n = 0;
             int c[2] = {0, 0};        // tiles processed per warpgroup (phase of s_full / p_half / p_full / o_full)
-            int uses[2] = {0, 0};     // items in which the warpgroup had work (phase of o_free)
+            int uses[2] = {0, 0};     // items in which the warpgroup had work (phase of q_full / o_free)
+            bool early = false;       // the upper tile's first Q.K of item n was issued during item n-1
             bool ok = true;
             while (ok) {
-                if (!(ok = mbar_wait_spin(&sm.item_full[n_it & 3], (n_it >> 2) & 1, cta_abort, p.err_flag))) break;
-                const long long id = sm.item_id[n_it & 3];
+                if (!(ok = mbar_wait_spin(&sm.item_full[n & 3], (n >> 2) & 1, cta_abort, p.err_flag))) break;
+                const long long id = sm.item_id[n & 3];
                 if (id < 0) break;
                 const Item2p it = decode_item(p, id);
-                const int nw[2] = {it.n0, it.n1};
-                if (!(ok = mbar_wait_spin(&sm.q_full, n_it & 1, cta_abort, p.err_flag))) break;
+                // Within an item the warpgroup with the upper query tile is served first in every
+                // round: it has one key tile more and (after an early start) is one tile ahead.
+                const int wu = (n & 1) ? 0 : 1, wl = wu ^ 1;
+                int nw[2];
+                nw[wu] = it.n1;
+                nw[wl] = it.n0;
                 if (!(ok = mbar_wait_spin(&sm.k_full[g & 1], (g >> 1) & 1, cta_abort, p.err_flag))) break;
+                if (it.n1 > 0 && !early) {
+                    if (!(ok = mbar_wait_spin(&sm.q_full[wu], uses[wu] & 1, cta_abort, p.err_flag))) break;
+                    tc_fence_after();
+                    issue_qk(wu, g & 1);
+                }
+                if (!(ok = mbar_wait_spin(&sm.q_full[wl], uses[wl] & 1, cta_abort, p.err_flag))) break;
                 tc_fence_after();
-                issue_qk(0, g & 1);
-                if (it.n1 > 0) issue_qk(1, g & 1);
+                issue_qk(wl, g & 1);
                 umma_commit(&sm.k_empty[g & 1]);
-                if (it.nmax == 1) umma_commit(&sm.q_empty);
+                if (it.n0 == 1) umma_commit(&sm.q_empty[wl]);
+                early = false;
                 for (int j = 0; ok && j < it.nmax; ++j) {
                     const int s = (g + j) & 1;
                     const uint32_t ph = ((g + j) >> 1) & 1;
-                    for (int w = 0; w < 2 && ok; ++w) {
+                    if (j == it.nmax - 1 && it.n1 > 0) {
+                        // Last key tile: only the upper query tile needs it.  The other warpgroup
+                        // takes the upper tile of the next item: start that item's first Q.K now
+                        // if the item, its Q tile and its first K tile are already there.  (Polling
+                        // for them while waiting for P, and a second MMA thread so that each
+                        // warpgroup advances by itself, were both measured: short sequences gain,
+                        // but the alternation of the two warpgroups is lost and long ones lose more.)
+                        const int G1 = g + it.nmax;
+                        if (mbar_test(&sm.item_full[(n + 1) & 3], ((n + 1) >> 2) & 1)) {
+                            const long long id1 = sm.item_id[(n + 1) & 3];
+                            if (id1 >= 0 && decode_item(p, id1).n1 > 0 && mbar_test(&sm.q_full[wl], (uses[wl] + 1) & 1) &&
+                                mbar_test(&sm.k_full[G1 & 1], (G1 >> 1) & 1)) {
+                                tc_fence_after();
+                                issue_qk(wl, G1 & 1);
+                                early = true;
+                            }
+                        }
+                    }
+                    for (int t = 0; t < 2 && ok; ++t) {
+                        const int w = t ? wl : wu;
                         if (j < nw[w]) {
                             if (j == 0 && uses[w] > 0) {     // the previous item's O must have been read out
                                 if (!(ok = mbar_wait_spin(&sm.o_free[w], (uses[w] - 1) & 1, cta_abort, p.err_flag))) break;
                             }
                             if (!(ok = mbar_wait_spin(&sm.p_half[w], (c[w] + j) & 1, cta_abort, p.err_flag))) break;
-                            if (w == 0 || j >= it.n0) { if (!(ok = mbar_wait_spin(&sm.v_full[s], ph, cta_abort, p.err_flag))) break; }
+                            if (t == 0 || j >= nw[wu]) { if (!(ok = mbar_wait_spin(&sm.v_full[s], ph, cta_abort, p.err_flag))) break; }
                             tc_fence_after();
                             issue_pv(w, s, 0, j == 0);
                             if (!(ok = mbar_wait_spin(&sm.p_full[w], (c[w] + j) & 1, cta_abort, p.err_flag))) break;
                             tc_fence_after();
                             issue_pv(w, s, 1, j == 0);
                         }
-                        if (w == 1) umma_commit(&sm.v_empty[s]);
+                        if (t == 1) umma_commit(&sm.v_empty[s]);
                         if (j + 1 < nw[w]) {
                             const int s1 = (g + j + 1) & 1;
-                            if (w == 0 || j + 1 >= it.n0) {
+                            if (t == 0 || j + 1 >= nw[wu]) {
                                 if (!(ok = mbar_wait_spin(&sm.k_full[s1], ((g + j + 1) >> 1) & 1, cta_abort, p.err_flag))) break;
                             }
                             tc_fence_after();
                             issue_qk(w, s1);
+                            if (j + 2 == nw[w]) umma_commit(&sm.q_empty[w]);     // last Q.K of this warpgroup's tile
                         }
-                        if (w == 1 && j + 1 < it.nmax) {
-                            umma_commit(&sm.k_empty[(g + j + 1) & 1]);
-                            if (j + 2 == it.nmax) umma_commit(&sm.q_empty);     // last Q.K of the item issued
-                        }
+                        if (t == 1 && j + 1 < it.nmax) umma_commit(&sm.k_empty[(g + j + 1) & 1]);
                     }
                 }
                 for (int w = 0; w < 2; ++w) {
@@ -921,7 +965,7 @@ prefill_tc2p_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                     uses[w] += nw[w] > 0;
                 }
                 g += it.nmax;
-                ++n_it;
+                ++n;
             }
         }
         __syncwarp();
@@ -940,11 +984,12 @@ prefill_tc2p_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             if (id < 0) break;
             const Item2p it = decode_item(p, id);
             if (*cta_abort) break;
-            const int nk = w ? it.n1 : it.n0;
-            const int tq = 2 * it.tp + w;
+            const int u = upper_of(w, n_it);
+            const int nk = u ? it.n1 : it.n0;
+            if (nk == 0) continue;
+            const int tq = 2 * it.tp + u;
             softmax_row<T, 2>(&sm.s_full[w], &sm.p_half[w], &sm.p_full[w], &sm.o_full[w], s_addr, o_addr, nk, tq * BM + r, r, w, p,
-                              cta_abort, it.q0 + w * BM + r < it.L, it.seq_beg + it.q0 + w * BM + r, it.h, c0,
-                              nk > 0 ? &sm.o_free[w] : nullptr);
+                              cta_abort, it.q0 + u * BM + r < it.L, it.seq_beg + it.q0 + u * BM + r, it.h, c0, &sm.o_free[w]);
             c0 += nk;
         }
     }
@@ -952,7 +997,8 @@ prefill_tc2p_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     if (warp == 8 && lane == 0 && sm.abort) {
         // give the copies still in flight a bounded time to land before shared memory is released
         const long long t0 = clock64();
-        if (q_issued > 0) while (!mbar_try(&sm.q_full, (q_issued - 1) & 1) && clock64() - t0 < WAIT_CYCLES) {}
+        for (int w = 0; w < 2; ++w)
+            if (q_issued[w] > 0) while (!mbar_try(&sm.q_full[w], (q_issued[w] - 1) & 1) && clock64() - t0 < WAIT_CYCLES) {}
         for (int gg = g_issued_k > STAGES ? g_issued_k - STAGES : 0; gg < g_issued_k; ++gg)
             while (!mbar_try(&sm.k_full[gg & 1], (gg >> 1) & 1) && clock64() - t0 < WAIT_CYCLES) {}
         for (int gg = g_issued_v > STAGES ? g_issued_v - STAGES : 0; gg < g_issued_v; ++gg)

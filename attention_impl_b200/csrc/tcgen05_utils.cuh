@@ -30,6 +30,13 @@ __device__ __forceinline__ bool mbar_try(void* bar, uint32_t parity) {
                  : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
     return ok != 0;
 }
+// Non-blocking test of a phase (never suspends the thread).
+__device__ __forceinline__ bool mbar_test(void* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
 // Bounded wait.  Returns false if the CTA is aborting or the limit ran out (then it raises the abort).
 __device__ __forceinline__ bool mbar_wait(void* bar, uint32_t parity, volatile int* cta_abort, int32_t* err_flag) {
     if (mbar_try(bar, parity)) return true;
