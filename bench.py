@@ -518,6 +518,97 @@ class Prefill(Workload):
         return fl / sec / 1e12, sec, f"1 of {self.B} sequences ({T} tokens) per step", T
 
 
+class PagedPrefill(Prefill):
+    """Chunked prefill through the slot table: the last <= 512 tokens of every sequence attend to the
+    whole sequence (prefix + chunk), whose K/V rows are scattered over the pools."""
+    name, metric = "paged_prefill", "chunked_prefill_throughput"
+    CHUNK = 512
+
+    def setup(self):
+        import attention_impl_b200 as A
+        self.A = A
+        dev = self.dev
+        self.lens_ = seeded_lengths(self.args.batch or self.B, self.LO, self.HI, self.SEED)
+        self.qlens_ = self.lens_.clamp(max=self.CHUNK)
+        self.T, self.Tq = int(self.lens_.sum()), int(self.qlens_.sum())
+        torch.manual_seed(3100 + self.rank)
+        self.Q = torch.randn(self.Tq, self.H * self.D, device=dev, dtype=torch.bfloat16)
+        self.K, self.V = (torch.randn(self.T, self.H * self.D, device=dev, dtype=torch.bfloat16) for _ in range(2))
+        self.slots = torch.randperm(self.T, device=dev).to(torch.int32)
+        self.kvo = self.lens_.cumsum(0).to(torch.int32).to(dev)
+        self.qo = self.qlens_.cumsum(0).to(torch.int32).to(dev)
+        self.flag = torch.zeros(1, dtype=torch.int32, device=dev)
+
+    def step(self):
+        self.out = self.A.paged_prefill_attention(self.Q, self.K, self.V, self.slots, self.kvo, self.qo, self.H,
+                                                  max_q_len=int(self.qlens_.max()), max_kv_len=int(self.lens_.max()),
+                                                  err_flag=self.flag)
+
+    def e2e_setup(self):
+        # the pools are device-resident state (the cache); the chunk's queries and the tables come from the host
+        self.h_in = [x.cpu().pin_memory() for x in (self.Q, self.slots, self.kvo, self.qo)]
+        self.h_out = torch.empty(self.Q.shape, dtype=self.Q.dtype).pin_memory()
+        return sum(x.numel() * x.element_size() for x in self.h_in), self.h_out.numel() * 2
+
+    def e2e_step(self):
+        dQ, dsl, dkvo, dqo = (x.to(self.dev, non_blocking=True) for x in self.h_in)
+        o = self.A.paged_prefill_attention(dQ, self.K, self.V, dsl, dkvo, dqo, self.H, max_q_len=int(self.qlens_.max()),
+                                           max_kv_len=int(self.lens_.max()))
+        self.h_out.copy_(o, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    def _flops(self, l, q):
+        # visible (query, key) pairs: row i of a chunk sees kv_len - q_len + i + 1 keys
+        return 4.0 * self.D * self.H * float((q * (l - q) + q * (q + 1) / 2).sum())
+
+    def units_per_step_rank(self):
+        return self._flops(self.lens_.double(), self.qlens_.double())
+
+    def sequences_per_step(self):
+        return self.Tq
+
+    def kernel_name(self):
+        return "paged_prefill_tc_kernel<bf16>"
+
+    def config(self):
+        return {"workload": "chunked_prefill_through_slot_table", "sequences": len(self.lens_), "heads": self.H,
+                "head_dim": self.D, "kv_len_range": [self.LO, self.HI], "chunk": self.CHUNK, "query_tokens": self.Tq,
+                "kv_tokens": self.T, "flops_per_step": self.units_per_step_rank(), "sharding": "replicas only",
+                "l2": f"K/V pools = {2 * self.T * self.H * self.D * 2 / 1e9:.1f} GB per step (> 126 MB L2)"}
+
+    def cpu_baseline(self):
+        from oracle import attention_oracle as orc
+        n_seq = 2
+        T, Tq = int(self.lens_[:n_seq].sum()), int(self.qlens_[:n_seq].sum())
+        Q, K, V, sl = self.Q[:Tq].cpu(), self.K.cpu(), self.V.cpu(), self.slots[:T].cpu()
+        kvo, qo = self.kvo[:n_seq].cpu(), self.qo[:n_seq].cpu()
+        sec = time_cpu(lambda: orc.paged_prefill(Q, K, V, sl, kvo, qo, self.H))
+        O32 = orc.paged_prefill(Q, K, V, sl, kvo, qo, self.H, compute_dtype=torch.float32, out_dtype=torch.float32)
+        self.step()
+        torch.cuda.synchronize()
+        err = (self.out[:Tq].cpu().float() - O32).abs().max().item()
+        fl = self._flops(self.lens_[:n_seq].double(), self.qlens_[:n_seq].double())
+        return ({"value": fl / sec / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+                 "sample": f"first {n_seq} of {len(self.lens_)} sequences ({Tq} query tokens over {T} cached tokens)",
+                 "seconds": sec, "torch": torch.__version__},
+                {"max_abs_err_vs_fp32_oracle": err, "tolerance": 1.6e-2, "sequences_checked": n_seq,
+                 "kernel_flag": int(self.flag.item())})
+
+    def reference_run(self, steps, warmup):
+        from oracle import attention_oracle as orc
+        lens = seeded_lengths(self.B, self.LO, self.HI, self.SEED)[:1].clamp(max=2048)
+        qlens = lens.clamp(max=self.CHUNK)
+        T, Tq = int(lens.sum()), int(qlens.sum())
+        g = torch.Generator().manual_seed(3)
+        Q = torch.randn(Tq, self.H * self.D, generator=g).bfloat16()
+        K, V = (torch.randn(T, self.H * self.D, generator=g).bfloat16() for _ in range(2))
+        sl = torch.randperm(T, generator=g).int()
+        sec = time_cpu(lambda: orc.paged_prefill(Q, K, V, sl, lens.cumsum(0).int(), qlens.cumsum(0).int(), self.H),
+                       steps=steps, warmup=warmup)
+        return self._flops(lens.double(), qlens.double()) / sec / 1e12, sec, \
+            f"1 of {self.B} sequences ({Tq} query tokens over {T} cached tokens) per step", Tq
+
+
 class Fp8Split(Workload):
     name, metric, unit, dtype = "fp8_split", "paged_decode_kv_read_bandwidth", "TB/s", "e4m3"
     B, H, D, LO, HI, SEED = 64, 32, 128, 32768, 131072, 5
@@ -627,7 +718,7 @@ class Fp8Split(Workload):
         return 2.0 * T * H * D / sec / 1e12, sec, f"1 sequence of {T} tokens per step", 1
 
 
-WORKLOADS = {w.name: w for w in (LargeDecode, SmallDecode, Rope, Prefill, Fp8Split)}
+WORKLOADS = {w.name: w for w in (LargeDecode, SmallDecode, Rope, Prefill, PagedPrefill, Fp8Split)}
 
 
 # ================================================================================================
