@@ -96,3 +96,45 @@ def test_prefill_tc_rows_past_the_last_sequence_are_zero():
     _, _, O = lm_ops.packed_attention(Q.cuda(), K.cuda(), V.cuda(), off.cuda(), 2, return_sp=False)
     assert O[300:].abs().sum().item() == 0
     assert O[:300].abs().sum().item() > 0
+
+
+def test_prefill_tc_concurrent_streams_and_back_to_back_launches():
+    """The persistent kernel draws its work items from a per-launch counter.  Launches that overlap on
+    two streams, and launches queued back to back on one stream, must not share a counter: every
+    result equals the one computed alone."""
+    import lm_ops
+    H = 8
+    cases = []
+    for seed, lens in ((21, [700, 33, 1500, 256, 90]), (22, [2048, 2048, 5]), (23, [64] * 40)):
+        Q, K, V, off = prefill_inputs(lens, H, 128, torch.bfloat16, seed=seed)
+        cases.append(tuple(x.cuda() for x in (Q, K, V, off)))
+    alone = [lm_ops.packed_attention(*c, H, return_sp=False)[2].clone() for c in cases]
+    torch.cuda.synchronize()
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    outs = [[] for _ in cases]
+    for rep in range(6):
+        for i, c in enumerate(cases):
+            with torch.cuda.stream(streams[(i + rep) % 2]):
+                outs[i].append(lm_ops.packed_attention(*c, H, return_sp=False)[2])
+    torch.cuda.synchronize()
+    for i in range(len(cases)):
+        for o in outs[i]:
+            assert torch.equal(o, alone[i])
+
+
+def test_prefill_tc_long_sequence_many_key_tiles():
+    """One 8192-token sequence: 32 pairs of query tiles, up to 64 key tiles per pair (ring phases wrap
+    many times inside one work item)."""
+    H = 2
+    Q, K, V, off = prefill_inputs([8192], H, 128, torch.float16, seed=5)
+    O = _run(Q, K, V, off, H, out_dtype=torch.float32)
+    # the oracle on the last 256 query rows only (they see all keys): cheap on the CPU
+    import math
+    q = Q[-256:].float().reshape(256, H, 128).permute(1, 0, 2)
+    k = K.float().reshape(8192, H, 128).permute(1, 0, 2)
+    v = V.float().reshape(8192, H, 128).permute(1, 0, 2)
+    S = torch.matmul(q, k.transpose(-1, -2)) / math.sqrt(128)
+    vis = torch.arange(8192).unsqueeze(0) <= (8192 - 256 + torch.arange(256)).unsqueeze(1)
+    P = S.masked_fill(~vis.unsqueeze(0), float("-inf")).softmax(-1)
+    ref = torch.matmul(P, v).permute(1, 0, 2).reshape(256, H * 128)
+    assert (O[-256:] - ref).abs().max() <= 2e-3
