@@ -415,8 +415,8 @@ __device__ __forceinline__ void softmax_row(unsigned long long* s_full, unsigned
                 // bf16 inputs: fp32 ex2, the remaining fp32 arithmetic as packed pairs (f32x2).  A
                 // warp's 128 exponentials occupy the special-function unit for 1024 clocks (4 lanes
                 // per clock per scheduler), so kPolyOf8 of every 8 elements take a cubic on the
-                // FMA pipe instead (2 where the schedulers have slots to spare, 0 in the paged kernel,
-                // whose gather warps share them).
+                // FMA pipe instead (2 in the packed kernels; 0 in the paged kernel, whose gather warps
+                // share the schedulers: measured 895 against 820 TFLOP/s).
                 float rs4[4] = {0.f, 0.f, 0.f, 0.f};
                 const float nm = -m_ref;
 #pragma unroll
@@ -1189,7 +1189,10 @@ prefill_tc3_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 // of K/V: a fourth warpgroup (warps 12-13 for K, 14-15 for V) copies the 128 rows of a tile with
 // 16-byte cp.async (16 consecutive lanes = one 256-byte row, so a warp instruction reads two whole
 // rows) into the same 128-byte-swizzled layout TMA would have produced; rows past the end of the
-// sequence are zero-filled.  A tile is published (fence.proxy.async + mbarrier arrive by the
+// sequence are zero-filled.  The 16 lanes of a row need the same slots: each loads and checks two
+// of the group's 32 slots per tile and the copies take them by shuffle (with every lane loading
+// and checking all 32 itself the gather warps' instructions slowed the softmax warps on the same
+// schedulers: 686 against 895 TFLOP/s).  A tile is published (fence.proxy.async + mbarrier arrive by the
 // stream's 64 threads) once it has landed.  Grouped-query heads: query head h reads KV head h / (H / Hkv).
 // =============================================================================================
 constexpr int THREADS_PG = 512;
@@ -1300,44 +1303,42 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const Params 
         unsigned long long* empty = v_stream ? sm.v_empty : sm.k_empty;
         unsigned char (*stage)[TILE_BYTES] = v_stream ? sm.v : sm.k;
         const int n_stages = v_stream ? STAGES : KSTAGES_PG;
-        // slots of a half tile (16 of this thread's 32 rows), fetched as 16 independent loads: no
-        // atomic (a memory side effect the compiler may not move loads across) inside the loop
-        auto load_slots = [&](int j, int half, int* sl) {
+        // A thread copies chunk c of the 32 rows q*4 + rsub (q = 0..31) of a tile.  The 16 threads
+        // of a row group need the same 32 slots: thread c loads and checks the slots of rows q = c
+        // and q = c + 16 (ahead of the wait for the stage), and the copies take them from there by
+        // shuffle, which keeps the gather's share of the schedulers' issue slots small.
+        auto tile_slots = [&](int j, int& sa, int& sb) {
             bool bad = false;
 #pragma unroll
-            for (int q = 0; q < 16; ++q) {
-                const int kvpos = j * BN + (half * 16 + q) * 4 + rsub;
-                const bool live = j < nmax && kvpos < kv_len;
+            for (int i = 0; i < 2; ++i) {
+                const int kvpos = j * BN + (c + 16 * i) * 4 + rsub;
+                const bool live = kvpos < kv_len;
                 const int v = live ? __ldg(pg.slots + kv_beg + kvpos) : -1;
                 const bool in_range = v >= 0 && v < pg.n_slots;
                 bad |= live && !in_range;
-                sl[q] = in_range ? v : -1;
+                (i ? sb : sa) = in_range ? v : -1;
             }
             if (bad && p.err_flag) atomicOr(p.err_flag, ATTN_B200_FLAG_BAD_SLOT);
         };
-        // destination of row (half*16+q)*4 + rsub, chunk c, in the 128-byte-swizzled tile: the row's
-        // low three bits are (q&1)*4 + rsub, so there are only two swizzle terms per thread and
-        // everything else is a compile-time offset: one add per copy on top of the source address
+        // destination of row q*4 + rsub, chunk c, in the 128-byte-swizzled tile: the row's low three
+        // bits are (q&1)*4 + rsub, so there are only two swizzle terms per thread and everything
+        // else is a compile-time offset
         const uint32_t swz_even = rsub * 128 + ((((uint32_t)c & 7) ^ (uint32_t)rsub) << 4);
         const uint32_t swz_odd = rsub * 128 + ((((uint32_t)c & 7) ^ (uint32_t)(4 + rsub)) << 4);
-        auto copy_rows = [&](uint32_t sbase, int half, const int* sl) {
-            const uint32_t be = sbase + swz_even, bo = sbase + swz_odd;
-#pragma unroll
-            for (int q = 0; q < 16; ++q) {
-                const uint32_t dst = ((q & 1) ? bo : be) + (uint32_t)(half * 16 + q) * 512u;
-                cp_async16(dst, base + (int64_t)(sl[q] >= 0 ? sl[q] : 0) * row_bytes, sl[q] >= 0 ? 16 : 0);
-            }
-        };
         bool ok = true;
         for (int j = 0; j < nmax; ++j) {
             const int s = j % n_stages;
-            if (j >= n_stages && !(ok = mbar_wait(&empty[s], ((j - n_stages) / n_stages) & 1, cta_abort, p.err_flag))) break;
+            int sa, sb;
+            tile_slots(j, sa, sb);
+            if (j >= n_stages) ok = mbar_wait(&empty[s], ((j - n_stages) / n_stages) & 1, cta_abort, p.err_flag);
+            if (!__all_sync(0xffffffffu, ok)) break;
             const uint32_t sbase = smem_u32(stage[s]) + dst_off;
+            const uint32_t be = sbase + swz_even, bo = sbase + swz_odd;
 #pragma unroll
-            for (int half = 0; half < 2; ++half) {
-                int sl[16];
-                load_slots(j, half, sl);
-                copy_rows(sbase, half, sl);
+            for (int q = 0; q < 32; ++q) {
+                const int v = __shfl_sync(0xffffffffu, q < 16 ? sa : sb, q & 15, 16);
+                const uint32_t dst = ((q & 1) ? bo : be) + (uint32_t)q * 512u;
+                cp_async16(dst, base + (int64_t)(v >= 0 ? v : 0) * row_bytes, v >= 0 ? 16 : 0);
             }
             asm volatile("cp.async.commit_group;" ::: "memory");
             asm volatile("cp.async.wait_group 0;" ::: "memory");
@@ -1444,7 +1445,6 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const Params 
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512));
     }
 }
-
 // Rows of the packed buffer past the last sequence belong to no query tile; zero them so that the
 // output never carries uninitialised memory (the reference returns zeros there, zeros_like(V)).
 __global__ void zero_tail_kernel(void* out, const int32_t* offsets, int B, int64_t n_tokens, int64_t row_bytes) {
