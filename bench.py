@@ -201,6 +201,9 @@ class Workload:
     def cpu_baseline(self):             # (cpu_baseline dict, parity dict) or (None, None)
         return None, None
 
+    def static_config(self):            # the keys of config() that need no device: shared with the reference arm
+        return {"workload": self.name}
+
 
 class LargeDecode(Workload):
     name, metric, unit, dtype = "large_decode", "paged_decode_kv_read_bandwidth", "TB/s", "f16"
@@ -271,9 +274,15 @@ class LargeDecode(Workload):
     def traffic(self):
         return DECODE_TRAFFIC_RATIO * self.units_per_step_rank()
 
+    LABEL = "large_batch_paged_decode"
+
+    def static_config(self):
+        return {"workload": self.LABEL, "batch": self.args.batch or self.B, "heads": self.H, "head_dim": self.D,
+                "ctx_range": [self.LO, self.HI]}
+
     def config(self):
         per = self.units_per_step_rank()
-        return {"workload": "large_batch_paged_decode", "batch": self.Bn, "heads": self.H, "head_dim": self.D,
+        return {"workload": self.LABEL, "batch": self.Bn, "heads": self.H, "head_dim": self.D,
                 "ctx_range": [self.LO, self.HI], "context_tokens": self.T, "kv_bytes_total": per * self.world,
                 "kv_bytes_per_gpu": per, "sharding": f"heads/{self.world} per GPU, no collective",
                 "chunk": self.chunk, "l2": f"inputs larger than L2 ({per / 1e9:.1f} GB of KV per GPU per step)"}
@@ -348,9 +357,11 @@ class SmallDecode(LargeDecode):
             self.Kc, self.Vc = self.pools[self.i % self.POOLS]
         super()._call(stages)
 
+    LABEL = "small_batch_paged_decode"
+
     def config(self):
         c = super().config()
-        c.update(workload="small_batch_paged_decode", sharding="replicas only",
+        c.update(workload=self.LABEL, sharding="replicas only",
                  l2=f"{self.POOLS} KV pools of {self.SLOTS} slots rotated: {self.POOLS} x "
                     f"{self.units_per_step_rank() / 1e6:.0f} MB touched cyclically (> 126 MB L2)")
         return c
@@ -418,6 +429,10 @@ class Rope(Workload):
     def kernel_name(self):
         return "rope_vec8_kernel<half2>"
 
+    def static_config(self):
+        return {"workload": "rotary_embedding", "tokens": self.N, "heads": self.H, "head_dim": self.D,
+                "positions": [0, self.MAXPOS - 1]}
+
     def config(self):
         return {"workload": "rotary_embedding", "tokens": self.N, "heads": self.H, "head_dim": self.D,
                 "positions": [0, self.MAXPOS - 1], "sharding": "replicas only",
@@ -479,6 +494,10 @@ class Prefill(Workload):
 
     def kernel_name(self):
         return "prefill_tc2p_kernel<bf16>"
+
+    def static_config(self):
+        return {"workload": "packed_varlen_causal_prefill", "sequences": self.args.batch or self.B, "heads": self.H,
+                "head_dim": self.D, "len_range": [self.LO, self.HI]}
 
     def config(self):
         return {"workload": "packed_varlen_causal_prefill", "sequences": len(self.lens_), "heads": self.H,
@@ -569,6 +588,10 @@ class PagedPrefill(Prefill):
 
     def kernel_name(self):
         return "paged_prefill_tc_kernel<bf16>"
+
+    def static_config(self):
+        return {"workload": "chunked_prefill_through_slot_table", "sequences": self.args.batch or self.B,
+                "heads": self.H, "head_dim": self.D, "kv_len_range": [self.LO, self.HI], "chunk": self.CHUNK}
 
     def config(self):
         return {"workload": "chunked_prefill_through_slot_table", "sequences": len(self.lens_), "heads": self.H,
@@ -689,6 +712,10 @@ class Fp8Split(Workload):
     def kernel_name(self):
         return "paged_decode_mha_kernel<half,e4m3,128,heads-per-warp>"
 
+    def static_config(self):
+        return {"workload": "long_context_fp8_kv_paged_decode", "batch": self.args.batch or self.B, "heads": self.H,
+                "head_dim": self.D, "ctx_range": [self.LO, self.HI]}
+
     def config(self):
         per = self.units_per_step_rank()
         return {"workload": "long_context_fp8_kv_paged_decode", "batch": self.Bn, "heads": self.H,
@@ -732,8 +759,8 @@ def run_reference(args, W):
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
         "scaling": W.scaling, "vs_baseline": None, "dtype": W.dtype, "data": "synthetic",
         "tokens_per_s": seqs / sec,
-        "config": {"workload": W.name, "note": "torch CPU path (oracle restatement of the reference's test-side "
-                                               "math), " + sample},
+        "config": dict(w.static_config(), note="torch CPU path (oracle restatement of the reference's test-side "
+                                                "math), " + sample),
         "cpu_baseline": {"value": value, "unit": W.unit, "cores": torch.get_num_threads(), "kind": "port",
                          "sample": sample, "torch": torch.__version__},
         "e2e": {"value": value, "unit": W.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
