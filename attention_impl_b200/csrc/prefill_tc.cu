@@ -1,20 +1,13 @@
-// Packed (varlen) causal prefill on the 5th-generation tensor cores: tcgen05.mma with TMEM
-// accumulators, operands staged in shared memory by TMA (cp.async.bulk.tensor, 128-byte swizzle).
+// Causal prefill on the 5th-generation tensor cores: tcgen05.mma with TMEM accumulators, operands
+// staged in shared memory by TMA (cp.async.bulk.tensor, 128-byte swizzle).
 //
 // Semantics: paged_attention_kernel.cu:15-98 of the reference (per sequence slice of the packed
 // buffer, key j visible to query i iff j <= i, softmax of scale*QK^T, O = P V), evaluated flash
-// style: S and P never leave the SM.
-//
-// One CTA = one 128-row query tile of one (sequence, head); it walks the key tiles 0..t of that
-// sequence (t = its own tile index, the diagonal tile is masked).
-//   warp 4      TMA producer: Q once, then K and V tiles into a 2-stage ring
-//   warp 5      MMA issuer (one lane): S = Q K^T  (8 x tcgen05.mma 128x128x16, both operands
-//               K-major) into TMEM columns [0,128); after the softmax warps have written P:
-//               PV = P V (A = P from shared memory, B = V as an MN-major operand) into [128,256)
-//   warps 0-3   softmax: thread r owns row r (TMEM lane r): tcgen05.ld of the S row, running max
-//               and sum in the log2 domain, P rounded to the input type and stored to shared
-//               memory in the swizzled K-major layout, then the PV tile is read back and added to
-//               a register accumulator  o = o*alpha + pv.  Final o/l is stored straight to global.
+// style: S and P never leave the SM.  Three kernels share one pipeline (a pair of 128-row query
+// tiles per work item, one softmax thread per query row, P and O resident in tensor memory):
+//   prefill_tc2_kernel       one CTA per pair (ATTN_B200_PREFILL_VERSION=2, kept for A/B runs)
+//   prefill_tc2p_kernel      persistent: one CTA per SM draws pairs from a counter (the default)
+//   paged_prefill_tc_kernel  K/V gathered through a slot table (chunked / prefix-cached prefill)
 // Every mbarrier wait is bounded (about one second of SM clocks); on expiry the kernel raises
 // ATTN_B200_FLAG_TIMEOUT, all roles leave their loops, outstanding copies are given a bounded
 // wait, TMEM is freed and the CTA returns.  CTAs that start after a timeout exit at once.
@@ -36,18 +29,6 @@ constexpr int HD = 128;          // head_dim
 constexpr int SUB_BYTES = 128 * 128;   // one [128 rows x 64 elements] swizzled sub-tile (16-bit elements)
 constexpr int TILE_BYTES = 2 * SUB_BYTES;
 constexpr int STAGES = 2;
-constexpr int THREADS = 192;
-struct SmemLayout {
-    alignas(1024) unsigned char q[TILE_BYTES];
-    alignas(1024) unsigned char p[TILE_BYTES];
-    alignas(1024) unsigned char k[STAGES][TILE_BYTES];
-    alignas(1024) unsigned char v[STAGES][TILE_BYTES];
-    alignas(8) unsigned long long q_full, s_full, p_full, o_full, o_empty;
-    unsigned long long k_full[STAGES], v_full[STAGES], kv_empty[STAGES];
-    unsigned int tmem_base;
-    int abort;
-};
-
 struct Params {
     const int32_t* offsets;
     void* out;
@@ -59,217 +40,8 @@ struct Params {
     int32_t* err_flag;
 };
 
-template <typename T>
-__global__ void __launch_bounds__(THREADS, 1)
-prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                  const __grid_constant__ CUtensorMap map_v, const Params p) {
-    extern __shared__ unsigned char smem_raw[];
-    SmemLayout& sm = *reinterpret_cast<SmemLayout*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int b = blockIdx.z, h = blockIdx.y;
-    const int t = p.n_qtiles - 1 - (int)blockIdx.x;        // heavy (late) tiles first
-    const int64_t seq_beg = b ? p.offsets[b - 1] : 0;
-    const int64_t seq_end = p.offsets[b];
-    if (seq_beg < 0 || seq_end < seq_beg || seq_end > p.n_tokens) {
-        if (p.err_flag && threadIdx.x == 0) atomicOr(p.err_flag, ATTN_B200_FLAG_BAD_OFFSETS);
-        return;
-    }
-    const int L = (int)(seq_end - seq_beg);
-    const int q0 = t * BM;
-    if (q0 >= L) return;
-    if (*(volatile int*)&g_abort) return;
-    const int n_kv = t + 1;
-    volatile int* cta_abort = &sm.abort;
-
-    if (threadIdx.x == 0) {
-        mbar_init(&sm.q_full, 1);
-        mbar_init(&sm.s_full, 1);
-        mbar_init(&sm.p_full, 128);
-        mbar_init(&sm.o_full, 1);
-        mbar_init(&sm.o_empty, 128);
-        for (int s = 0; s < STAGES; ++s) {
-            mbar_init(&sm.k_full[s], 1);
-            mbar_init(&sm.v_full[s], 1);
-            mbar_init(&sm.kv_empty[s], 1);
-        }
-        sm.abort = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    if (warp == 5) {   // TMEM: 256 columns (S and PV accumulators)
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(256));
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem = sm.tmem_base;
-    const int col0 = h * HD;
-
-    int issued_k[STAGES] = {0, 0};   // producer bookkeeping for the drain on abort
-    if (warp == 4) {
-        // ------------------------------------------------------------------ TMA producer
-        if (lane == 0) {
-            mbar_expect_tx(&sm.q_full, TILE_BYTES);
-            tma_load_2d(sm.q, &map_q, col0, (int)(seq_beg + q0), &sm.q_full);
-            tma_load_2d(sm.q + SUB_BYTES, &map_q, col0 + 64, (int)(seq_beg + q0), &sm.q_full);
-            for (int j = 0; j < n_kv; ++j) {
-                const int s = j & 1;
-                if (j >= STAGES && !mbar_wait(&sm.kv_empty[s], ((j - STAGES) >> 1) & 1, cta_abort, p.err_flag)) break;
-                const int row = (int)(seq_beg + (int64_t)j * BN);
-                mbar_expect_tx(&sm.k_full[s], TILE_BYTES);
-                tma_load_2d(sm.k[s], &map_k, col0, row, &sm.k_full[s]);
-                tma_load_2d(sm.k[s] + SUB_BYTES, &map_k, col0 + 64, row, &sm.k_full[s]);
-                mbar_expect_tx(&sm.v_full[s], TILE_BYTES);
-                tma_load_2d(sm.v[s], &map_v, col0, row, &sm.v_full[s]);
-                tma_load_2d(sm.v[s] + SUB_BYTES, &map_v, col0 + 64, row, &sm.v_full[s]);
-                issued_k[s] = j + 1;
-            }
-        }
-    } else if (warp == 5) {
-        // ------------------------------------------------------------------ MMA issuer
-        constexpr uint32_t fmt = sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
-        constexpr uint32_t idesc_qk = (1u << 4) | (fmt << 7) | (fmt << 10) | ((BN >> 3) << 17) | ((BM >> 4) << 24);
-        constexpr uint32_t idesc_pv = idesc_qk | (1u << 16);   // B (= V) is MN-major
-        const uint32_t q_addr = smem_u32(sm.q), p_addr = smem_u32(sm.p);
-        bool ok = mbar_wait(&sm.q_full, 0, cta_abort, p.err_flag);
-        for (int j = 0; ok && j < n_kv; ++j) {
-            const int s = j & 1;
-            const uint32_t ph = (j >> 1) & 1;
-            if (!(ok = mbar_wait(&sm.k_full[s], ph, cta_abort, p.err_flag))) break;
-            tc_fence_after();
-            if (lane == 0) {
-                const uint32_t k_addr = smem_u32(sm.k[s]);
-#pragma unroll
-                for (int kk = 0; kk < HD / 16; ++kk) {
-                    const uint32_t off = (kk >> 2) * SUB_BYTES + (kk & 3) * 32;
-                    umma_f16(tmem, smem_desc(q_addr + off, 16, 1024), smem_desc(k_addr + off, 16, 1024), idesc_qk, kk > 0);
-                }
-                umma_commit(&sm.s_full);
-            }
-            __syncwarp();
-            if (!(ok = mbar_wait(&sm.p_full, j & 1, cta_abort, p.err_flag))) break;
-            if (!(ok = mbar_wait(&sm.v_full[s], ph, cta_abort, p.err_flag))) break;
-            if (j > 0 && !(ok = mbar_wait(&sm.o_empty, (j - 1) & 1, cta_abort, p.err_flag))) break;
-            tc_fence_after();
-            if (lane == 0) {
-                const uint32_t v_addr = smem_u32(sm.v[s]);
-#pragma unroll
-                for (int kk = 0; kk < BN / 16; ++kk) {
-                    const uint32_t a_off = (kk >> 2) * SUB_BYTES + (kk & 3) * 32;
-                    umma_f16(tmem + 128, smem_desc(p_addr + a_off, 16, 1024),
-                             smem_desc(v_addr + kk * 2048, SUB_BYTES, 1024), idesc_pv, kk > 0);
-                }
-                umma_commit(&sm.o_full);
-                umma_commit(&sm.kv_empty[s]);
-            }
-            __syncwarp();
-        }
-    } else {
-        // ------------------------------------------------------------------ softmax warps 0-3
-        const int r = threadIdx.x;                       // row of the tile == TMEM lane
-        const uint32_t lane_addr = tmem + ((uint32_t)(warp * 32) << 16);
-        float m = -INFINITY, l = 0.f;
-        float o[HD];
-#pragma unroll
-        for (int i = 0; i < HD; ++i) o[i] = 0.f;
-        bool ok = true;
-        for (int j = 0; j < n_kv; ++j) {
-            if (!(ok = mbar_wait(&sm.s_full, j & 1, cta_abort, p.err_flag))) break;
-            tc_fence_after();
-            const bool diag = (j == t);
-            float mx = -INFINITY;
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                float sv[32];
-                tmem_ld32(lane_addr + c * 32, sv);
-#pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const bool vis = !diag || (c * 32 + i <= r);
-                    mx = fmaxf(mx, vis ? sv[i] : -INFINITY);
-                }
-            }
-            const float m_new = fmaxf(m, mx * p.scale_log2);
-            const float alpha = fast_exp2(m - m_new);
-            float rs = 0.f;
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                float sv[32];
-                tmem_ld32(lane_addr + c * 32, sv);
-                uint32_t pk[16];
-#pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    const bool v0 = !diag || (c * 32 + i <= r), v1 = !diag || (c * 32 + i + 1 <= r);
-                    const float p0 = v0 ? fast_exp2(fmaf(sv[i], p.scale_log2, -m_new)) : 0.f;
-                    const float p1 = v1 ? fast_exp2(fmaf(sv[i + 1], p.scale_log2, -m_new)) : 0.f;
-                    rs += p0 + p1;
-                    pk[i >> 1] = pack2<T>(p0, p1);
-                }
-                // keys [c*32, c*32+32) -> sub-tile c>>1, 16-byte chunks (c&1)*4 .. +4, xor-swizzled by row
-                unsigned char* rowp = sm.p + (c >> 1) * SUB_BYTES + r * 128;
-#pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4) {
-                    const int chunk = ((c & 1) * 4 + q4) ^ (r & 7);
-                    *reinterpret_cast<uint4*>(rowp + chunk * 16) =
-                        make_uint4(pk[q4 * 4], pk[q4 * 4 + 1], pk[q4 * 4 + 2], pk[q4 * 4 + 3]);
-                }
-            }
-            l = l * alpha + rs;
-            m = m_new;
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            tc_fence_before();
-            mbar_arrive(&sm.p_full);
-            if (!(ok = mbar_wait(&sm.o_full, j & 1, cta_abort, p.err_flag))) break;
-            tc_fence_after();
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                float pv[32];
-                tmem_ld32(lane_addr + 128 + c * 32, pv);
-#pragma unroll
-                for (int i = 0; i < 32; ++i) o[c * 32 + i] = fmaf(o[c * 32 + i], alpha, pv[i]);
-            }
-            tc_fence_before();
-            mbar_arrive(&sm.o_empty);
-        }
-        if (ok && q0 + r < L) {
-            const float inv = 1.f / l;
-            const int64_t row = seq_beg + q0 + r;
-            if (p.out_f32) {
-                float4* dst = reinterpret_cast<float4*>((float*)p.out + (row * p.H + h) * HD);
-#pragma unroll
-                for (int i = 0; i < HD / 4; ++i)
-                    dst[i] = make_float4(o[4 * i] * inv, o[4 * i + 1] * inv, o[4 * i + 2] * inv, o[4 * i + 3] * inv);
-            } else {
-                uint4* dst = reinterpret_cast<uint4*>((T*)p.out + (row * p.H + h) * HD);
-#pragma unroll
-                for (int i = 0; i < HD / 8; ++i)
-                    dst[i] = make_uint4(pack2<T>(o[8 * i] * inv, o[8 * i + 1] * inv), pack2<T>(o[8 * i + 2] * inv, o[8 * i + 3] * inv),
-                                        pack2<T>(o[8 * i + 4] * inv, o[8 * i + 5] * inv), pack2<T>(o[8 * i + 6] * inv, o[8 * i + 7] * inv));
-            }
-        }
-    }
-    // ---------------------------------------------------------------------- teardown
-    if (warp == 4 && lane == 0 && sm.abort) {
-        // give copies that were issued but never consumed a bounded chance to land
-        const long long t0 = clock64();
-        for (int s = 0; s < STAGES; ++s) {
-            if (!issued_k[s]) continue;
-            const uint32_t ph = ((issued_k[s] - 1) >> 1) & 1;
-            while (!(mbar_try(&sm.k_full[s], ph) && mbar_try(&sm.v_full[s], ph)) && clock64() - t0 < WAIT_CYCLES) {}
-        }
-        while (!mbar_try(&sm.q_full, 0) && clock64() - t0 < WAIT_CYCLES) {}
-    }
-    tc_fence_before();
-    __syncthreads();
-    if (warp == 5) {
-        tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(256));
-    }
-}
-
-
 // =============================================================================================
-// Version 2: two query tiles per CTA, P kept in tensor memory, O accumulated in tensor memory.
+// The pair kernel: two query tiles per CTA, P kept in tensor memory, O accumulated in tensor memory.
 //
 //   warps 0-3 / 4-7   softmax warpgroup 0 / 1, one 128-row query tile each (rows q0.. / q0+128..)
 //   warp 8            TMA producer: both Q tiles, then K and V tiles into separate 2-stage rings
@@ -677,9 +449,9 @@ prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 
 
 // =============================================================================================
-// Persistent form of version 2.
+// Persistent form of the pair kernel.
 //
-// Version 2 spends about two of a CTA's ~ten key-tile periods outside its steady state: set-up and
+// The pair kernel spends about two of a CTA's ~ten key-tile periods outside its steady state: set-up and
 // the first TMA round trip before any softmax can run, the read-out of O at the end, and the last
 // key tile of the pair, which only the upper query tile needs (the other warpgroup idles).  Here
 // the grid is one CTA per SM and every CTA walks work items (a pair of query tiles of one
@@ -1014,177 +786,11 @@ prefill_tc2p_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 
 
 // =============================================================================================
-// Version 3: one 128-row query tile per CTA, TWO CTAs per SM.
-//
-// Same tensor-memory pipeline as version 2 (S -> P in place, O accumulated by the MMA, lazy
-// maximum) but each CTA owns a single query tile: 96 KB of shared memory (Q, one K tile, one V
-// tile), 256 TMEM columns (S, O), 256 threads.  Two such CTAs share an SM, so the second
-// warpgroup of version 2 becomes a second, independent CTA: one CTA's softmax overlaps the other's
-// MMAs as before, and in addition one CTA's prologue (TMEM allocation, first TMA loads) and
-// epilogue (O read-back and store) overlap the other's main loop, and a CTA never idles half of
-// its warps on the last key tile.  The price: K and V tiles are fetched from L2 once per query
-// tile instead of once per pair.
-//   warps 0-3  softmax (thread = query row)      warp 4  TMA: Q, then K_j / V_j as their tile frees
-//   warp 5     MMA issue (one spinning thread)   warps 6-7  idle (complete the register-donor warpgroup)
-// Registers: launched with 128 per thread (2 CTAs x 256 threads); 4 x 200 + 4 x 56 = 8 x 128.
-// =============================================================================================
-constexpr int THREADS3 = 256;
-
-struct SmemLayout3 {
-    alignas(1024) unsigned char q[TILE_BYTES];
-    alignas(1024) unsigned char k[TILE_BYTES];
-    alignas(1024) unsigned char v[TILE_BYTES];
-    alignas(8) unsigned long long q_full, s_full, p_half, p_full, o_full, k_full, k_empty, v_full, v_empty;
-    unsigned int tmem_base;
-    int abort;
-};
-
-template <typename T>
-__global__ void __launch_bounds__(THREADS3, 2)
-prefill_tc3_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                   const __grid_constant__ CUtensorMap map_v, const Params p) {
-    extern __shared__ unsigned char smem_raw[];
-    SmemLayout3& sm = *reinterpret_cast<SmemLayout3*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int b = blockIdx.z, h = blockIdx.y;
-    const int t = p.n_qtiles - 1 - (int)blockIdx.x;        // heavy (late) tiles first
-    const int64_t seq_beg = b ? p.offsets[b - 1] : 0;
-    const int64_t seq_end = p.offsets[b];
-    if (seq_beg < 0 || seq_end < seq_beg || seq_end > p.n_tokens) {
-        if (p.err_flag && threadIdx.x == 0) atomicOr(p.err_flag, ATTN_B200_FLAG_BAD_OFFSETS);
-        return;
-    }
-    const int L = (int)(seq_end - seq_beg);
-    const int q0 = t * BM;
-    if (q0 >= L) return;
-    if (*(volatile int*)&g_abort) return;
-    const int n_kv = t + 1;
-    volatile int* cta_abort = &sm.abort;
-
-    if (threadIdx.x == 0) {
-        mbar_init(&sm.q_full, 1);
-        mbar_init(&sm.s_full, 1);
-        mbar_init(&sm.p_half, 128);
-        mbar_init(&sm.p_full, 128);
-        mbar_init(&sm.o_full, 1);
-        mbar_init(&sm.k_full, 1);
-        mbar_init(&sm.k_empty, 1);
-        mbar_init(&sm.v_full, 1);
-        mbar_init(&sm.v_empty, 1);
-        sm.abort = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    if (warp == 5) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(256));
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem = sm.tmem_base;
-    const int col0 = h * HD;
-
-    int issued = 0;
-    if (warp >= 4) {
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
-        if (warp == 4) {
-            // -------------------------------------------------------------- TMA producer
-            if (lane == 0) {
-                mbar_expect_tx(&sm.q_full, TILE_BYTES);
-                tma_load_2d(sm.q, &map_q, col0, (int)(seq_beg + q0), &sm.q_full);
-                tma_load_2d(sm.q + SUB_BYTES, &map_q, col0 + 64, (int)(seq_beg + q0), &sm.q_full);
-                for (int j = 0; j < n_kv; ++j) {
-                    const int row = (int)(seq_beg + (int64_t)j * BN);
-                    if (j > 0 && !mbar_wait(&sm.k_empty, (j - 1) & 1, cta_abort, p.err_flag)) break;
-                    mbar_expect_tx(&sm.k_full, TILE_BYTES);
-                    tma_load_2d(sm.k, &map_k, col0, row, &sm.k_full);
-                    tma_load_2d(sm.k + SUB_BYTES, &map_k, col0 + 64, row, &sm.k_full);
-                    if (j > 0 && !mbar_wait(&sm.v_empty, (j - 1) & 1, cta_abort, p.err_flag)) { issued = 2 * j + 1; break; }
-                    mbar_expect_tx(&sm.v_full, TILE_BYTES);
-                    tma_load_2d(sm.v, &map_v, col0, row, &sm.v_full);
-                    tma_load_2d(sm.v + SUB_BYTES, &map_v, col0 + 64, row, &sm.v_full);
-                    issued = 2 * j + 2;          // K tiles issued = (issued+1)/2, V tiles = issued/2
-                }
-            }
-        } else if (warp == 5) {
-            // -------------------------------------------------------------- MMA issuer
-            constexpr uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
-            constexpr uint32_t idesc_qk = (1u << 4) | (fmt << 7) | (fmt << 10) | ((BN >> 3) << 17) | ((BM >> 4) << 24);
-            constexpr uint32_t idesc_pv = idesc_qk | (1u << 16);   // B (= V) is MN-major, same type as P
-            if (elect_one()) {
-                const uint64_t qd = smem_desc(smem_u32(sm.q), 16, 1024), kd = smem_desc(smem_u32(sm.k), 16, 1024);
-                const uint64_t vd = smem_desc(smem_u32(sm.v), SUB_BYTES, 1024);
-                auto issue_qk = [&]() {
-#pragma unroll
-                    for (int kk = 0; kk < HD / 16; ++kk) {
-                        const uint32_t off16 = ((kk >> 2) * SUB_BYTES + (kk & 3) * 32) >> 4;
-                        umma_f16(tmem, qd + off16, kd + off16, idesc_qk, kk > 0);
-                    }
-                    umma_commit(&sm.s_full);
-                    umma_commit(&sm.k_empty);
-                };
-                bool ok = mbar_wait_spin(&sm.q_full, 0, cta_abort, p.err_flag) &&
-                          mbar_wait_spin(&sm.k_full, 0, cta_abort, p.err_flag);
-                if (ok) {
-                    tc_fence_after();
-                    issue_qk();
-                }
-                for (int j = 0; ok && j < n_kv; ++j) {
-                    if (!(ok = mbar_wait_spin(&sm.p_half, j & 1, cta_abort, p.err_flag))) break;
-                    if (!(ok = mbar_wait_spin(&sm.v_full, j & 1, cta_abort, p.err_flag))) break;
-                    tc_fence_after();
-                    umma_f16_ts(tmem + 128, tmem, vd, idesc_pv, j > 0 ? 1u : 0u);
-#pragma unroll
-                    for (int kk = 1; kk < BN / 32; ++kk)
-                        umma_f16_ts(tmem + 128, tmem + kk * 8, vd + ((kk * 2048) >> 4), idesc_pv, 1u);
-                    if (!(ok = mbar_wait_spin(&sm.p_full, j & 1, cta_abort, p.err_flag))) break;
-                    tc_fence_after();
-#pragma unroll
-                    for (int kk = BN / 32; kk < BN / 16; ++kk)
-                        umma_f16_ts(tmem + 128, tmem + kk * 8, vd + ((kk * 2048) >> 4), idesc_pv, 1u);
-                    umma_commit(&sm.o_full);
-                    umma_commit(&sm.v_empty);
-                    if (j + 1 < n_kv) {
-                        if (!(ok = mbar_wait_spin(&sm.k_full, (j + 1) & 1, cta_abort, p.err_flag))) break;
-                        tc_fence_after();
-                        issue_qk();
-                    }
-                }
-            }
-            __syncwarp();
-        }
-    } else {
-        // ------------------------------------------------------------------ softmax
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 200;");
-        const int r = threadIdx.x;
-        const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
-        softmax_row<T, 2>(&sm.s_full, &sm.p_half, &sm.p_full, &sm.o_full, lane_base, lane_base + 128, n_kv, t * BM + r, r, 0, p, cta_abort,
-                       q0 + r < L, seq_beg + q0 + r, h);
-    }
-    // ---------------------------------------------------------------------- teardown
-    if (warp == 4 && lane == 0 && sm.abort) {
-        const long long t0 = clock64();
-        while (!mbar_try(&sm.q_full, 0) && clock64() - t0 < WAIT_CYCLES) {}
-        const int nk_issued = (issued + 1) / 2, nv_issued = issued / 2;
-        if (nk_issued > 0) while (!mbar_try(&sm.k_full, (nk_issued - 1) & 1) && clock64() - t0 < WAIT_CYCLES) {}
-        if (nv_issued > 0) while (!mbar_try(&sm.v_full, (nv_issued - 1) & 1) && clock64() - t0 < WAIT_CYCLES) {}
-    }
-    tc_fence_before();
-    __syncthreads();
-    if (warp == 5) {
-        tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(256));
-    }
-}
-
-
-// =============================================================================================
-// Paged form of version 2: the K and V tiles are GATHERED through the slot table.
+// Paged form of the pair kernel: the K and V tiles are GATHERED through the slot table.
 //
 // Chunked / prefix-cached prefill: sequence b's query rows are its last q_len tokens (packed in q),
 // its keys are the pool rows slots[kv_beg .. kv_beg + kv_len) (prefix and chunk); query i sees key
-// j iff j <= kv_len - q_len + i.  Everything downstream of shared memory is version 2 (two query
+// j iff j <= kv_len - q_len + i.  Everything downstream of shared memory is the pair kernel (two query
 // tiles per CTA, S -> P in tensor memory, O accumulated by the MMA).  What changes is the producer
 // of K/V: a fourth warpgroup (warps 12-13 for K, 14-15 for V) copies the 128 rows of a tile with
 // 16-byte cp.async (16 consecutive lanes = one 256-byte row, so a warp instruction reads two whole
@@ -1517,18 +1123,14 @@ int prefill_tc_launch(const void* q, const void* k, const void* v, const int32_t
         (rc = make_map(&mv, v, n_tokens, H, dtype)))
         return rc;
     static const int version = [] { const char* e = getenv("ATTN_B200_PREFILL_VERSION"); return e ? atoi(e) : 6; }();
-    const bool use_v1 = version == 1, use_v3 = version == 3, use_p = version == 6;
-    const int rows_per_cta = (use_v1 || use_v3) ? BM : 2 * BM;
-    const int smem = (int)(use_v1 ? sizeof(SmemLayout) : use_v3 ? sizeof(SmemLayout3) : sizeof(SmemLayout2)) + 1024;
-    Params p{offsets, out, B, H, n_tokens, (max_len + rows_per_cta - 1) / rows_per_cta, scale * kLog2e, out_f32,
-             err_flag};
-    dim3 grid(p.n_qtiles, H, B);
+    const bool persistent = version != 2;
+    Params p{offsets, out, B, H, n_tokens, (max_len + 2 * BM - 1) / (2 * BM), scale * kLog2e, out_f32, err_flag};
     void* abort_addr = nullptr;
     cudaError_t e = cudaGetSymbolAddress(&abort_addr, g_abort);
     if (e != cudaSuccess) return (int)e;
     if ((e = cudaMemsetAsync(abort_addr, 0, sizeof(int), st)) != cudaSuccess) return (int)e;
     zero_tail_kernel<<<64, 256, 0, st>>>(out, offsets, B, n_tokens, (int64_t)H * HD * (out_f32 ? 4 : 2));
-    if (use_p) {
+    if (persistent) {
         int dev = 0, n_sm = 0;
         if ((e = cudaGetDevice(&dev)) != cudaSuccess) return (int)e;
         if ((e = cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return (int)e;
@@ -1553,38 +1155,16 @@ int prefill_tc_launch(const void* q, const void* k, const void* v, const int32_t
         }
         return (int)cudaGetLastError();
     }
-    if (use_v3) {
-        if (dtype == ATTN_B200_BF16) {
-            if ((e = cudaFuncSetAttribute(prefill_tc3_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) != cudaSuccess)
-                return (int)e;
-            prefill_tc3_kernel<__nv_bfloat16><<<grid, THREADS3, smem, st>>>(mq, mk, mv, p);
-        } else {
-            if ((e = cudaFuncSetAttribute(prefill_tc3_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) != cudaSuccess)
-                return (int)e;
-            prefill_tc3_kernel<__half><<<grid, THREADS3, smem, st>>>(mq, mk, mv, p);
-        }
-        return (int)cudaGetLastError();
-    }
-    if (!use_v1) {
-        if (dtype == ATTN_B200_BF16) {
-            if ((e = cudaFuncSetAttribute(prefill_tc2_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) != cudaSuccess)
-                return (int)e;
-            prefill_tc2_kernel<__nv_bfloat16><<<grid, THREADS2, smem, st>>>(mq, mk, mv, p);
-        } else {
-            if ((e = cudaFuncSetAttribute(prefill_tc2_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) != cudaSuccess)
-                return (int)e;
-            prefill_tc2_kernel<__half><<<grid, THREADS2, smem, st>>>(mq, mk, mv, p);
-        }
-        return (int)cudaGetLastError();
-    }
+    const int smem = (int)sizeof(SmemLayout2) + 1024;
+    dim3 grid(p.n_qtiles, H, B);
     if (dtype == ATTN_B200_BF16) {
-        if ((e = cudaFuncSetAttribute(prefill_tc_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) != cudaSuccess)
+        if ((e = cudaFuncSetAttribute(prefill_tc2_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) != cudaSuccess)
             return (int)e;
-        prefill_tc_kernel<__nv_bfloat16><<<grid, THREADS, smem, st>>>(mq, mk, mv, p);
+        prefill_tc2_kernel<__nv_bfloat16><<<grid, THREADS2, smem, st>>>(mq, mk, mv, p);
     } else {
-        if ((e = cudaFuncSetAttribute(prefill_tc_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) != cudaSuccess)
+        if ((e = cudaFuncSetAttribute(prefill_tc2_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) != cudaSuccess)
             return (int)e;
-        prefill_tc_kernel<__half><<<grid, THREADS, smem, st>>>(mq, mk, mv, p);
+        prefill_tc2_kernel<__half><<<grid, THREADS2, smem, st>>>(mq, mk, mv, p);
     }
     return (int)cudaGetLastError();
 }
