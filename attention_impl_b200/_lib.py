@@ -38,6 +38,7 @@ PROTOTYPES = {
     "attn_b200_peer_push_ctas": (_i32, [_sz]),
     "attn_b200_peer_push": (_i32, [_vp, _sz, _vp, _vp, _i32, _vp]),
     "attn_b200_wait_flags": (_i32, [_vp, _i32, _i32, _vp, _vp]),
+    "attn_b200_wait_flags_consume": (_i32, [_vp, _i32, _i32, _vp, _vp]),
     "attn_b200_lse_combine": (_i32, [_vp, _i32, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _f32, _i32, _vp]),
     "attn_b200_varlen_prefill": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i64, _i32, _i32, _i32, _f32,
                                         _i32, _i32, _i32, _vp, _vp]),

@@ -46,15 +46,21 @@ peer_push_kernel(const PushParams p) {
 }
 
 // One thread per counter; gives up after kWaitCycles and raises ATTN_B200_FLAG_TIMEOUT.
-__global__ void wait_flags_kernel(const int32_t* flags, int n, int32_t expected, int32_t* err_flag) {
+// With `consume` the thread takes `expected` off its counter once it has been reached (system-scope
+// atomic: peers may already be adding the arrivals of their next push), so that the same `expected`
+// serves every step and the launch can be replayed from a CUDA graph.
+__global__ void wait_flags_kernel(int32_t* flags, int n, int32_t expected, int32_t* err_flag, int consume) {
     const int i = threadIdx.x;
     if (i >= n) return;
-    const volatile int32_t* f = flags + i;
+    int32_t* f = flags + i;
     const long long t0 = clock64();
     while (true) {
         int32_t v;
         asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
-        if (v - expected >= 0) break;
+        if (v - expected >= 0) {
+            if (consume) atomicSub_system(f, expected);
+            break;
+        }
         if (clock64() - t0 > kWaitCycles) {
             if (err_flag) atomicOr(err_flag, ATTN_B200_FLAG_TIMEOUT);
             break;
@@ -93,6 +99,13 @@ extern "C" int attn_b200_peer_push(const void* src, size_t n_bytes, void* const*
 extern "C" int attn_b200_wait_flags(const int32_t* flags, int n_flags, int32_t expected, int32_t* err_flag,
                                     void* stream) {
     if (!flags || n_flags <= 0 || n_flags > 32) return ATTN_B200_EINVAL;
-    wait_flags_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(flags, n_flags, expected, err_flag);
+    wait_flags_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(const_cast<int32_t*>(flags), n_flags, expected, err_flag, 0);
+    return (int)cudaGetLastError();
+}
+
+extern "C" int attn_b200_wait_flags_consume(int32_t* flags, int n_flags, int32_t count, int32_t* err_flag,
+                                            void* stream) {
+    if (!flags || n_flags <= 0 || n_flags > 32 || count <= 0) return ATTN_B200_EINVAL;
+    wait_flags_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(flags, n_flags, count, err_flag, 1);
     return (int)cudaGetLastError();
 }

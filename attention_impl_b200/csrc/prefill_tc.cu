@@ -53,9 +53,9 @@ struct Params {
 // in the input type, two per 32-bit column; the PV MMA takes A from tensor memory and B = V from
 // shared memory.  O is
 // accumulated by the MMA itself.  The running maximum used for P is only advanced when a row's
-// new maximum exceeds it by more than 1 (fp16 inputs) or 4 (bf16 inputs) in the log2 domain, so P
-// stays small; only then is O read back,
-// scaled and written again (rare after the first tiles).  The true maximum never enters the result:
+// new maximum exceeds it by more than 8 in the log2 domain, so P stays below 2^8; only then is O
+// read back, scaled and written again (rare after the first tiles).  The true maximum never enters
+// the result:
 // O and l are consistent with the reference maximum, and O/l is formed in the epilogue.
 // =============================================================================================
 #ifdef ATTN_B200_TRACE
@@ -96,9 +96,8 @@ __device__ __forceinline__ void softmax_row(unsigned long long* s_full, unsigned
     // signalled once the accumulator has been read out and may be overwritten by the next item.
     {
         float m_ref = -INFINITY, l = 0.f;
-        // P <= 2^kLazy.  On the fp16 path the exponent argument passes through fp16: keeping it
-        // below 1 keeps its rounding below the rounding of P itself.
-        constexpr float kLazy = std::is_same<T, __nv_bfloat16>::value ? 8.f : 1.f;
+        // P <= 2^kLazy: far inside the range of fp16 and bf16, and O is rescaled rarely.
+        constexpr float kLazy = 8.f;
         bool ok = true;
         for (int j = 0; j < nk; ++j) {
             if (r == 0) TRACE(trace_role, j, 0);
@@ -149,42 +148,13 @@ __device__ __forceinline__ void softmax_row(unsigned long long* s_full, unsigned
                 m_ref = m_new;
             }
             if (r == 0) TRACE(trace_role, j, 3);
-            // P = 2^(s*scale - m_ref): the exponent argument is formed in fp32, packed to f16x2 and
-            // passed through the packed ex2 of the special-function unit (two results per
-            // operation).  fp16 inputs: that result is P itself and row sums run over eight short
-            // fp16x2 chains before widening.  bf16 inputs: A and B of one MMA must share a type, and
-            // widening + re-packing the f16x2 result costs more issue slots than it saves, so that
-            // path uses the fp32 ex2.
+            // P = 2^(s*scale - m_ref), rounded to the input type.  (fp16 inputs once took the packed
+            // ex2.approx.f16x2 with fp16 row sums: its two results per operation cost the
+            // special-function unit as much as two fp32 ex2, and the fp32 form measured 842 against
+            // 756 TFLOP/s.)
             float rs = 0.f;
-            if constexpr (std::is_same<T, __half>::value) {
-                __half2 hs[8];
-#pragma unroll
-                for (int c = 0; c < 2; ++c) {           // 64 keys -> 32 packed columns per store
-                    uint32_t pk[32];
-#pragma unroll
-                    for (int i = 0; i < 64; i += 2) {
-                        const float x0 = fmaf(sv[c * 64 + i], p.scale_log2, -m_ref);
-                        const float x1 = fmaf(sv[c * 64 + i + 1], p.scale_log2, -m_ref);
-                        const uint32_t e = ex2_f16x2(pack2<__half>(x0, x1));
-                        pk[i >> 1] = e;
-                        const __half2 eh = *reinterpret_cast<const __half2*>(&e);
-                        const int g = (i >> 1) & 7;
-                        hs[g] = (c == 0 && i < 16) ? eh : __hadd2(hs[g], eh);
-                    }
-                    tmem_st32(s_addr + c * 32, pk);
-                    if (c == 0 && p_half) {      // keys 0..63 of P are in place: their P.V steps may start
-                        tmem_st_wait();
-                        tc_fence_before();
-                        mbar_arrive(p_half);
-                    }
-                }
-#pragma unroll
-                for (int g = 0; g < 8; g += 2) {
-                    const float2 a = __half22float2(hs[g]), b2 = __half22float2(hs[g + 1]);
-                    rs += (a.x + a.y) + (b2.x + b2.y);
-                }
-            } else {
-                // bf16 inputs: fp32 ex2, the remaining fp32 arithmetic as packed pairs (f32x2).  A
+            {
+                // fp32 ex2, the remaining fp32 arithmetic as packed pairs (f32x2).  A
                 // warp's 128 exponentials occupy the special-function unit for 1024 clocks (4 lanes
                 // per clock per scheduler), so kPolyOf8 of every 8 elements take a cubic on the
                 // FMA pipe instead (2 in the packed kernels; 0 in the paged kernel, whose gather warps

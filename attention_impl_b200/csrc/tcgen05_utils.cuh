@@ -156,13 +156,6 @@ __device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, ui
         ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(acc), "r"(0u) : "memory");
 }
 
-// Two fp16 exponentials (base 2) in one special-function operation.
-__device__ __forceinline__ uint32_t ex2_f16x2(uint32_t x) {
-    uint32_t y;
-    asm("ex2.approx.f16x2 %0, %1;" : "=r"(y) : "r"(x));
-    return y;
-}
-
 // Packed fp32 pairs (one instruction for two lanes' worth of fp32 FMA / ADD on sm_100).
 __device__ __forceinline__ void fma2(float& d0, float& d1, float a0, float a1, float b0, float b1, float c0, float c1) {
     asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmov.b64 rc, {%6, %7};\n\t"

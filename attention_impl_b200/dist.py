@@ -96,8 +96,11 @@ class KvSplitExchange:
     still combining) and ``G`` arrival counters per rank, mapped into every process with
     ``torch.distributed._symmetric_memory``.  Per step: local partial rows (two kernels), one push
     kernel (stores into every rank's slot ``[parity, my_rank]`` + one system-scope atomic per CTA on
-    that rank's counter for me), one wait kernel (bounded; raises ``FLAG_TIMEOUT`` in ``err_flag``),
-    then the usual LSE combine over the gathered rows.  No host synchronisation, no NCCL call.
+    that rank's counter for me), one wait kernel (bounded; raises ``FLAG_TIMEOUT`` in ``err_flag``;
+    it takes the arrivals it has waited for off the counters again, so every step has the same
+    arguments), then the usual LSE combine over the gathered rows.  No host synchronisation, no NCCL
+    call.  :meth:`capture` records the step for each of the two buffer halves as a CUDA graph and
+    :meth:`replay` launches them alternately.
     """
 
     def __init__(self, batch: int, num_heads: int, head_dim: int, device, group=None):
@@ -132,16 +135,44 @@ class KvSplitExchange:
         self.err_flag = torch.zeros(1, dtype=torch.int32, device=device)
 
     def decode(self, Q, K, V, K_cache_local, V_cache_local, local_indices, local_offsets, *, scale=None,
-               k_scale=None, v_scale=None, chunk=None) -> torch.Tensor:
+               k_scale=None, v_scale=None, chunk=None, _parity=None) -> torch.Tensor:
         from . import ops
         lib, check = self._lib.lib, self._lib.check
         part = ops.paged_decode_partial(Q, K_cache_local, V_cache_local, local_indices, local_offsets, self.H,
                                         scale=scale, chunk=chunk, k_scale=k_scale, v_scale=v_scale)
-        parity = self.step & 1
-        self.step += 1
+        parity = self.step & 1 if _parity is None else _parity
+        if _parity is None:
+            self.step += 1
         stream = torch.cuda.current_stream().cuda_stream
         check(lib.attn_b200_peer_push(part.data_ptr(), self.row_bytes, self._dst[parity], self._flag, self.G, stream),
               "peer_push")
-        check(lib.attn_b200_wait_flags(self.flags.data_ptr(), self.G, self.step * self.ctas_per_push,
-                                       self.err_flag.data_ptr(), stream), "wait_flags")
+        check(lib.attn_b200_wait_flags_consume(self.flags.data_ptr(), self.G, self.ctas_per_push,
+                                               self.err_flag.data_ptr(), stream), "wait_flags_consume")
         return ops.lse_combine(self.parts[parity], Q, K, V, num_heads=self.H, scale=scale)
+
+    def capture(self, Q, K, V, K_cache_local, V_cache_local, local_indices, local_offsets, **kw) -> None:
+        """Record the step on these (static) tensors as two CUDA graphs, one per buffer half.  The
+        caller refreshes the tensors' contents between replays; every rank must capture and replay in
+        step with the others (a replay is one exchange)."""
+        args = (Q, K, V, K_cache_local, V_cache_local, local_indices, local_offsets)
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):          # warm-up outside capture: two real steps, parity stays aligned
+            for _ in range(2):
+                self.decode(*args, **kw)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        self._graphs, self._graph_out = [], []
+        for parity in range(2):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                out = self.decode(*args, _parity=parity, **kw)
+            self._graphs.append(g)
+            self._graph_out.append(out)
+
+    def replay(self) -> torch.Tensor:
+        """One captured step; returns the graph's output tensor for this buffer half."""
+        parity = self.step & 1
+        self.step += 1
+        self._graphs[parity].replay()
+        return self._graph_out[parity]

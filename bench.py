@@ -682,7 +682,8 @@ class Fp8Split(Workload):
                                   for _ in range(3))
         self.chunk = A.ops.pick_chunk(self.Bn, self.H, self.D, self.T, dev)
         self.xchg = None
-        if self.args.exchange == "peer" and G > 1:
+        self.graphed = False
+        if self.args.exchange in ("peer", "peer_graph") and G > 1:
             self.xchg = adist.KvSplitExchange(self.Bn, self.H, self.D, dev)
             ref = adist.kv_split_decode(self.Q, self.K, self.V, self.Kc, self.Vc, self.ci, self.off, self.H,
                                         k_scale=self.ks, v_scale=self.vs, chunk=self.chunk)
@@ -694,8 +695,20 @@ class Fp8Split(Workload):
                 raise SystemExit(f"rank {r}: peer exchange differs from the NCCL path "
                                  f"(flag {int(self.xchg.err_flag.item())}, "
                                  f"max diff {(got.float() - ref.float()).abs().max().item()})")
+            if self.args.exchange == "peer_graph":      # the whole step replayed from a CUDA graph per buffer half
+                self.xchg.capture(self.Q, self.K, self.V, self.Kc, self.Vc, self.ci, self.off,
+                                  k_scale=self.ks, v_scale=self.vs, chunk=self.chunk)
+                for _ in range(3):
+                    got = self.xchg.replay()
+                torch.cuda.synchronize()
+                if int(self.xchg.err_flag.item()) != 0 or not torch.equal(got, ref):
+                    raise SystemExit(f"rank {r}: graph replay of the peer exchange differs from the NCCL path")
+                self.graphed = True
 
     def step(self):
+        if self.graphed:
+            self.out = self.xchg.replay()
+            return
         if self.xchg is not None:
             self.out = self.xchg.decode(self.Q, self.K, self.V, self.Kc, self.Vc, self.ci, self.off,
                                         k_scale=self.ks, v_scale=self.vs, chunk=self.chunk)
@@ -737,7 +750,8 @@ class Fp8Split(Workload):
                 "head_dim": self.D, "ctx_range": [self.LO, self.HI], "context_tokens": self.T_all,
                 "kv_bytes_total": 2.0 * self.T_all * self.H * self.D, "kv_bytes_per_gpu": per,
                 "sharding": f"each sequence's KV split {self.world} ways; [B,H,D+2] fp32 partials exchanged by "
-                            + ("peer stores over NVLink" if self.xchg is not None else "NCCL all-gather")
+                            + (("peer stores over NVLink" + (", step replayed from a CUDA graph" if self.graphed else ""))
+                               if self.xchg is not None else "NCCL all-gather")
                             + " + LSE combine", "chunk": self.chunk,
                 "l2": f"inputs larger than L2 ({per / 1e9:.1f} GB of KV per GPU per step)"}
 
@@ -895,7 +909,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="large_decode", choices=sorted(WORKLOADS))
     ap.add_argument("--batch", type=int, default=None, help="override the batch size (profiling a small case)")
-    ap.add_argument("--exchange", default="nccl", choices=["nccl", "peer"],
+    ap.add_argument("--exchange", default="nccl", choices=["nccl", "peer", "peer_graph"],
                     help="fp8_split: how the partial rows travel between ranks")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (profiling runs)")
     args = ap.parse_args()

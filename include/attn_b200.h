@@ -166,6 +166,12 @@ ATTN_B200_API int attn_b200_peer_push(const void* src, size_t n_bytes, void* con
                                       int32_t* const* peer_flag, int n_peers, void* stream);
 ATTN_B200_API int attn_b200_wait_flags(const int32_t* flags, int n_flags, int32_t expected, int32_t* err_flag,
                                        void* stream);
+/* The same wait, but every counter that has reached `count` has `count` taken off it again
+ * (system-scope atomic; arrivals of a peer's next push that are already there stay).  With
+ * count = attn_b200_peer_push_ctas(n_bytes) every step of an exchange uses the same arguments, so
+ * the step can be captured in a CUDA graph and replayed.  A peer may run at most one push ahead. */
+ATTN_B200_API int attn_b200_wait_flags_consume(int32_t* flags, int n_flags, int32_t count, int32_t* err_flag,
+                                               void* stream);
 
 /* Paged decode that allocates nothing and needs no scratch from the caller.
  * (No counterpart in the reference: its launcher allocates S, P and O itself with torch::zeros.)

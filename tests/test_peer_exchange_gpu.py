@@ -48,3 +48,40 @@ def test_wait_gives_up_with_a_status_instead_of_hanging():
     assert int(err.item()) & _lib.FLAG_TIMEOUT
     # the context is still usable
     assert float(torch.ones(4, device="cuda").sum().item()) == 4.0
+
+
+def test_consuming_wait_takes_its_count_off_and_keeps_early_arrivals():
+    """The graph-replayable wait: the same `count` every step; arrivals of a peer that is one push ahead
+    stay on the counter for the next step."""
+    from attention_impl_b200 import _lib
+    lib = _lib.lib
+    n = 64 * 32 * 130
+    src = torch.randn(n, device="cuda")
+    dst = torch.zeros(n, device="cuda")
+    flags = torch.zeros(4, dtype=torch.int32, device="cuda")
+    Ptr = ctypes.c_void_p * 1
+    d, f = Ptr(dst.data_ptr()), Ptr(flags[2:].data_ptr())
+    stream = torch.cuda.current_stream().cuda_stream
+    ctas = lib.attn_b200_peer_push_ctas(n * 4)
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    # the "peer" pushes twice before the local rank waits once: one step ahead
+    for _ in range(2):
+        _lib.check(lib.attn_b200_peer_push(src.data_ptr(), n * 4, d, f, 1, stream), "peer_push")
+    _lib.check(lib.attn_b200_wait_flags_consume(flags[2:].data_ptr(), 1, ctas, err.data_ptr(), stream), "wait")
+    torch.cuda.synchronize()
+    assert flags.tolist() == [0, 0, ctas, 0] and int(err.item()) == 0
+    _lib.check(lib.attn_b200_wait_flags_consume(flags[2:].data_ptr(), 1, ctas, err.data_ptr(), stream), "wait")
+    torch.cuda.synchronize()
+    assert flags.tolist() == [0, 0, 0, 0] and int(err.item()) == 0
+    # captured once, replayed three times with constant arguments
+    g = torch.cuda.CUDAGraph()
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        with torch.cuda.graph(g, stream=s):
+            st = s.cuda_stream
+            _lib.check(lib.attn_b200_peer_push(src.data_ptr(), n * 4, d, f, 1, st), "peer_push")
+            _lib.check(lib.attn_b200_wait_flags_consume(flags[2:].data_ptr(), 1, ctas, err.data_ptr(), st), "wait")
+    for _ in range(3):
+        g.replay()
+    torch.cuda.synchronize()
+    assert flags.tolist() == [0, 0, 0, 0] and int(err.item()) == 0 and torch.equal(dst, src)
