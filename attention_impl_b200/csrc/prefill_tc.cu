@@ -772,7 +772,7 @@ prefill_tc2p_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 // stream's 64 threads) once it has landed.  Grouped-query heads: query head h reads KV head h / (H / Hkv).
 // =============================================================================================
 constexpr int THREADS_PG = 512;
-constexpr int KSTAGES_PG = 2;    // K tiles in flight (3 fit in shared memory and were measured: no gain)
+constexpr int KSTAGES_PG = 2;    // K tiles in flight (3 fit in shared memory and were measured: 854 against 935 TFLOP/s)
 
 struct PagedTcParams {
     const int32_t* slots;
