@@ -345,7 +345,12 @@ paged_decode_mha_kernel(const DecodeParams p) {
 // group keeps its own softmax state.  G > 1 (grouped-query attention): the G query heads that share
 // a KV head are all served from the one copy of the row held in registers.
 template <typename QT, typename KVT, int D, int G>
-__global__ void __launch_bounds__(256, G == 1 ? 2 : 1)     // G = 1: 128 registers, two CTAs (16 warps) per SM
+// CTAs per SM.  G = 1, 2 and (16-bit KV) 4: two CTAs of 128 registers (16 warps per SM): the
+// kernel needs the loads of many warps in flight more than it needs the registers (measured at
+// G = 2: 3.66 -> 5.34 TB/s, at G = 4: 2.29 -> 3.25; the e4m3 form of G = 4 spills too much at 128
+// and G = 8 needs all 255).  Packed fp16 arithmetic for fp16 rows was also measured (G = 4: 3.62):
+// not worth the fp16 sums; groups this large want the rows multiplied on the tensor cores.
+__global__ void __launch_bounds__(256, (G <= 2 || (G == 4 && sizeof(KVT) == 2)) ? 2 : 1)
 paged_decode_fast_kernel(const DecodeParams p) {
     constexpr int EPL = 16 / (int)sizeof(KVT);   // elements per lane (one 16-byte slice)
     constexpr int LPR = D / EPL;                 // lanes per row
