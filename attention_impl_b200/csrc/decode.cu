@@ -22,6 +22,8 @@
 // in the log2 domain in registers.  Each warp writes one partial row [o[D], m, l].
 //
 // Generic kernel (any dtype / head_dim): one CTA per (unit, head); small-shape compatibility path.
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace attn {
@@ -756,6 +758,23 @@ static int launch_mha(const DecodeParams& p, int warps, int64_t n_units, cudaStr
     return (int)cudaGetLastError();
 }
 
+#include "decode_gqa.cuh"
+
+// Grouped-query decode on the tensor cores (G = 4 or 8, 16-bit KV of the query's type, head_dim 128).
+template <typename T>
+static int launch_gqa_mma(DecodeParams& p, int64_t n_units, cudaStream_t st) {
+    p.head_groups = (p.Hkv + gqa::kWarps - 1) / gqa::kWarps;
+    const int64_t blocks = n_units * p.head_groups;
+    if (blocks > 0x7fffffffLL) return ATTN_B200_ETOOLARGE;
+    auto go = [&](auto kernel) -> int {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, gqa::kSmemBytes);
+        if (e != cudaSuccess) return (int)e;
+        kernel<<<(unsigned)blocks, gqa::kWarps * 32, gqa::kSmemBytes, st>>>(p);
+        return (int)cudaGetLastError();
+    };
+    return p.G == 4 ? go(paged_decode_gqa_mma_kernel<T, 4>) : go(paged_decode_gqa_mma_kernel<T, 8>);
+}
+
 template <typename QT, typename KVT, int G>
 static int launch_fast_g(const DecodeParams& p, int warps, int64_t n_units, cudaStream_t st) {
     const int64_t blocks = n_units * p.head_groups;
@@ -813,6 +832,10 @@ static int run_stage1(DecodeParams& p, int q_dtype, int kv_dtype, cudaStream_t s
         int warps = (p.Hkv + hpw - 1) / hpw;
         if (warps > 8) warps = 8;
         p.head_groups = (p.Hkv + warps * hpw - 1) / (warps * hpw);
+        static const bool no_mma = getenv("ATTN_B200_GQA_NO_MMA") != nullptr;       // A/B runs
+        if ((p.G == 4 || p.G == 8) && kv_dtype == q_dtype && p.D == 128 && !p.S && !no_mma)
+            return q_dtype == ATTN_B200_F16 ? launch_gqa_mma<__half>(p, n_units, st)
+                                            : launch_gqa_mma<__nv_bfloat16>(p, n_units, st);
         if (p.G == 1 && p.block_size <= 1) {      // multi-head, per-token slot table: specialised kernel
             if (kv_dtype == ATTN_B200_E4M3)
                 return q_dtype == ATTN_B200_F16 ? launch_mha<__half, __nv_fp8_e4m3>(p, warps, n_units, st)
