@@ -775,6 +775,20 @@ static int launch_gqa_mma(DecodeParams& p, int64_t n_units, cudaStream_t st) {
     return p.G == 4 ? go(paged_decode_gqa_mma_kernel<T, 4>) : go(paged_decode_gqa_mma_kernel<T, 8>);
 }
 
+template <typename QT>
+static int launch_gqa_mma_e4m3(DecodeParams& p, int64_t n_units, cudaStream_t st) {
+    p.head_groups = (p.Hkv + gqa::kWarps - 1) / gqa::kWarps;
+    const int64_t blocks = n_units * p.head_groups;
+    if (blocks > 0x7fffffffLL) return ATTN_B200_ETOOLARGE;
+    auto go = [&](auto kernel) -> int {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, gqa::kSmemBytes8);
+        if (e != cudaSuccess) return (int)e;
+        kernel<<<(unsigned)blocks, gqa::kWarps * 32, gqa::kSmemBytes8, st>>>(p);
+        return (int)cudaGetLastError();
+    };
+    return p.G == 4 ? go(paged_decode_gqa_mma_e4m3_kernel<QT, 4>) : go(paged_decode_gqa_mma_e4m3_kernel<QT, 8>);
+}
+
 template <typename QT, typename KVT, int G>
 static int launch_fast_g(const DecodeParams& p, int warps, int64_t n_units, cudaStream_t st) {
     const int64_t blocks = n_units * p.head_groups;
@@ -836,6 +850,9 @@ static int run_stage1(DecodeParams& p, int q_dtype, int kv_dtype, cudaStream_t s
         if ((p.G == 4 || p.G == 8) && kv_dtype == q_dtype && p.D == 128 && !p.S && !no_mma)
             return q_dtype == ATTN_B200_F16 ? launch_gqa_mma<__half>(p, n_units, st)
                                             : launch_gqa_mma<__nv_bfloat16>(p, n_units, st);
+        if ((p.G == 4 || p.G == 8) && kv_dtype == ATTN_B200_E4M3 && p.D == 128 && !p.S && !no_mma)
+            return q_dtype == ATTN_B200_F16 ? launch_gqa_mma_e4m3<__half>(p, n_units, st)
+                                            : launch_gqa_mma_e4m3<__nv_bfloat16>(p, n_units, st);
         if (p.G == 1 && p.block_size <= 1) {      // multi-head, per-token slot table: specialised kernel
             if (kv_dtype == ATTN_B200_E4M3)
                 return q_dtype == ATTN_B200_F16 ? launch_mha<__half, __nv_fp8_e4m3>(p, warps, n_units, st)
@@ -909,6 +926,21 @@ extern "C" int attn_b200_paged_decode_pick_chunk(int B, int H, int D, int64_t n_
     int chunk = 1024;
     // largest chunk that still yields >= 16 CTAs per SM (two resident CTAs x eight waves)
     while (chunk > 32 && (n_tokens / chunk + B) * hg < 16LL * sm_count) chunk >>= 1;
+    return chunk;
+}
+
+extern "C" int attn_b200_paged_decode_pick_chunk_gqa(int B, int n_kv_heads, int group, int D, int kv_dtype,
+                                                     int64_t n_tokens, int sm_count) {
+    const bool mma = (group == 4 || group == 8) && D == 128 &&
+                     (kv_dtype == ATTN_B200_F16 || kv_dtype == ATTN_B200_BF16 || kv_dtype == ATTN_B200_E4M3);
+    if (!mma) return attn_b200_paged_decode_pick_chunk(B, n_kv_heads, D, n_tokens, sm_count);
+    // tensor-core kernel: a CTA of 4 warps = 4 KV heads, two CTAs per SM; every unit pays for its Q
+    // fragments and for filling its copy pipeline, so long units win as soon as there are a few
+    // waves of them (measured at G = 8: chunk 256 4.4 TB/s, 1024 5.0)
+    if (sm_count <= 0) sm_count = 148;
+    const int64_t hg = (n_kv_heads + gqa::kWarps - 1) / gqa::kWarps;
+    int chunk = 1024;
+    while (chunk > 64 && (n_tokens / chunk + B) * hg < 4LL * sm_count) chunk >>= 1;
     return chunk;
 }
 

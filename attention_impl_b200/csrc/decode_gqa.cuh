@@ -234,3 +234,186 @@ paged_decode_gqa_mma_kernel(const DecodeParams p) {
         if (c == 0) *reinterpret_cast<float2*>(row + D) = make_float2(m, l);
     }
 }
+
+// The same kernel for e4m3 pools: a token's row of a head is 128 bytes = 8 chunks of 16 dims, lane
+// (n, c) copies chunks 4j + c (j = 0, 1); a 32-bit word of a chunk (4 e4m3) becomes two fp16 pairs
+// (cvt.rn.f16x2.e4m3x2), which are the two B registers of one k-slice for Q K^T and two 8-dim output
+// blocks for P V.  The MMAs are fp16 for either query type (q is converted once, as the CUDA-core
+// e4m3 kernels do); the per-head scales enter the score and the output.
+namespace gqa {
+constexpr int kStageBytes8 = kTile * 256;
+constexpr int kSmemBytes8 = kWarps * kStages * kStageBytes8;
+}  // namespace gqa
+
+template <typename QT, int G>
+__global__ void __launch_bounds__(gqa::kWarps * 32, 2)
+paged_decode_gqa_mma_e4m3_kernel(const DecodeParams p) {
+    using namespace gqa;
+    using M16 = Mma<__half>;
+    constexpr int D = 128;
+    extern __shared__ __align__(16) unsigned char ring_raw[];
+    __shared__ int32_t s_off[kMaxStagedB];
+    SeqBounds sb{stage_offsets(p, s_off), p.uniform_ctx, p.n_tokens};
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n = lane >> 2, c = lane & 3;
+    const int64_t u = blockIdx.x / p.head_groups;
+    const int hk = (int)(blockIdx.x % p.head_groups) * kWarps + warp;
+    Unit un;
+    if (!resolve_unit(u, p.B, p.chunk, sb, un) || hk >= p.Hkv) return;
+
+    // Q as fp16 A fragments: slice s = 4j + e takes dims (4j + c) * 16 + 4e + {0, 1} and + {2, 3}
+    uint32_t aq[8][2];
+    {
+        const bool row_ok = n < G;
+        const QT* qrow = (const QT*)p.q + ((int64_t)un.b * p.H + hk * G + (row_ok ? n : 0)) * D;
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const QT* src = qrow + (4 * j + c) * 16 + 4 * e;
+                aq[4 * j + e][0] = row_ok ? M16::pack(to_f32<QT>(src[0]), to_f32<QT>(src[1])) : 0u;
+                aq[4 * j + e][1] = row_ok ? M16::pack(to_f32<QT>(src[2]), to_f32<QT>(src[3])) : 0u;
+            }
+    }
+    const float qs = p.scale_log2 * (p.k_scale ? p.k_scale[hk] : 1.f);
+    const int64_t row_bytes = (int64_t)p.Hkv * D;
+    const char* kbase = (const char*)p.k_cache + (int64_t)hk * D + c * 16;
+    const char* vbase = (const char*)p.v_cache + (int64_t)hk * D + c * 16;
+    const uint32_t ring = (uint32_t)__cvta_generic_to_shared(ring_raw) + warp * kStages * kStageBytes8 + lane * 16;
+
+    const int nt = (int)((un.tend - un.tbeg + kTile - 1) / kTile);
+    auto tile_slot = [&](int t) -> int {
+        const int64_t tok = un.tbeg + (int64_t)t * kTile + lane;
+        return (t < nt && lane < kTile && tok < un.tend) ? token_slot(p, un, tok) : -1;
+    };
+    auto issue = [&](int t, int my_slot) -> unsigned {
+        const uint32_t base = ring + (t % kStages) * kStageBytes8;
+#pragma unroll
+        for (int grp = 0; grp < 2; ++grp) {
+            const int sl = __shfl_sync(0xffffffffu, my_slot, grp * 8 + n);
+            const int64_t off = (int64_t)(sl >= 0 ? sl : 0) * row_bytes;
+            const int nb = sl >= 0 ? 16 : 0;
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                cp_async_16(base + ((grp * 2 + 0) * 2 + j) * 512, kbase + off + j * 64, nb);
+                cp_async_16(base + ((grp * 2 + 1) * 2 + j) * 512, vbase + off + j * 64, nb);
+            }
+        }
+        return __ballot_sync(0xffffffffu, my_slot >= 0) & 0xffffu;
+    };
+
+    float oacc[16][4];
+#pragma unroll
+    for (int i = 0; i < 16; ++i)
+#pragma unroll
+        for (int k = 0; k < 4; ++k) oacc[i][k] = 0.f;
+    float m = -INFINITY, l = 0.f;
+
+    unsigned v0 = 0, v1 = 0, v2 = 0;
+    int next_slot = tile_slot(0);
+    {
+        const int s0 = next_slot;
+        next_slot = tile_slot(1);
+        v0 = issue(0, s0);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        const int s1 = next_slot;
+        next_slot = tile_slot(2);
+        if (nt > 1) v1 = issue(1, s1);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    for (int t = 0; t < nt; ++t) {
+        {
+            const int s2 = next_slot;
+            next_slot = tile_slot(t + 3);
+            v2 = 0;
+            if (t + 2 < nt) v2 = issue(t + 2, s2);
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        }
+        asm volatile("cp.async.wait_group 2;" ::: "memory");
+        const uint32_t base = ring + (t % kStages) * kStageBytes8;
+        const unsigned vb = v0;
+        v0 = v1;
+        v1 = v2;
+
+        float sacc[2][4];
+#pragma unroll
+        for (int grp = 0; grp < 2; ++grp) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) sacc[grp][k] = 0.f;
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                uint32_t w[4];
+                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3])
+                             : "r"(base + ((grp * 2 + 0) * 2 + j) * 512));
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    __half2 lo, hi;
+                    e4m3x4_to_half2x2(w[e], lo, hi);
+                    const uint32_t a[4] = {aq[4 * j + e][0], 0u, aq[4 * j + e][1], 0u};
+                    M16::run(sacc[grp], a, *reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+                }
+            }
+        }
+        float sc[4];
+#pragma unroll
+        for (int grp = 0; grp < 2; ++grp)
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const bool ok = (vb >> (grp * 8 + 2 * c + i)) & 1u;
+                sc[grp * 2 + i] = ok ? sacc[grp][i] * qs : -INFINITY;
+            }
+        float tmax = fmaxf(fmaxf(sc[0], sc[1]), fmaxf(sc[2], sc[3]));
+        tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
+        tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
+        const float m_new = fmaxf(m, tmax);
+        const float msub = m_new > -INFINITY ? m_new : 0.f;
+        const float alpha = fast_exp2(m - msub);
+        float pr[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) pr[i] = fast_exp2(sc[i] - msub);
+        l = l * alpha + ((pr[0] + pr[1]) + (pr[2] + pr[3]));
+        m = m_new;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            oacc[i][0] *= alpha;
+            oacc[i][1] *= alpha;
+        }
+        const uint32_t pa[4] = {M16::pack(pr[0], pr[1]), 0u, M16::pack(pr[2], pr[3]), 0u};
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            uint32_t w0[4], w1[4];
+            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w0[0]), "=r"(w0[1]), "=r"(w0[2]), "=r"(w0[3])
+                         : "r"(base + ((0 * 2 + 1) * 2 + j) * 512));
+            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w1[0]), "=r"(w1[1]), "=r"(w1[2]), "=r"(w1[3])
+                         : "r"(base + ((1 * 2 + 1) * 2 + j) * 512));
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                __half2 lo0, hi0, lo1, hi1;
+                e4m3x4_to_half2x2(w0[e], lo0, hi0);
+                e4m3x4_to_half2x2(w1[e], lo1, hi1);
+                M16::run(oacc[(j * 4 + e) * 2 + 0], pa, movmatrix_trans(*reinterpret_cast<const uint32_t*>(&lo0)),
+                         movmatrix_trans(*reinterpret_cast<const uint32_t*>(&lo1)));
+                M16::run(oacc[(j * 4 + e) * 2 + 1], pa, movmatrix_trans(*reinterpret_cast<const uint32_t*>(&hi0)),
+                         movmatrix_trans(*reinterpret_cast<const uint32_t*>(&hi1)));
+            }
+        }
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    l += __shfl_xor_sync(0xffffffffu, l, 1);
+    l += __shfl_xor_sync(0xffffffffu, l, 2);
+    if (n < G) {
+        const float vs = p.v_scale ? p.v_scale[hk] : 1.f;
+        float* row = p.part + ((int64_t)u * p.H + hk * G + n) * (D + 2);
+        // output block (j, e, h) of this lane: dims (4j + c) * 16 + 4e + 2h + {0, 1}
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh)
+                    *reinterpret_cast<float2*>(row + (4 * j + c) * 16 + 4 * e + 2 * hh) =
+                        make_float2(oacc[(j * 4 + e) * 2 + hh][0] * vs, oacc[(j * 4 + e) * 2 + hh][1] * vs);
+        if (c == 0) *reinterpret_cast<float2*>(row + D) = make_float2(m, l);
+    }
+}

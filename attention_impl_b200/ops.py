@@ -122,7 +122,10 @@ def _kv_code(kc: torch.Tensor, q: torch.Tensor) -> int:
     return _DT[q.dtype]
 
 
-def pick_chunk(B: int, H: int, D: int, n_tokens: int, device) -> int:
+def pick_chunk(B: int, H: int, D: int, n_tokens: int, device, group: int = 1, kv_dtype: int = 0) -> int:
+    """Chunk length for ``H`` KV heads serving ``group`` query heads each (``kv_dtype``: ABI dtype code)."""
+    if group > 1:
+        return lib.attn_b200_paged_decode_pick_chunk_gqa(B, H, group, D, kv_dtype, n_tokens, sm_count(device))
     return lib.attn_b200_paged_decode_pick_chunk(B, H, D, n_tokens, sm_count(device))
 
 
@@ -193,7 +196,7 @@ def paged_kv_attention_forward(Q, K, V, K_cache, V_cache, cache_indices, offsets
     dev = Q.device
     with torch.cuda.device(dev):
         if chunk is None:
-            chunk = pick_chunk(B, Hkv, D, T, dev)
+            chunk = pick_chunk(B, Hkv, D, T, dev, group=H // Hkv, kv_dtype=kvd)
         need = decode_workspace_bytes(B, H, D, T, chunk)
         if workspace is None:
             workspace = torch.empty(need, dtype=torch.uint8, device=dev)
@@ -396,7 +399,7 @@ def paged_decode_partial(Q, K_cache, V_cache, cache_indices, offsets, num_heads:
     dev = Q.device
     with torch.cuda.device(dev):
         if chunk is None:
-            chunk = pick_chunk(B, Hkv, D, T, dev)
+            chunk = pick_chunk(B, Hkv, D, T, dev, group=H // Hkv, kv_dtype=kvd)
         need = decode_workspace_bytes(B, H, D, T, chunk)
         if workspace is None:
             workspace = torch.empty(need, dtype=torch.uint8, device=dev)

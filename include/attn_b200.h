@@ -131,6 +131,10 @@ ATTN_B200_API int attn_b200_paged_decode(const void* q, const void* k_new, const
 ATTN_B200_API size_t attn_b200_paged_decode_workspace_bytes(int B, int H, int D, int64_t n_tokens, int chunk);
 /* Heuristic chunk length: enough (chunk, head-group) work items to fill `sm_count` SMs. */
 ATTN_B200_API int attn_b200_paged_decode_pick_chunk(int B, int H, int D, int64_t n_tokens, int sm_count);
+/* The same for grouped-query heads: `group` query heads per KV head, `kv_dtype` of the pools.  Groups
+ * of 4 and 8 over fp16/bf16 pools at head_dim 128 run on the tensor cores and prefer longer chunks. */
+ATTN_B200_API int attn_b200_paged_decode_pick_chunk_gqa(int B, int n_kv_heads, int group, int D, int kv_dtype,
+                                                        int64_t n_tokens, int sm_count);
 
 /* Same first stage as attn_b200_paged_decode, but the second stage writes, per (b, h), one
  * partial row  [m (log2 domain), l, o[D] (un-normalised)]  of D+2 floats into
