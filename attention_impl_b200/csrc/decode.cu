@@ -760,7 +760,7 @@ static int launch_mha(const DecodeParams& p, int warps, int64_t n_units, cudaStr
 
 #include "decode_gqa.cuh"
 
-// Grouped-query decode on the tensor cores (G = 4 or 8, 16-bit KV of the query's type, head_dim 128).
+// Grouped-query decode on the tensor cores (G = 2, 4 or 8, 16-bit KV of the query's type, head_dim 128).
 template <typename T>
 static int launch_gqa_mma(DecodeParams& p, int64_t n_units, cudaStream_t st) {
     p.head_groups = (p.Hkv + gqa::kWarps - 1) / gqa::kWarps;
@@ -772,7 +772,8 @@ static int launch_gqa_mma(DecodeParams& p, int64_t n_units, cudaStream_t st) {
         kernel<<<(unsigned)blocks, gqa::kWarps * 32, gqa::kSmemBytes, st>>>(p);
         return (int)cudaGetLastError();
     };
-    return p.G == 4 ? go(paged_decode_gqa_mma_kernel<T, 4>) : go(paged_decode_gqa_mma_kernel<T, 8>);
+    return p.G == 2 ? go(paged_decode_gqa_mma_kernel<T, 2>)
+                    : p.G == 4 ? go(paged_decode_gqa_mma_kernel<T, 4>) : go(paged_decode_gqa_mma_kernel<T, 8>);
 }
 
 template <typename QT>
@@ -786,7 +787,8 @@ static int launch_gqa_mma_e4m3(DecodeParams& p, int64_t n_units, cudaStream_t st
         kernel<<<(unsigned)blocks, gqa::kWarps * 32, gqa::kSmemBytes8, st>>>(p);
         return (int)cudaGetLastError();
     };
-    return p.G == 4 ? go(paged_decode_gqa_mma_e4m3_kernel<QT, 4>) : go(paged_decode_gqa_mma_e4m3_kernel<QT, 8>);
+    return p.G == 2 ? go(paged_decode_gqa_mma_e4m3_kernel<QT, 2>)
+                    : p.G == 4 ? go(paged_decode_gqa_mma_e4m3_kernel<QT, 4>) : go(paged_decode_gqa_mma_e4m3_kernel<QT, 8>);
 }
 
 template <typename QT, typename KVT, int G>
@@ -847,10 +849,10 @@ static int run_stage1(DecodeParams& p, int q_dtype, int kv_dtype, cudaStream_t s
         if (warps > 8) warps = 8;
         p.head_groups = (p.Hkv + warps * hpw - 1) / (warps * hpw);
         static const bool no_mma = getenv("ATTN_B200_GQA_NO_MMA") != nullptr;       // A/B runs
-        if ((p.G == 4 || p.G == 8) && kv_dtype == q_dtype && p.D == 128 && !p.S && !no_mma)
+        if ((p.G == 2 || p.G == 4 || p.G == 8) && kv_dtype == q_dtype && p.D == 128 && !p.S && !no_mma)
             return q_dtype == ATTN_B200_F16 ? launch_gqa_mma<__half>(p, n_units, st)
                                             : launch_gqa_mma<__nv_bfloat16>(p, n_units, st);
-        if ((p.G == 4 || p.G == 8) && kv_dtype == ATTN_B200_E4M3 && p.D == 128 && !p.S && !no_mma)
+        if ((p.G == 2 || p.G == 4 || p.G == 8) && kv_dtype == ATTN_B200_E4M3 && p.D == 128 && !p.S && !no_mma)
             return q_dtype == ATTN_B200_F16 ? launch_gqa_mma_e4m3<__half>(p, n_units, st)
                                             : launch_gqa_mma_e4m3<__nv_bfloat16>(p, n_units, st);
         if (p.G == 1 && p.block_size <= 1) {      // multi-head, per-token slot table: specialised kernel
@@ -931,7 +933,7 @@ extern "C" int attn_b200_paged_decode_pick_chunk(int B, int H, int D, int64_t n_
 
 extern "C" int attn_b200_paged_decode_pick_chunk_gqa(int B, int n_kv_heads, int group, int D, int kv_dtype,
                                                      int64_t n_tokens, int sm_count) {
-    const bool mma = (group == 4 || group == 8) && D == 128 &&
+    const bool mma = (group == 2 || group == 4 || group == 8) && D == 128 &&
                      (kv_dtype == ATTN_B200_F16 || kv_dtype == ATTN_B200_BF16 || kv_dtype == ATTN_B200_E4M3);
     if (!mma) return attn_b200_paged_decode_pick_chunk(B, n_kv_heads, D, n_tokens, sm_count);
     // tensor-core kernel: a CTA of 4 warps = 4 KV heads, two CTAs per SM; every unit pays for its Q

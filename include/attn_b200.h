@@ -132,7 +132,7 @@ ATTN_B200_API size_t attn_b200_paged_decode_workspace_bytes(int B, int H, int D,
 /* Heuristic chunk length: enough (chunk, head-group) work items to fill `sm_count` SMs. */
 ATTN_B200_API int attn_b200_paged_decode_pick_chunk(int B, int H, int D, int64_t n_tokens, int sm_count);
 /* The same for grouped-query heads: `group` query heads per KV head, `kv_dtype` of the pools.  Groups
- * of 4 and 8 over fp16/bf16 pools at head_dim 128 run on the tensor cores and prefer longer chunks. */
+ * of 2, 4 and 8 at head_dim 128 run on the tensor cores and prefer longer chunks. */
 ATTN_B200_API int attn_b200_paged_decode_pick_chunk_gqa(int B, int n_kv_heads, int group, int D, int kv_dtype,
                                                         int64_t n_tokens, int sm_count);
 

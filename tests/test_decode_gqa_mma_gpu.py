@@ -1,4 +1,4 @@
-"""GPU: grouped-query decode on the tensor cores (G = 4 or 8 query heads per KV head, head_dim 128,
+"""GPU: grouped-query decode on the tensor cores (G = 2, 4 or 8 query heads per KV head, head_dim 128,
 fp16 / bf16 / e4m3 pools; taken when S and P are not requested) against the CPU oracle."""
 import pytest
 import torch
@@ -28,7 +28,7 @@ def _run(inp, Hq, **kw):
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
-@pytest.mark.parametrize("Hq,Hkv", [(8, 2), (16, 2), (32, 8), (40, 5), (24, 3)])
+@pytest.mark.parametrize("Hq,Hkv", [(8, 2), (16, 2), (32, 8), (40, 5), (24, 3), (8, 4), (6, 3)])
 @pytest.mark.parametrize("chunk", [None, 32, 64, 1024])
 def test_gqa_mma_matches_oracle(dtype, Hq, Hkv, chunk):
     """Ragged lengths around the 16-token tile (0, 1, 15, 16, 17 ...), KV head counts that do and do not
@@ -52,7 +52,7 @@ def test_gqa_mma_equals_cuda_core_kernel_closely():
     assert (O.float() - O_cc.float()).abs().max() <= 1e-3
 
 
-@pytest.mark.parametrize("G", [4, 8])
+@pytest.mark.parametrize("G", [2, 4, 8])
 def test_gqa_mma_e4m3(G):
     Hkv, D = 6, 128
     Hq = Hkv * G
