@@ -647,6 +647,112 @@ class PagedPrefill(Prefill):
             f"1 of {self.B} sequences ({Tq} query tokens over {T} cached tokens) per step", Tq
 
 
+class GqaDecode(Workload):
+    """Grouped-query paged decode (not in the reference): 32 query heads over 8 KV heads, fp16 pools."""
+    name, metric, unit, dtype = "gqa_decode", "paged_decode_kv_read_bandwidth", "TB/s", "f16"
+    B, H, HKV, D, LO, HI, SEED = 64, 32, 8, 128, 1024, 32768, 4
+
+    def setup(self):
+        import attention_impl_b200 as A
+        self.A = A
+        dev = self.dev
+        self.lens_ = seeded_lengths(self.args.batch or self.B, self.LO, self.HI, self.SEED)
+        self.Bn, self.T = len(self.lens_), int(self.lens_.sum())
+        torch.manual_seed(4100 + self.rank)
+        kvdim = self.HKV * self.D
+        self.Kc = torch.empty(self.T, kvdim, dtype=torch.float16, device=dev)
+        self.Vc = torch.empty(self.T, kvdim, dtype=torch.float16, device=dev)
+        fill_normal(self.Kc)
+        fill_normal(self.Vc)
+        self.ci = torch.randperm(self.T, device=dev).to(torch.int32)
+        self.off = self.lens_.cumsum(0).to(torch.int32).to(dev)
+        self.Q = torch.randn(self.Bn, self.H * self.D, device=dev, dtype=torch.float16)
+        self.K, self.V = (torch.randn(self.Bn, kvdim, device=dev, dtype=torch.float16) for _ in range(2))
+        self.O = torch.empty_like(self.Q)
+        self.chunk = A.ops.pick_chunk(self.Bn, self.HKV, self.D, self.T, dev, group=self.H // self.HKV, kv_dtype=0)
+        self.ws = torch.empty(A.ops.decode_workspace_bytes(self.Bn, self.H, self.D, self.T, self.chunk),
+                              dtype=torch.uint8, device=dev)
+
+    def _call(self, stages):
+        self.A.paged_kv_attention_forward(self.Q, self.K, self.V, self.Kc, self.Vc, self.ci, self.off, self.H,
+                                          return_sp=False, chunk=self.chunk, workspace=self.ws, out=self.O,
+                                          stages=stages)
+
+    def step(self):
+        self._call(3)
+
+    def step_split(self):
+        return (lambda: self._call(1)), (lambda: self._call(2))
+
+    def e2e_setup(self):
+        self.h_in = [x.cpu().pin_memory() for x in (self.Q, self.K, self.V, self.ci, self.off)]
+        self.h_out = torch.empty(self.O.shape, dtype=self.O.dtype).pin_memory()
+        return sum(x.numel() * x.element_size() for x in self.h_in), self.h_out.numel() * 2
+
+    def e2e_step(self):
+        dQ, dK, dV, dci, doff = (x.to(self.dev, non_blocking=True) for x in self.h_in)
+        o = self.A.paged_kv_attention_forward(dQ, dK, dV, self.Kc, self.Vc, dci, doff, self.H, return_sp=False,
+                                              max_context_len=int(self.lens_.max()))[2]
+        self.h_out.copy_(o, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    def units_per_step_rank(self):
+        return 2.0 * self.T * self.HKV * self.D * 2
+
+    def sequences_per_step(self):
+        return self.Bn
+
+    def launches_per_step(self):
+        return 2
+
+    def kernel_name(self):
+        return "paged_decode_gqa_mma_kernel<half,4>"
+
+    def static_config(self):
+        return {"workload": "grouped_query_paged_decode", "batch": self.args.batch or self.B, "heads": self.H,
+                "kv_heads": self.HKV, "head_dim": self.D, "ctx_range": [self.LO, self.HI]}
+
+    def config(self):
+        per = self.units_per_step_rank()
+        return dict(self.static_config(), context_tokens=self.T, kv_bytes_total=per, sharding="replicas only",
+                    chunk=self.chunk, l2=f"inputs larger than L2 ({per / 1e9:.1f} GB of KV per step)")
+
+    def _sample(self, n_seq):
+        T = int(self.lens_[:n_seq].sum())
+        rows = self.ci[:T].long()
+        order = torch.argsort(rows)
+        rank_of = torch.empty_like(order)
+        rank_of[order] = torch.arange(T, device=self.dev)
+        return (self.Q[:n_seq].cpu(), self.K[:n_seq].cpu(), self.V[:n_seq].cpu(), self.Kc[rows[order]].cpu(),
+                self.Vc[rows[order]].cpu(), rank_of.int().cpu(), self.off[:n_seq].cpu()), T
+
+    def cpu_baseline(self):
+        from oracle import attention_oracle as orc
+        n_seq = 2
+        inputs, T = self._sample(n_seq)
+        sec = time_cpu(lambda: orc.paged_decode(*inputs, self.H))
+        O32 = orc.paged_decode(*inputs, self.H, compute_dtype=torch.float32)[2]
+        self.step()
+        torch.cuda.synchronize()
+        err = (self.O[:n_seq].cpu().float() - O32.float()).abs().max().item()
+        kv_bytes = 2 * T * self.HKV * self.D * 2
+        return ({"value": kv_bytes / sec / 1e12, "unit": "TB/s", "cores": torch.get_num_threads(), "kind": "port",
+                 "sample": f"first {n_seq} of {self.Bn} sequences ({T} tokens)", "seconds": sec,
+                 "torch": torch.__version__},
+                {"max_abs_err_vs_fp32_oracle": err, "tolerance": 2e-3, "sequences_checked": n_seq})
+
+    def reference_run(self, steps, warmup):
+        from oracle import attention_oracle as orc
+        g = torch.Generator().manual_seed(7)
+        T = 16384
+        Q = torch.randn(1, self.H * self.D, generator=g).half()
+        K, V = (torch.randn(1, self.HKV * self.D, generator=g).half() for _ in range(2))
+        Kc, Vc = (torch.randn(T, self.HKV * self.D, generator=g).half() for _ in range(2))
+        ci, off = torch.randperm(T, generator=g).int(), torch.tensor([T]).int()
+        sec = time_cpu(lambda: orc.paged_decode(Q, K, V, Kc, Vc, ci, off, self.H), steps=steps, warmup=warmup)
+        return 2.0 * T * self.HKV * self.D * 2 / sec / 1e12, sec, f"1 sequence of {T} tokens per step", 1
+
+
 class Fp8Split(Workload):
     name, metric, unit, dtype = "fp8_split", "paged_decode_kv_read_bandwidth", "TB/s", "e4m3"
     B, H, D, LO, HI, SEED = 64, 32, 128, 32768, 131072, 5
@@ -774,7 +880,7 @@ class Fp8Split(Workload):
         return 2.0 * T * H * D / sec / 1e12, sec, f"1 sequence of {T} tokens per step", 1
 
 
-WORKLOADS = {w.name: w for w in (LargeDecode, SmallDecode, Rope, Prefill, PagedPrefill, Fp8Split)}
+WORKLOADS = {w.name: w for w in (LargeDecode, SmallDecode, Rope, Prefill, PagedPrefill, GqaDecode, Fp8Split)}
 
 
 # ================================================================================================
