@@ -42,49 +42,49 @@ template <> struct RnArith2<__nv_bfloat162> {
     static __device__ __forceinline__ __nv_bfloat162 neg(__nv_bfloat162 a) { return __hneg2(a); }
 };
 
-// 16-bit types, rot_half % 8 == 0, head_dim % 8 == 0: one thread = 8 + 8 partner elements.
+// 16-bit types, rot_half % 8 == 0, head_dim % 8 == 0: a thread rotates 8 elements and their 8
+// partners at a time.  One CTA per token: the position is read once, all index arithmetic is 32-bit
+// and a thread walks several (chunk, partner) pairs of the token, q heads first, then k.  (With one
+// thread per pair over the whole batch - a 64-bit division and four loads per thread - the same
+// arithmetic ran at 0.88 of the measured copy bandwidth against 0.92.)
 template <typename T2>
 __global__ void __launch_bounds__(256)
-rope_vec8_kernel(uint4* __restrict__ q, uint4* __restrict__ k, const int32_t* __restrict__ positions,
-                 const uint4* __restrict__ cos, const uint4* __restrict__ sin, int64_t n_items,
-                 int items_per_token, int n_heads_q, int chunks_per_half, int head_vec, int half_vec,
-                 int64_t max_pos, int32_t* __restrict__ err_flag) {
-    const int64_t g = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (g >= n_items) return;
-    const int64_t token = g / items_per_token;
-    const int r = (int)(g - token * items_per_token);
-    const int head = r / chunks_per_half;
-    const int c = r - head * chunks_per_half;
+rope_token_kernel(uint4* __restrict__ q, uint4* __restrict__ k, const int32_t* __restrict__ positions,
+                  const uint4* __restrict__ cos, const uint4* __restrict__ sin, int n_heads_q, int n_heads_k,
+                  int head_vec, int half_vec, int64_t max_pos, int32_t* __restrict__ err_flag) {
+    const int64_t token = blockIdx.x;
     const int pos = positions[token];
     if (pos < 0 || pos >= max_pos) {
-        if (err_flag) atomicOr(err_flag, ATTN_B200_FLAG_BAD_POSITION);
+        if (err_flag && threadIdx.x == 0) atomicOr(err_flag, ATTN_B200_FLAG_BAD_POSITION);
         return;
     }
-    uint4* base;
-    if (head < n_heads_q) {
-        base = q + (token * n_heads_q + head) * head_vec;
-    } else {
-        const int n_heads_k = items_per_token / chunks_per_half - n_heads_q;
-        base = k + (token * n_heads_k + (head - n_heads_q)) * head_vec;
-    }
-    uint4 x1 = base[c];
-    uint4 x2 = base[c + half_vec];
-    const uint4 cs = __ldg(cos + (int64_t)pos * half_vec + c);
-    const uint4 sn = __ldg(sin + (int64_t)pos * half_vec + c);
-    T2* a = reinterpret_cast<T2*>(&x1);
-    T2* b = reinterpret_cast<T2*>(&x2);
-    const T2* cc = reinterpret_cast<const T2*>(&cs);
-    const T2* ss = reinterpret_cast<const T2*>(&sn);
+    const uint4* cosr = cos + (int64_t)pos * half_vec;
+    const uint4* sinr = sin + (int64_t)pos * half_vec;
+    uint4* qrow = q + token * n_heads_q * head_vec;
+    uint4* krow = k ? k + token * n_heads_k * head_vec : nullptr;
+    const int q_items = n_heads_q * half_vec, items = q_items + n_heads_k * half_vec;
     using A = RnArith2<T2>;
+    for (int r = threadIdx.x; r < items; r += blockDim.x) {
+        const bool is_q = r < q_items;
+        const int rr = is_q ? r : r - q_items;
+        const int head = rr / half_vec, c = rr - head * half_vec;
+        uint4* base = (is_q ? qrow : krow) + head * head_vec;
+        uint4 x1 = base[c], x2 = base[c + half_vec];
+        const uint4 cs = __ldg(cosr + c), sn = __ldg(sinr + c);
+        T2* a = reinterpret_cast<T2*>(&x1);
+        T2* b = reinterpret_cast<T2*>(&x2);
+        const T2* cc = reinterpret_cast<const T2*>(&cs);
+        const T2* ss = reinterpret_cast<const T2*>(&sn);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const T2 lo = A::add(A::mul(a[i], cc[i]), A::mul(A::neg(b[i]), ss[i]));
-        const T2 hi = A::add(A::mul(b[i], cc[i]), A::mul(a[i], ss[i]));
-        a[i] = lo;
-        b[i] = hi;
+        for (int i = 0; i < 4; ++i) {
+            const T2 lo = A::add(A::mul(a[i], cc[i]), A::mul(A::neg(b[i]), ss[i]));
+            const T2 hi = A::add(A::mul(b[i], cc[i]), A::mul(a[i], ss[i]));
+            a[i] = lo;
+            b[i] = hi;
+        }
+        base[c] = x1;
+        base[c + half_vec] = x2;
     }
-    base[c] = x1;
-    base[c + half_vec] = x2;
 }
 
 // Any dtype / any rot_half: one thread per (token, head, d < rot_half).
@@ -125,13 +125,10 @@ static int launch_rope(void* q, void* k, const int32_t* positions, const void* c
     if (kVec && rot_half % 8 == 0 && head_dim % 8 == 0 && aligned) {
         if constexpr (kVec) {
             const int cph = rot_half / 8;
-            const int ipt = (hq + hk) * cph;
-            const int64_t n_items = n_tokens * ipt;
-            const int64_t blocks = (n_items + 255) / 256;
-            if (blocks > 0x7fffffffLL) return ATTN_B200_ETOOLARGE;
-            rope_vec8_kernel<T2><<<(unsigned)blocks, 256, 0, stream>>>(
-                (uint4*)q, (uint4*)k, positions, (const uint4*)cos, (const uint4*)sin, n_items, ipt, hq, cph,
-                head_dim / 8, cph, max_pos, err_flag);
+            if (n_tokens > 0x7fffffffLL) return ATTN_B200_ETOOLARGE;
+            rope_token_kernel<T2><<<(unsigned)n_tokens, 256, 0, stream>>>(
+                (uint4*)q, (uint4*)k, positions, (const uint4*)cos, (const uint4*)sin, hq, hk, head_dim / 8, cph,
+                max_pos, err_flag);
         }
     } else {
         const int64_t n_items = n_tokens * (int64_t)(hq + hk) * rot_half;

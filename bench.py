@@ -442,7 +442,7 @@ class Rope(Workload):
         return 1
 
     def kernel_name(self):
-        return "rope_vec8_kernel<half2>"
+        return "rope_token_kernel<half2>"
 
     def static_config(self):
         return {"workload": "rotary_embedding", "tokens": self.N, "heads": self.H, "head_dim": self.D,
@@ -463,6 +463,66 @@ class Rope(Workload):
         cos, sin = orc.rope_tables(self.D, self.MAXPOS)
         sec = time_cpu(lambda: orc.rope(q, k, pos, cos, sin, self.D), steps=steps, warmup=warmup)
         return 4.0 * n * self.H * self.D * 2 / sec / 1e12, sec, f"{n} of {self.N} tokens per step", n
+
+
+class RopeKv(Rope):
+    """RoPE on q and k fused with the append of k and v to the KV pools (the step before decode)."""
+    name, metric = "rope_kv", "rope_cache_write_bandwidth"
+
+    def setup(self):
+        super().setup()
+        dev = self.dev
+        self.v = torch.randn(self.N, self.H * self.D, device=dev, dtype=torch.float16)
+        self.slots = torch.randperm(4 * self.N, device=dev)[: self.N].to(torch.int32)
+        self.Kc = torch.empty(4 * self.N, self.H * self.D, device=dev, dtype=torch.float16)
+        self.Vc = torch.empty_like(self.Kc)
+
+    def step(self):
+        self.A.rope_and_cache_write(self.q, self.k, self.v, self.pos, self.cos, self.sin, self.slots, self.Kc,
+                                    self.Vc, self.D)
+
+    def e2e_setup(self):
+        self.hq, self.hk, self.hv = (t.cpu().pin_memory() for t in (self.q, self.k, self.v))
+        self.hpos, self.hsl = self.pos.cpu().pin_memory(), self.slots.cpu().pin_memory()
+        return 3 * self.hq.numel() * 2 + 2 * self.hpos.numel() * 4, self.hq.numel() * 2
+
+    def e2e_step(self):
+        dq, dk, dv = (t.to(self.dev, non_blocking=True) for t in (self.hq, self.hk, self.hv))
+        dpos, dsl = self.hpos.to(self.dev, non_blocking=True), self.hsl.to(self.dev, non_blocking=True)
+        self.A.rope_and_cache_write(dq, dk, dv, dpos, self.cos, self.sin, dsl, self.Kc, self.Vc, self.D)
+        self.hq.copy_(dq, non_blocking=True)          # the rotated q goes on to the attention call; k, v stay in the pools
+        torch.cuda.current_stream().synchronize()
+
+    def units_per_step_rank(self):
+        # q read + written, k read + rotated k written back + stored, v read + stored
+        return 7.0 * self.N * self.H * self.D * 2
+
+    def kernel_name(self):
+        return "rope_write_kv_kernel<half>"
+
+    def static_config(self):
+        return dict(super().static_config(), workload="rope_and_kv_cache_append")
+
+    def config(self):
+        return dict(self.static_config(), sharding="replicas only",
+                    l2="940 MB moved per step: q, k, v rows and their pool rows (> 126 MB L2)")
+
+    def reference_run(self, steps, warmup):
+        from oracle import attention_oracle as orc
+        g = torch.Generator().manual_seed(2)
+        n = 2048
+        q, k, v = (torch.randn(n, self.H * self.D, generator=g).half() for _ in range(3))
+        pos = torch.randint(0, self.MAXPOS, (n,), generator=g).int()
+        sl = torch.randperm(4 * n, generator=g)[:n]
+        Kc, Vc = torch.empty(4 * n, self.H * self.D).half(), torch.empty(4 * n, self.H * self.D).half()
+        cos, sin = orc.rope_tables(self.D, self.MAXPOS)
+
+        def fn():
+            q2, k2 = orc.rope(q, k, pos, cos, sin, self.D)
+            Kc[sl] = k2
+            Vc[sl] = v
+        sec = time_cpu(fn, steps=steps, warmup=warmup)
+        return 7.0 * n * self.H * self.D * 2 / sec / 1e12, sec, f"{n} of {self.N} tokens per step", n
 
 
 class Prefill(Workload):
@@ -880,7 +940,7 @@ class Fp8Split(Workload):
         return 2.0 * T * H * D / sec / 1e12, sec, f"1 sequence of {T} tokens per step", 1
 
 
-WORKLOADS = {w.name: w for w in (LargeDecode, SmallDecode, Rope, Prefill, PagedPrefill, GqaDecode, Fp8Split)}
+WORKLOADS = {w.name: w for w in (LargeDecode, SmallDecode, Rope, RopeKv, Prefill, PagedPrefill, GqaDecode, Fp8Split)}
 
 
 # ================================================================================================
