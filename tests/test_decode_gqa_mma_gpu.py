@@ -52,12 +52,14 @@ def test_gqa_mma_equals_cuda_core_kernel_closely():
     assert (O.float() - O_cc.float()).abs().max() <= 1e-3
 
 
+@pytest.mark.parametrize("qdtype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("G", [2, 4, 8])
-def test_gqa_mma_e4m3(G):
+def test_gqa_mma_e4m3(G, qdtype):
     Hkv, D = 6, 128
     Hq = Hkv * G
     lens = [0, 1, 17, 100, 1500, 3000]
-    Q, K, V, Kc, Vc, ci, off = _inputs(Hq, Hkv, D, lens, 8192, torch.float16, seed=11 + G)
+    Q, K, V, Kc, Vc, ci, off = _inputs(Hq, Hkv, D, lens, 8192, qdtype, seed=11 + G)
+    Kc, Vc = Kc.float(), Vc.float()
     K8, ks = orc.quantize_e4m3_per_head(Kc, Hkv)
     V8, vs = orc.quantize_e4m3_per_head(Vc, Hkv)
     Kd, Vd = orc.dequantize_e4m3_per_head(K8, ks, Hkv), orc.dequantize_e4m3_per_head(V8, vs, Hkv)
