@@ -14,7 +14,7 @@ LIB_PATH = os.path.join(_HERE, "lib", "libattn_b200.so")
 
 F16, BF16, F32, E4M3 = 0, 1, 2, 3
 FLAG_BAD_SLOT, FLAG_BAD_POSITION, FLAG_BAD_OFFSETS, FLAG_TIMEOUT = 1, 2, 4, 8
-ABI_VERSION = 2
+ABI_VERSION = 3
 STATIC_SCRATCH_BYTES = 16 << 20
 
 _vp, _i32, _i64, _f32, _sz = C.c_void_p, C.c_int, C.c_int64, C.c_float, C.c_size_t
@@ -30,6 +30,7 @@ PROTOTYPES = {
                                       _i32, _i32, _i32, _i32, _i64, _i64, _i32, _i32, _i32, _i32, _f32, _vp, _vp,
                                       _i32, _i32, _i32, _vp, _vp]),
     "attn_b200_paged_decode_workspace_bytes": (_sz, [_i32, _i32, _i32, _i64, _i32]),
+    "attn_b200_paged_decode_ticket_bytes": (_sz, [_i32, _i32]),
     "attn_b200_paged_decode_pick_chunk": (_i32, [_i32, _i32, _i32, _i64, _i32]),
     "attn_b200_paged_decode_pick_chunk_gqa": (_i32, [_i32, _i32, _i32, _i32, _i32, _i64, _i32]),
     "attn_b200_paged_decode_partial": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _i32, _i32, _i32, _i32, _i64,
@@ -40,6 +41,11 @@ PROTOTYPES = {
     "attn_b200_peer_push": (_i32, [_vp, _sz, _vp, _vp, _i32, _vp]),
     "attn_b200_wait_flags": (_i32, [_vp, _i32, _i32, _vp, _vp]),
     "attn_b200_wait_flags_consume": (_i32, [_vp, _i32, _i32, _vp, _vp]),
+    "attn_b200_paged_decode_partial_push": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _sz, _i32, _i32, _i32, _i32, _i64, _i64,
+                                                   _i32, _i32, _i32, _f32, _vp, _vp, _i32, _i32, _vp, _vp, _i32, _vp,
+                                                   _vp]),
+    "attn_b200_lse_combine_wait": (_i32, [_vp, _i32, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _f32, _i32, _vp, _vp,
+                                          _vp, _vp]),
     "attn_b200_lse_combine": (_i32, [_vp, _i32, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _f32, _i32, _vp]),
     "attn_b200_varlen_prefill": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i64, _i32, _i32, _i32, _f32,
                                         _i32, _i32, _i32, _vp, _vp]),

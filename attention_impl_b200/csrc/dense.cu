@@ -53,7 +53,10 @@ dense_attention_kernel(const DenseParams p) {
             return;
         }
         len = (int)(e - beg);
-        if (len > p.L) len = p.L;
+        if (len > p.L) {       // max_len understates this sequence: rows past it are not computed
+            if (p.err_flag && threadIdx.x == 0) atomicOr(p.err_flag, ATTN_B200_FLAG_BAD_OFFSETS);
+            len = p.L;
+        }
     } else {
         beg = (int64_t)b * p.L;
         len = p.L;
@@ -137,8 +140,11 @@ extern "C" int attn_b200_varlen_prefill(const void* q, const void* k, const void
     if (!q || !k || !v || !offsets || !out || B <= 0 || H <= 0 || D <= 0 || n_tokens < 0 || max_len < 0)
         return ATTN_B200_EINVAL;
     if ((S == nullptr) != (P == nullptr)) return ATTN_B200_EINVAL;
-    if (n_tokens == 0 || max_len == 0) return 0;
+    if (n_tokens == 0) return 0;
     cudaStream_t st = (cudaStream_t)stream;
+    const size_t out_el = out_f32 ? 4 : (dtype == ATTN_B200_F32 ? 4 : 2);
+    if (max_len == 0)          // no sequence has a token: the output is all zeros, as the reference's zeros_like
+        return (int)cudaMemsetAsync(out, 0, (size_t)n_tokens * H * D * out_el, st);
     if (!force_generic && !S && prefill_tc_supported(D, dtype))
         return prefill_tc_launch(q, k, v, offsets, out, B, n_tokens, max_len, H, D, scale, dtype, out_f32, err_flag,
                                  st);

@@ -3,10 +3,9 @@
 //
 // Semantics: paged_attention_kernel.cu:15-98 of the reference (per sequence slice of the packed
 // buffer, key j visible to query i iff j <= i, softmax of scale*QK^T, O = P V), evaluated flash
-// style: S and P never leave the SM.  Three kernels share one pipeline (a pair of 128-row query
+// style: S and P never leave the SM.  Two kernels share one pipeline (a pair of 128-row query
 // tiles per work item, one softmax thread per query row, P and O resident in tensor memory):
-//   prefill_tc2_kernel       one CTA per pair (ATTN_B200_PREFILL_VERSION=2, kept for A/B runs)
-//   prefill_tc2p_kernel      persistent: one CTA per SM draws pairs from a counter (the default)
+//   prefill_tc2p_kernel      persistent: one CTA per SM draws pairs from a counter
 //   paged_prefill_tc_kernel  K/V gathered through a slot table (chunked / prefix-cached prefill)
 // Every mbarrier wait is bounded (about one second of SM clocks); on expiry the kernel raises
 // ATTN_B200_FLAG_TIMEOUT, all roles leave their loops, outstanding copies are given a bounded
@@ -38,6 +37,7 @@ struct Params {
     float scale_log2;
     int out_f32;
     int32_t* err_flag;
+    int* launch_abort;   // this launch's abort word (LaunchState::abort)
 };
 
 // =============================================================================================
@@ -58,27 +58,15 @@ struct Params {
 // the result:
 // O and l are consistent with the reference maximum, and O/l is formed in the epilogue.
 // =============================================================================================
-#ifdef ATTN_B200_TRACE
-// Development aid (not part of the product build): clock64 stamps of one CTA's pipeline events.
-__device__ long long g_trace[3 * 64 * 8];
-#define TRACE(role, j, slot) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (j) < 64) \
-    g_trace[((role) * 64 + (j)) * 8 + (slot)] = clock64(); } while (0)
-#else
-#define TRACE(role, j, slot) do {} while (0)
-#endif
+//
+// `split`.  P is rounded to the input type for the P.V MMA: 2^-9 per probability for bf16.  Over
+// many keys those roundings average out (for N(0,1) inputs the output error of a row with n visible
+// keys is about 1.9e-3 / sqrt(n) rms), but the first rows of a sequence see only a few keys and
+// reach 8e-3 max-abs, beyond the 2e-3 the fp16 path meets everywhere.  So the work item that holds
+// a sequence's first 256 query rows writes P as TWO terms, hi = round(p) and lo = round(p - hi),
+// and the MMA thread issues P.V for both (columns 0..63 and 64..127 of the S region): 2^-17 per
+// probability there.  That item is 3 of a sequence's ~150 tile steps; the rest is unchanged.
 constexpr int THREADS2 = 384;   // 3 warpgroups: softmax 0, softmax 1, {TMA, MMA, 2 idle warps}
-
-struct SmemLayout2 {
-    alignas(1024) unsigned char q[2][TILE_BYTES];
-    alignas(1024) unsigned char k[STAGES][TILE_BYTES];
-    alignas(1024) unsigned char v[STAGES][TILE_BYTES];
-    alignas(8) unsigned long long q_full;
-    unsigned long long s_full[2], p_half[2], p_full[2], o_full[2];
-    unsigned long long k_full[STAGES], k_empty[STAGES], v_full[STAGES], v_empty[STAGES];
-    unsigned int tmem_base;
-    int abort;
-};
-
 
 // One softmax thread = one query row (TMEM lane) of a 128-row tile: walks the key tiles, turns S into
 // P in place, keeps the running maximum lazily, and writes the normalised output row at the end.
@@ -88,8 +76,8 @@ template <typename T, int kPolyOf8>
 __device__ __forceinline__ void softmax_row(unsigned long long* s_full, unsigned long long* p_half,
                                             unsigned long long* p_full,
                                             unsigned long long* o_full, uint32_t s_addr, uint32_t o_addr, int nk,
-                                            int qpos, int r, int trace_role, const Params& p, volatile int* cta_abort,
-                                            bool row_valid, int64_t out_row, int h, int c0 = 0,
+                                            int qpos, int r, const Params& p, AbortBox* wc,
+                                            bool row_valid, int64_t out_row, int h, bool split, int c0 = 0,
                                             unsigned long long* o_free = nullptr) {
     // c0: tiles this warpgroup has processed before this call (persistent kernels keep their
     // barriers across work items, so the phase of tile j is (c0 + j) & 1); o_free, if given, is
@@ -100,15 +88,12 @@ __device__ __forceinline__ void softmax_row(unsigned long long* s_full, unsigned
         constexpr float kLazy = 8.f;
         bool ok = true;
         for (int j = 0; j < nk; ++j) {
-            if (r == 0) TRACE(trace_role, j, 0);
-            if (!(ok = mbar_wait(s_full, (c0 + j) & 1, cta_abort, p.err_flag))) break;
+            if (!(ok = mbar_wait(s_full, (c0 + j) & 1, wc))) break;
             tc_fence_after();
-            if (r == 0) TRACE(trace_role, j, 1);
             float sv[BN];
 #pragma unroll
             for (int c = 0; c < 4; ++c) tmem_ld32_nowait(s_addr + c * 32, sv + c * 32);
             tmem_ld_wait();
-            if (r == 0) TRACE(trace_role, j, 2);
             // key (j*BN + i) is visible to this row iff it is <= qpos (the row's position among the keys)
             const int lim = qpos - j * BN;
             if (lim < BN - 1) {
@@ -133,7 +118,7 @@ __device__ __forceinline__ void softmax_row(unsigned long long* s_full, unsigned
                 if (j > 0) {
                     const float alpha = fast_exp2(m_ref - m_new);
                     l *= alpha;
-                    if (!(ok = mbar_wait(o_full, (c0 + j - 1) & 1, cta_abort, p.err_flag))) break;
+                    if (!(ok = mbar_wait(o_full, (c0 + j - 1) & 1, wc))) break;
                     tc_fence_after();
 #pragma unroll
                     for (int c = 0; c < 4; ++c) {
@@ -147,7 +132,6 @@ __device__ __forceinline__ void softmax_row(unsigned long long* s_full, unsigned
                 }
                 m_ref = m_new;
             }
-            if (r == 0) TRACE(trace_role, j, 3);
             // P = 2^(s*scale - m_ref), rounded to the input type.  (fp16 inputs once took the packed
             // ex2.approx.f16x2 with fp16 row sums: its two results per operation cost the
             // special-function unit as much as two fp32 ex2, and the fp32 form measured 842 against
@@ -192,13 +176,30 @@ __device__ __forceinline__ void softmax_row(unsigned long long* s_full, unsigned
                 rs = (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
             }
             l += rs;
-            if (r == 0) TRACE(trace_role, j, 4);
+            if (split) {
+                // Second term of P for rows with few visible keys (see the note on `split` above the
+                // kernels): lo = p - round(p), rounded to the input type, into columns 64..127 of the
+                // S region (free: the whole S row is in registers).  Cold path: first item of a sequence.
+                const float nm = -m_ref;
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    uint32_t pk[32];
+#pragma unroll
+                    for (int i = 0; i < 64; i += 2) {
+                        const float p0 = fast_exp2(fmaf(sv[c * 64 + i], p.scale_log2, nm));
+                        const float p1 = fast_exp2(fmaf(sv[c * 64 + i + 1], p.scale_log2, nm));
+                        float h0, h1;
+                        unpack2(pack2<T>(p0, p1), T(), h0, h1);
+                        pk[i >> 1] = pack2<T>(p0 - h0, p1 - h1);
+                    }
+                    tmem_st32(s_addr + 64 + c * 32, pk);
+                }
+            }
             tmem_st_wait();
             tc_fence_before();
             mbar_arrive(p_full);
-            if (r == 0) TRACE(trace_role, j, 5);
         }
-        if (ok && nk > 0) ok = mbar_wait(o_full, (c0 + nk - 1) & 1, cta_abort, p.err_flag);
+        if (ok && nk > 0) ok = mbar_wait(o_full, (c0 + nk - 1) & 1, wc);
         if (ok && nk > 0) {
             tc_fence_after();
             const bool valid = row_valid;
@@ -232,192 +233,6 @@ __device__ __forceinline__ void softmax_row(unsigned long long* s_full, unsigned
         }
 }
 
-template <typename T>
-__global__ void __launch_bounds__(THREADS2, 1)
-prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                   const __grid_constant__ CUtensorMap map_v, const Params p) {
-    extern __shared__ unsigned char smem_raw[];
-    SmemLayout2& sm = *reinterpret_cast<SmemLayout2*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int b = blockIdx.z, h = blockIdx.y;
-    const int tp = p.n_qtiles - 1 - (int)blockIdx.x;       // pair index, heavy first (n_qtiles counts pairs here)
-    const int64_t seq_beg = b ? p.offsets[b - 1] : 0;
-    const int64_t seq_end = p.offsets[b];
-    if (seq_beg < 0 || seq_end < seq_beg || seq_end > p.n_tokens) {
-        if (p.err_flag && threadIdx.x == 0) atomicOr(p.err_flag, ATTN_B200_FLAG_BAD_OFFSETS);
-        return;
-    }
-    const int L = (int)(seq_end - seq_beg);
-    const int q0 = tp * 2 * BM;
-    if (q0 >= L) return;
-    if (*(volatile int*)&g_abort) return;
-    // key tiles per warpgroup: tile index of its query tile + 1; warpgroup 1 idle if its rows are past the end
-    const int n0 = 2 * tp + 1;
-    const int n1 = (q0 + BM < L) ? 2 * tp + 2 : 0;
-    const int nmax = n1 > n0 ? n1 : n0;
-    volatile int* cta_abort = &sm.abort;
-
-    if (threadIdx.x == 0) {
-        mbar_init(&sm.q_full, 1);
-        for (int w = 0; w < 2; ++w) {
-            mbar_init(&sm.s_full[w], 1);
-            mbar_init(&sm.p_half[w], 128);
-            mbar_init(&sm.p_full[w], 128);
-            mbar_init(&sm.o_full[w], 1);
-        }
-        for (int s = 0; s < STAGES; ++s) {
-            mbar_init(&sm.k_full[s], 1);
-            mbar_init(&sm.k_empty[s], 1);
-            mbar_init(&sm.v_full[s], 1);
-            mbar_init(&sm.v_empty[s], 1);
-        }
-        sm.abort = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    if (warp == 9) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(512));
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem = sm.tmem_base;
-    const int col0 = h * HD;
-
-    // Register reallocation.  The CTA is launched with 168 registers per thread (12 warps), and
-    // setmaxnreg can only move registers inside that allocation: 8 * 224 + 4 * 56 = 12 * 168.  A
-    // request beyond the pool would block forever, so these two numbers must keep that identity.
-    int issued = 0;   // producer: key tiles issued (for the drain on abort)
-    if (warp >= 8) {
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
-    if (warp == 8) {
-        // ------------------------------------------------------------------ TMA producer
-        if (lane == 0) {
-            mbar_expect_tx(&sm.q_full, 2 * TILE_BYTES);
-            for (int w = 0; w < 2; ++w) {
-                tma_load_2d(sm.q[w], &map_q, col0, (int)(seq_beg + q0 + w * BM), &sm.q_full);
-                tma_load_2d(sm.q[w] + SUB_BYTES, &map_q, col0 + 64, (int)(seq_beg + q0 + w * BM), &sm.q_full);
-            }
-            for (int j = 0; j < nmax; ++j) {
-                const int s = j & 1;
-                const uint32_t ph = ((j - STAGES) >> 1) & 1;
-                const int row = (int)(seq_beg + (int64_t)j * BN);
-                if (j >= STAGES && !mbar_wait(&sm.k_empty[s], ph, cta_abort, p.err_flag)) break;
-                mbar_expect_tx(&sm.k_full[s], TILE_BYTES);
-                tma_load_2d(sm.k[s], &map_k, col0, row, &sm.k_full[s]);
-                tma_load_2d(sm.k[s] + SUB_BYTES, &map_k, col0 + 64, row, &sm.k_full[s]);
-                if (j >= STAGES && !mbar_wait(&sm.v_empty[s], ph, cta_abort, p.err_flag)) { issued = j; break; }
-                mbar_expect_tx(&sm.v_full[s], TILE_BYTES);
-                tma_load_2d(sm.v[s], &map_v, col0, row, &sm.v_full[s]);
-                tma_load_2d(sm.v[s] + SUB_BYTES, &map_v, col0 + 64, row, &sm.v_full[s]);
-                issued = j + 1;
-            }
-        }
-    } else if (warp == 9) {
-        // ------------------------------------------------------------------ MMA issuer
-        constexpr uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
-        constexpr uint32_t idesc_qk = (1u << 4) | (fmt << 7) | (fmt << 10) | ((BN >> 3) << 17) | ((BM >> 4) << 24);
-        // P (A, from tensor memory) and V (B, MN-major) share the input type: a kind::f16 MMA with an
-        // fp16 A and a bf16 B raised an illegal-instruction fault on this hardware.
-        constexpr uint32_t idesc_pv = idesc_qk | (1u << 16);
-        const int nw[2] = {n0, n1};
-        // Descriptors are built once; a k-step only changes the start-address field (bits 0-13, in
-        // 16-byte units), so each MMA costs one 32-bit add per operand on the issuing thread, which
-        // would otherwise spend ~100 clocks of scalar code per instruction.
-        const uint64_t qd[2] = {smem_desc(smem_u32(sm.q[0]), 16, 1024), smem_desc(smem_u32(sm.q[1]), 16, 1024)};
-        const uint64_t kd[2] = {smem_desc(smem_u32(sm.k[0]), 16, 1024), smem_desc(smem_u32(sm.k[1]), 16, 1024)};
-        const uint64_t vd[2] = {smem_desc(smem_u32(sm.v[0]), SUB_BYTES, 1024), smem_desc(smem_u32(sm.v[1]), SUB_BYTES, 1024)};
-        auto issue_qk = [&](int w, int j) {      // S_w = Q_w K_j^T
-            const uint64_t a = qd[w], b2 = kd[j & 1];
-            const uint32_t d = tmem + w * 128;
-#pragma unroll
-            for (int kk = 0; kk < HD / 16; ++kk) {
-                constexpr int dummy = 0; (void)dummy;
-                const uint32_t off16 = ((kk >> 2) * SUB_BYTES + (kk & 3) * 32) >> 4;
-                umma_f16(d, a + off16, b2 + off16, idesc_qk, kk > 0);
-            }
-            umma_commit(&sm.s_full[w]);
-        };
-        // O_w (+)= P_w V_j, P_w in the first 64 columns of S_w; issued in two halves of 64 keys, the
-        // first as soon as the softmax threads have stored that half of P
-        auto issue_pv = [&](int w, int j, int half) {
-            const uint64_t b2 = vd[j & 1];
-            const uint32_t d = tmem + 256 + w * 128, a = tmem + w * 128;
-#pragma unroll
-            for (int k4 = 0; k4 < BN / 32; ++k4) {
-                const int kk = half * (BN / 32) + k4;
-                umma_f16_ts(d, a + kk * 8, b2 + ((kk * 2048) >> 4), idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
-            }
-            if (half) umma_commit(&sm.o_full[w]);
-        };
-        // one thread issues everything; it polls without suspending so that it reacts at once
-        if (elect_one()) {
-            bool ok = mbar_wait_spin(&sm.q_full, 0, cta_abort, p.err_flag) &&
-                      mbar_wait_spin(&sm.k_full[0], 0, cta_abort, p.err_flag);
-            if (ok) {
-                tc_fence_after();
-                issue_qk(0, 0);
-                if (n1 > 0) issue_qk(1, 0);
-                umma_commit(&sm.k_empty[0]);
-            }
-            for (int j = 0; ok && j < nmax; ++j) {
-                const int s = j & 1;
-                const uint32_t ph = (j >> 1) & 1;
-                for (int w = 0; w < 2 && ok; ++w) {
-                    if (j < nw[w]) {
-                        if (!(ok = mbar_wait_spin(&sm.p_half[w], j & 1, cta_abort, p.err_flag))) break;
-                        if (w == 0 || j >= n0) { if (!(ok = mbar_wait_spin(&sm.v_full[s], ph, cta_abort, p.err_flag))) break; }
-                        tc_fence_after();
-                        TRACE(2, j, w * 4 + 0); issue_pv(w, j, 0);
-                        if (!(ok = mbar_wait_spin(&sm.p_full[w], j & 1, cta_abort, p.err_flag))) break;
-                        tc_fence_after();
-                        issue_pv(w, j, 1); TRACE(2, j, w * 4 + 1);
-                    }
-                    if (w == 1) umma_commit(&sm.v_empty[s]);
-                    if (j + 1 < nw[w]) {
-                        if (w == 0 || j + 1 >= n0) {
-                            if (!(ok = mbar_wait_spin(&sm.k_full[(j + 1) & 1], ((j + 1) >> 1) & 1, cta_abort, p.err_flag))) break;
-                        }
-                        tc_fence_after();
-                        TRACE(2, j, w * 4 + 2); issue_qk(w, j + 1); TRACE(2, j, w * 4 + 3);
-                    }
-                    if (w == 1 && j + 1 < nmax) umma_commit(&sm.k_empty[(j + 1) & 1]);
-                }
-            }
-        }
-        __syncwarp();
-    }
-    } else {
-        // ------------------------------------------------------------------ softmax warpgroups
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
-        const int w = warp >> 2;                          // warpgroup = query tile of the pair
-        const int r = threadIdx.x & 127;                  // row of the tile == TMEM lane
-        const int nk = w ? n1 : n0;
-        const int tq = 2 * tp + w;                        // query tile index == index of its diagonal key tile
-        const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
-        const uint32_t s_addr = lane_base + w * 128, o_addr = lane_base + 256 + w * 128;
-        softmax_row<T, 2>(&sm.s_full[w], &sm.p_half[w], &sm.p_full[w], &sm.o_full[w], s_addr, o_addr, nk, tq * BM + r, r, w, p,
-                       cta_abort, q0 + w * BM + r < L, seq_beg + q0 + w * BM + r, h);
-    }
-    // ---------------------------------------------------------------------- teardown
-    if (warp == 8 && lane == 0 && sm.abort) {
-        const long long t0 = clock64();
-        while (!mbar_try(&sm.q_full, 0) && clock64() - t0 < WAIT_CYCLES) {}
-        for (int j = issued > STAGES ? issued - STAGES : 0; j < issued; ++j) {
-            const uint32_t ph = (j >> 1) & 1;
-            while (!(mbar_try(&sm.k_full[j & 1], ph) && mbar_try(&sm.v_full[j & 1], ph)) && clock64() - t0 < WAIT_CYCLES) {}
-        }
-    }
-    tc_fence_before();
-    __syncthreads();
-    if (warp == 9) {
-        tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512));
-    }
-}
-
-
 // =============================================================================================
 // Persistent form of the pair kernel.
 //
@@ -438,7 +253,18 @@ prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 // tiles of a pair are given to the warpgroups in alternating order from item to item: the early
 // starter takes the upper tile, which has one key tile more, and both finish together.
 // =============================================================================================
-static __device__ unsigned long long g_work[64];   // work counters of the persistent kernel, one slot per launch in flight
+
+// Per-launch state in global memory: the work counter of the persistent kernel and the abort word
+// that a CTA sets when one of its bounded waits runs out.  Launches in flight at the same time (on
+// different streams) must not share a slot, so each launch takes the next of kLaunchSlots slots in
+// rotation and zeroes it on its own stream.
+struct LaunchState {
+    unsigned long long work;
+    int abort;
+    int pad;
+};
+constexpr int kLaunchSlots = 64;
+static __device__ LaunchState g_launch[kLaunchSlots];
 
 struct SmemLayout2p {
     alignas(1024) unsigned char q[2][TILE_BYTES];
@@ -454,7 +280,7 @@ struct SmemLayout2p {
     unsigned long long s_full[2], p_half[2], p_full[2], o_full[2], o_free[2];
     unsigned long long k_full[STAGES], k_empty[STAGES], v_full[STAGES], v_empty[STAGES];
     unsigned int tmem_base;
-    int abort;
+    AbortBox box;
 };
 
 // Work item -> (pair index, head, sequence).  (sequence, head) combinations are taken in groups of
@@ -462,10 +288,7 @@ struct SmemLayout2p {
 // group come first while the CTAs running at any moment share the K/V of a few dozen (sequence,
 // head) combinations, which stay in L2 (with the pair index slowest over ALL combinations every CTA
 // would stream its own K/V from DRAM: measured 814 against 960 TFLOP/s).
-#ifndef ATTN_B200_ITEM_GROUP
-#define ATTN_B200_ITEM_GROUP 16
-#endif
-constexpr int ITEM_GROUP = ATTN_B200_ITEM_GROUP;
+constexpr int ITEM_GROUP = 16;
 struct Item2p {
     int tp, h, b, L, q0, n0, n1, nmax;
     int64_t seq_beg;
@@ -506,8 +329,8 @@ prefill_tc2p_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     SmemLayout2p& sm = *reinterpret_cast<SmemLayout2p*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    if (*(volatile int*)&g_abort) return;
-    volatile int* cta_abort = &sm.abort;
+    if (*(volatile int*)p.launch_abort) return;
+    AbortBox* const wc = &sm.box;
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < 4; ++i) mbar_init(&sm.item_full[i], 1);
@@ -526,7 +349,9 @@ prefill_tc2p_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             mbar_init(&sm.v_full[s], 1);
             mbar_init(&sm.v_empty[s], 1);
         }
-        sm.abort = 0;
+        sm.box.abort = 0;
+        sm.box.launch_abort = p.launch_abort;
+        sm.box.err_flag = p.err_flag;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 9) {
@@ -565,7 +390,7 @@ prefill_tc2p_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 auto load_q = [&](int w) -> bool {       // query tile of warpgroup w, once its buffer is free
                     const int u = upper_of(w, n_it);
                     if ((u ? it.n1 : it.n0) == 0) return true;
-                    if (q_issued[w] > 0 && !mbar_wait(&sm.q_empty[w], (q_issued[w] - 1) & 1, cta_abort, p.err_flag)) return false;
+                    if (q_issued[w] > 0 && !mbar_wait(&sm.q_empty[w], (q_issued[w] - 1) & 1, wc)) return false;
                     const int row = (int)(it.seq_beg + it.q0 + u * BM);
                     mbar_expect_tx(&sm.q_full[w], TILE_BYTES);
                     tma_load_2d(sm.q[w], &map_q, col0, row, &sm.q_full[w]);
@@ -582,13 +407,13 @@ prefill_tc2p_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                     const int s = g & 1;
                     const uint32_t ph = ((g - STAGES) >> 1) & 1;
                     const int row = (int)(it.seq_beg + (int64_t)j * BN);
-                    if (g >= STAGES && !(ok = mbar_wait(&sm.k_empty[s], ph, cta_abort, p.err_flag))) break;
+                    if (g >= STAGES && !(ok = mbar_wait(&sm.k_empty[s], ph, wc))) break;
                     mbar_expect_tx(&sm.k_full[s], TILE_BYTES);
                     tma_load_2d(sm.k[s], &map_k, col0, row, &sm.k_full[s]);
                     tma_load_2d(sm.k[s] + SUB_BYTES, &map_k, col0 + 64, row, &sm.k_full[s]);
                     g_issued_k = g + 1;
                     if (j == 0 && !(ok = load_q(w_first ^ 1))) break;
-                    if (g >= STAGES && !(ok = mbar_wait(&sm.v_empty[s], ph, cta_abort, p.err_flag))) break;
+                    if (g >= STAGES && !(ok = mbar_wait(&sm.v_empty[s], ph, wc))) break;
                     mbar_expect_tx(&sm.v_full[s], TILE_BYTES);
                     tma_load_2d(sm.v[s], &map_v, col0, row, &sm.v_full[s]);
                     tma_load_2d(sm.v[s] + SUB_BYTES, &map_v, col0 + 64, row, &sm.v_full[s]);
@@ -616,13 +441,19 @@ prefill_tc2p_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 }
                 umma_commit(&sm.s_full[w]);
             };
-            auto issue_pv = [&](int w, int stage, int half, bool first) {   // O_w (+)= P_w V, 64 keys per call
+            // O_w (+)= P_w V, 64 keys per call; with `split` the second call adds the lo term of all 128 keys
+            auto issue_pv = [&](int w, int stage, int half, bool first, bool split) {
                 const uint64_t b2 = vd[stage];
                 const uint32_t d = tmem + 256 + w * 128, a = tmem + w * 128;
 #pragma unroll
                 for (int k4 = 0; k4 < BN / 32; ++k4) {
                     const int kk = half * (BN / 32) + k4;
                     umma_f16_ts(d, a + kk * 8, b2 + ((kk * 2048) >> 4), idesc_pv, (!first || kk > 0) ? 1u : 0u);
+                }
+                if (half && split) {        // cold path: a rolled loop keeps the issuing thread's register count down
+#pragma unroll 1
+                    for (int kk = 0; kk < BN / 16; ++kk)
+                        umma_f16_ts(d, a + 64 + kk * 8, b2 + (uint64_t)(kk * (2048 >> 4)), idesc_pv, 1u);
                 }
                 if (half) umma_commit(&sm.o_full[w]);
             };
@@ -632,7 +463,7 @@ prefill_tc2p_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             bool early = false;       // the upper tile's first Q.K of item n was issued during item n-1
             bool ok = true;
             while (ok) {
-                if (!(ok = mbar_wait_spin(&sm.item_full[n & 3], (n >> 2) & 1, cta_abort, p.err_flag))) break;
+                if (!(ok = mbar_wait_spin(&sm.item_full[n & 3], (n >> 2) & 1, wc))) break;
                 const long long id = sm.item_id[n & 3];
                 if (id < 0) break;
                 const Item2p it = decode_item(p, id);
@@ -642,13 +473,13 @@ prefill_tc2p_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 int nw[2];
                 nw[wu] = it.n1;
                 nw[wl] = it.n0;
-                if (!(ok = mbar_wait_spin(&sm.k_full[g & 1], (g >> 1) & 1, cta_abort, p.err_flag))) break;
+                if (!(ok = mbar_wait_spin(&sm.k_full[g & 1], (g >> 1) & 1, wc))) break;
                 if (it.n1 > 0 && !early) {
-                    if (!(ok = mbar_wait_spin(&sm.q_full[wu], uses[wu] & 1, cta_abort, p.err_flag))) break;
+                    if (!(ok = mbar_wait_spin(&sm.q_full[wu], uses[wu] & 1, wc))) break;
                     tc_fence_after();
                     issue_qk(wu, g & 1);
                 }
-                if (!(ok = mbar_wait_spin(&sm.q_full[wl], uses[wl] & 1, cta_abort, p.err_flag))) break;
+                if (!(ok = mbar_wait_spin(&sm.q_full[wl], uses[wl] & 1, wc))) break;
                 tc_fence_after();
                 issue_qk(wl, g & 1);
                 umma_commit(&sm.k_empty[g & 1]);
@@ -679,21 +510,21 @@ prefill_tc2p_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                         const int w = t ? wl : wu;
                         if (j < nw[w]) {
                             if (j == 0 && uses[w] > 0) {     // the previous item's O must have been read out
-                                if (!(ok = mbar_wait_spin(&sm.o_free[w], (uses[w] - 1) & 1, cta_abort, p.err_flag))) break;
+                                if (!(ok = mbar_wait_spin(&sm.o_free[w], (uses[w] - 1) & 1, wc))) break;
                             }
-                            if (!(ok = mbar_wait_spin(&sm.p_half[w], (c[w] + j) & 1, cta_abort, p.err_flag))) break;
-                            if (t == 0 || j >= nw[wu]) { if (!(ok = mbar_wait_spin(&sm.v_full[s], ph, cta_abort, p.err_flag))) break; }
+                            if (!(ok = mbar_wait_spin(&sm.p_half[w], (c[w] + j) & 1, wc))) break;
+                            if (t == 0 || j >= nw[wu]) { if (!(ok = mbar_wait_spin(&sm.v_full[s], ph, wc))) break; }
                             tc_fence_after();
-                            issue_pv(w, s, 0, j == 0);
-                            if (!(ok = mbar_wait_spin(&sm.p_full[w], (c[w] + j) & 1, cta_abort, p.err_flag))) break;
+                            issue_pv(w, s, 0, j == 0, false);
+                            if (!(ok = mbar_wait_spin(&sm.p_full[w], (c[w] + j) & 1, wc))) break;
                             tc_fence_after();
-                            issue_pv(w, s, 1, j == 0);
+                            issue_pv(w, s, 1, j == 0, it.tp == 0);
                         }
                         if (t == 1) umma_commit(&sm.v_empty[s]);
                         if (j + 1 < nw[w]) {
                             const int s1 = (g + j + 1) & 1;
                             if (t == 0 || j + 1 >= nw[wu]) {
-                                if (!(ok = mbar_wait_spin(&sm.k_full[s1], ((g + j + 1) >> 1) & 1, cta_abort, p.err_flag))) break;
+                                if (!(ok = mbar_wait_spin(&sm.k_full[s1], ((g + j + 1) >> 1) & 1, wc))) break;
                             }
                             tc_fence_after();
                             issue_qk(w, s1);
@@ -721,22 +552,23 @@ prefill_tc2p_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         const uint32_t s_addr = lane_base + w * 128, o_addr = lane_base + 256 + w * 128;
         int c0 = 0;
         for (int n_it = 0;; ++n_it) {
-            if (!mbar_wait(&sm.item_full[n_it & 3], (n_it >> 2) & 1, cta_abort, p.err_flag)) break;
+            if (!mbar_wait(&sm.item_full[n_it & 3], (n_it >> 2) & 1, wc)) break;
             const long long id = sm.item_id[n_it & 3];
             if (id < 0) break;
             const Item2p it = decode_item(p, id);
-            if (*cta_abort) break;
+            if (wc->abort) break;
             const int u = upper_of(w, n_it);
             const int nk = u ? it.n1 : it.n0;
             if (nk == 0) continue;
             const int tq = 2 * it.tp + u;
-            softmax_row<T, 2>(&sm.s_full[w], &sm.p_half[w], &sm.p_full[w], &sm.o_full[w], s_addr, o_addr, nk, tq * BM + r, r, w, p,
-                              cta_abort, it.q0 + u * BM + r < it.L, it.seq_beg + it.q0 + u * BM + r, it.h, c0, &sm.o_free[w]);
+            softmax_row<T, 2>(&sm.s_full[w], &sm.p_half[w], &sm.p_full[w], &sm.o_full[w], s_addr, o_addr, nk, tq * BM + r, r, p,
+                              wc, it.q0 + u * BM + r < it.L, it.seq_beg + it.q0 + u * BM + r, it.h, it.tp == 0, c0,
+                              &sm.o_free[w]);
             c0 += nk;
         }
     }
     // ---------------------------------------------------------------------- teardown
-    if (warp == 8 && lane == 0 && sm.abort) {
+    if (warp == 8 && lane == 0 && sm.box.abort) {
         // give the copies still in flight a bounded time to land before shared memory is released
         const long long t0 = clock64();
         for (int w = 0; w < 2; ++w)
@@ -792,7 +624,7 @@ struct SmemLayoutPg {
     unsigned long long s_full[2], p_half[2], p_full[2], o_full[2];
     unsigned long long k_full[KSTAGES_PG], k_empty[KSTAGES_PG], v_full[STAGES], v_empty[STAGES];
     unsigned int tmem_base;
-    int abort;
+    AbortBox box;
 };
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes) {
@@ -818,7 +650,7 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const Params 
     const int q_len = (int)(q_end - q_beg), kv_len = (int)(kv_end - kv_beg);
     const int q0 = tp * 2 * BM;
     if (q0 >= q_len) return;
-    if (*(volatile int*)&g_abort) return;
+    if (*(volatile int*)p.launch_abort) return;
     const int shift = kv_len - q_len;
     // key tiles per warpgroup: up to the tile that holds its last row's last visible key
     auto tiles_for = [&](int w) {
@@ -829,7 +661,10 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const Params 
     };
     const int n0 = tiles_for(0), n1 = tiles_for(1);
     const int nmax = n1 > n0 ? n1 : n0;
-    volatile int* cta_abort = &sm.abort;
+    AbortBox* const wc = &sm.box;
+    // two-term P where rows see few keys: the chunk's first 256 rows, unless a prefix of >= 256
+    // cached tokens already gives every row that many keys
+    const bool split = tp == 0 && shift < 2 * BM;
 
     if (threadIdx.x == 0) {
         mbar_init(&sm.q_full, 1);
@@ -847,7 +682,9 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const Params 
             mbar_init(&sm.v_full[s], 64);
             mbar_init(&sm.v_empty[s], 1);
         }
-        sm.abort = 0;
+        sm.box.abort = 0;
+        sm.box.launch_abort = p.launch_abort;
+        sm.box.err_flag = p.err_flag;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 9) {
@@ -906,7 +743,7 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const Params 
             const int s = j % n_stages;
             int sa, sb;
             tile_slots(j, sa, sb);
-            if (j >= n_stages) ok = mbar_wait(&empty[s], ((j - n_stages) / n_stages) & 1, cta_abort, p.err_flag);
+            if (j >= n_stages) ok = mbar_wait(&empty[s], ((j - n_stages) / n_stages) & 1, wc);
             if (!__all_sync(0xffffffffu, ok)) break;
             const uint32_t sbase = smem_u32(stage[s]) + dst_off;
             const uint32_t be = sbase + swz_even, bo = sbase + swz_odd;
@@ -935,7 +772,7 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const Params 
                 }
             }
         } else if (warp == 9) {
-            // -------------------------------------------------------------- MMA issuer (as version 2)
+            // -------------------------------------------------------------- MMA issuer
             constexpr uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
             constexpr uint32_t idesc_qk = (1u << 4) | (fmt << 7) | (fmt << 10) | ((BN >> 3) << 17) | ((BM >> 4) << 24);
             constexpr uint32_t idesc_pv = idesc_qk | (1u << 16);
@@ -961,10 +798,15 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const Params 
                         const int kk = half * (BN / 32) + k4;
                         umma_f16_ts(d, a + kk * 8, b2 + ((kk * 2048) >> 4), idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
                     }
+                    if (half && split) {      // the lo term of P (columns 64..127 of the S region), all 128 keys
+#pragma unroll 1
+                        for (int kk = 0; kk < BN / 16; ++kk)
+                            umma_f16_ts(d, a + 64 + kk * 8, b2 + (uint64_t)(kk * (2048 >> 4)), idesc_pv, 1u);
+                    }
                     if (half) umma_commit(&sm.o_full[w]);
                 };
-                bool ok = mbar_wait_spin(&sm.q_full, 0, cta_abort, p.err_flag) &&
-                          mbar_wait_spin(&sm.k_full[0], 0, cta_abort, p.err_flag);
+                bool ok = mbar_wait_spin(&sm.q_full, 0, wc) &&
+                          mbar_wait_spin(&sm.k_full[0], 0, wc);
                 if (ok) {
                     tc_fence_after();
                     issue_qk(0, 0);
@@ -976,21 +818,21 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const Params 
                     const uint32_t ph = (j >> 1) & 1;
                     for (int w = 0; w < 2 && ok; ++w) {
                         if (j < nw[w]) {
-                            if (!(ok = mbar_wait_spin(&sm.p_half[w], j & 1, cta_abort, p.err_flag))) break;
-                            if (w == 0 || j >= n0) { if (!(ok = mbar_wait_spin(&sm.v_full[s], ph, cta_abort, p.err_flag))) break; }
+                            if (!(ok = mbar_wait_spin(&sm.p_half[w], j & 1, wc))) break;
+                            if (w == 0 || j >= n0) { if (!(ok = mbar_wait_spin(&sm.v_full[s], ph, wc))) break; }
                             tc_fence_after();
-                            TRACE(2, j, w * 4 + 0); issue_pv(w, j, 0);
-                            if (!(ok = mbar_wait_spin(&sm.p_full[w], j & 1, cta_abort, p.err_flag))) break;
+                            issue_pv(w, j, 0);
+                            if (!(ok = mbar_wait_spin(&sm.p_full[w], j & 1, wc))) break;
                             tc_fence_after();
-                            issue_pv(w, j, 1); TRACE(2, j, w * 4 + 1);
+                            issue_pv(w, j, 1);
                         }
                         if (w == 1) umma_commit(&sm.v_empty[s]);
                         if (j + 1 < nw[w]) {
                             if (w == 0 || j + 1 >= n0) {
-                                if (!(ok = mbar_wait_spin(&sm.k_full[(j + 1) % KSTAGES_PG], ((j + 1) / KSTAGES_PG) & 1, cta_abort, p.err_flag))) break;
+                                if (!(ok = mbar_wait_spin(&sm.k_full[(j + 1) % KSTAGES_PG], ((j + 1) / KSTAGES_PG) & 1, wc))) break;
                             }
                             tc_fence_after();
-                            TRACE(2, j, w * 4 + 2); issue_qk(w, j + 1); TRACE(2, j, w * 4 + 3);
+                            issue_qk(w, j + 1);
                         }
                         if (w == 1 && j + 1 < nmax) umma_commit(&sm.k_empty[(j + 1) % KSTAGES_PG]);
                     }
@@ -1007,10 +849,10 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const Params 
         const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
         const int qi = q0 + w * BM + r;                    // row within the chunk
         softmax_row<T, 0>(&sm.s_full[w], &sm.p_half[w], &sm.p_full[w], &sm.o_full[w], lane_base + w * 128, lane_base + 256 + w * 128,
-                       nk, shift + qi, r, w, p, cta_abort, qi < q_len, q_beg + qi, h);
+                       nk, shift + qi, r, p, wc, qi < q_len, q_beg + qi, h, split);
     }
     // ---------------------------------------------------------------------- teardown
-    if (warp == 8 && lane == 0 && sm.abort) {
+    if (warp == 8 && lane == 0 && sm.box.abort) {
         const long long t0 = clock64();
         while (!mbar_try(&sm.q_full, 0) && clock64() - t0 < WAIT_CYCLES) {}
     }
@@ -1021,16 +863,31 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const Params 
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512));
     }
 }
-// Rows of the packed buffer past the last sequence belong to no query tile; zero them so that the
-// output never carries uninitialised memory (the reference returns zeros there, zeros_like(V)).
-__global__ void zero_tail_kernel(void* out, const int32_t* offsets, int B, int64_t n_tokens, int64_t row_bytes) {
-    int64_t beg = offsets[B - 1];
-    if (beg < 0) beg = 0;
-    if (beg >= n_tokens) return;
-    const int64_t n_vec = (n_tokens - beg) * row_bytes / 16;
-    uint4* base = reinterpret_cast<uint4*>((char*)out + beg * row_bytes);
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_vec; i += (int64_t)gridDim.x * blockDim.x)
-        base[i] = make_uint4(0, 0, 0, 0);
+// Rows no query tile writes: those past the last sequence, and (when the caller's max_len is too
+// small, which also raises ATTN_B200_FLAG_BAD_OFFSETS) the rows of a sequence beyond max_len rounded
+// up to a pair of query tiles.  They are zeroed so that the output never carries uninitialised
+// memory (the reference returns zeros there, zeros_like(V)).
+__global__ void zero_uncovered_rows_kernel(void* out, const int32_t* offsets, int B, int64_t n_tokens, int max_len,
+                                           int64_t row_bytes, int32_t* err_flag) {
+    const int64_t vec_per_row = row_bytes / 16;
+    const int64_t covered = (int64_t)((max_len + 2 * BM - 1) / (2 * BM)) * (2 * BM);
+    auto clampt = [&](int64_t v) { return v < 0 ? (int64_t)0 : (v > n_tokens ? n_tokens : v); };
+    auto zero_rows = [&](int64_t beg, int64_t end) {
+        uint4* base = reinterpret_cast<uint4*>((char*)out + beg * row_bytes);
+        const int64_t n_vec = (end - beg) * vec_per_row;
+        for (int64_t i = threadIdx.x; i < n_vec; i += blockDim.x) base[i] = make_uint4(0, 0, 0, 0);
+    };
+    // CTA x takes sequences x, x + gridDim.x, ...; pseudo-sequence B is the tail past offsets[B-1]
+    for (int b = blockIdx.x; b <= B; b += gridDim.x) {
+        const int64_t beg = b ? clampt(offsets[b - 1]) : 0;
+        const int64_t end = b < B ? clampt(offsets[b]) : n_tokens;
+        if (end <= beg) continue;
+        if (b == B) { zero_rows(beg, end); continue; }
+        if (end - beg > covered) {
+            if (err_flag && threadIdx.x == 0) atomicOr(err_flag, ATTN_B200_FLAG_BAD_OFFSETS);
+            zero_rows(beg + covered, end);
+        }
+    }
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -1054,7 +911,18 @@ static EncodeTiledFn encode_fn() {
 }
 
 // [n_tokens, H*128] 16-bit row-major; box = 64 elements (128 B) x 128 rows, 128-byte swizzle.
+// A tensor map is a pure function of (base, n_tokens, H, dtype), so the last few are kept per host
+// thread: a serving loop that calls with the same buffers pays for the encoding once.
 static int make_map(CUtensorMap* map, const void* base, int64_t n_tokens, int H, int dtype) {
+    struct Entry { const void* base; int64_t n_tokens; int H, dtype; bool used; CUtensorMap map; };
+    constexpr int kEntries = 8;
+    static thread_local Entry cache[kEntries] = {};
+    static thread_local unsigned next = 0;
+    for (const Entry& e : cache)
+        if (e.used && e.base == base && e.n_tokens == n_tokens && e.H == H && e.dtype == dtype) {
+            *map = e.map;
+            return 0;
+        }
     EncodeTiledFn fn = encode_fn();
     if (!fn) return (int)cudaErrorNotSupported;
     const cuuint64_t dims[2] = {(cuuint64_t)H * HD, (cuuint64_t)n_tokens};
@@ -1065,16 +933,60 @@ static int make_map(CUtensorMap* map, const void* base, int64_t n_tokens, int H,
                           2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
+    if (r != CUDA_SUCCESS) return (int)cudaErrorInvalidValue;
+    cache[next++ % kEntries] = Entry{base, n_tokens, H, dtype, true, *map};
+    return 0;
+}
+
+// Per-device facts looked up once: the device address of g_launch, the SM count, and whether the
+// kernels' dynamic shared-memory limits have been raised.
+constexpr int kMaxDevices = 64;
+struct DeviceState {
+    LaunchState* launch_base = nullptr;
+    int n_sm = 0;
+    bool attrs_set = false;
+};
+static std::mutex g_dev_mu;
+static DeviceState g_dev[kMaxDevices];
+
+template <typename K>
+static cudaError_t raise_smem(K kernel, int bytes) {
+    return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+}
+
+static int device_state(DeviceState* out) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= kMaxDevices) return ATTN_B200_ETOOLARGE;
+    std::lock_guard<std::mutex> lock(g_dev_mu);
+    DeviceState& d = g_dev[dev];
+    if (!d.launch_base) {
+        void* base = nullptr;
+        if ((e = cudaGetSymbolAddress(&base, g_launch)) != cudaSuccess) return (int)e;
+        if ((e = cudaDeviceGetAttribute(&d.n_sm, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return (int)e;
+        d.launch_base = static_cast<LaunchState*>(base);
+    }
+    if (!d.attrs_set) {
+        if ((e = raise_smem(prefill_tc2p_kernel<__nv_bfloat16>, (int)sizeof(SmemLayout2p) + 1024)) != cudaSuccess ||
+            (e = raise_smem(prefill_tc2p_kernel<__half>, (int)sizeof(SmemLayout2p) + 1024)) != cudaSuccess ||
+            (e = raise_smem(paged_prefill_tc_kernel<__nv_bfloat16>, (int)sizeof(SmemLayoutPg) + 1024)) != cudaSuccess ||
+            (e = raise_smem(paged_prefill_tc_kernel<__half>, (int)sizeof(SmemLayoutPg) + 1024)) != cudaSuccess)
+            return (int)e;
+        d.attrs_set = true;
+    }
+    *out = d;
+    return 0;
+}
+
+// Takes the next of the kLaunchSlots launch-state slots and zeroes it on the launch's stream.
+static int take_launch_slot(const DeviceState& d, cudaStream_t st, LaunchState** slot) {
+    static std::atomic<unsigned> next_slot{0};
+    *slot = d.launch_base + (next_slot.fetch_add(1) % kLaunchSlots);
+    return (int)cudaMemsetAsync(*slot, 0, sizeof(LaunchState), st);
 }
 
 }  // namespace tc
-
-#ifdef ATTN_B200_TRACE
-extern "C" __attribute__((visibility("default"))) int attn_b200_debug_read_trace(long long* host, int n) {
-    return (int)cudaMemcpyFromSymbol(host, tc::g_trace, sizeof(long long) * n);
-}
-#endif
 
 bool prefill_tc_supported(int D, int dtype) {
     return D == tc::HD && (dtype == ATTN_B200_F16 || dtype == ATTN_B200_BF16);
@@ -1092,50 +1004,21 @@ int prefill_tc_launch(const void* q, const void* k, const void* v, const int32_t
     if ((rc = make_map(&mq, q, n_tokens, H, dtype)) || (rc = make_map(&mk, k, n_tokens, H, dtype)) ||
         (rc = make_map(&mv, v, n_tokens, H, dtype)))
         return rc;
-    static const int version = [] { const char* e = getenv("ATTN_B200_PREFILL_VERSION"); return e ? atoi(e) : 6; }();
-    const bool persistent = version != 2;
-    Params p{offsets, out, B, H, n_tokens, (max_len + 2 * BM - 1) / (2 * BM), scale * kLog2e, out_f32, err_flag};
-    void* abort_addr = nullptr;
-    cudaError_t e = cudaGetSymbolAddress(&abort_addr, g_abort);
-    if (e != cudaSuccess) return (int)e;
-    if ((e = cudaMemsetAsync(abort_addr, 0, sizeof(int), st)) != cudaSuccess) return (int)e;
-    zero_tail_kernel<<<64, 256, 0, st>>>(out, offsets, B, n_tokens, (int64_t)H * HD * (out_f32 ? 4 : 2));
-    if (persistent) {
-        int dev = 0, n_sm = 0;
-        if ((e = cudaGetDevice(&dev)) != cudaSuccess) return (int)e;
-        if ((e = cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return (int)e;
-        const int64_t n_items = (((int64_t)H * B + ITEM_GROUP - 1) / ITEM_GROUP) * ITEM_GROUP * p.n_qtiles;
-        const int smem_p = (int)sizeof(SmemLayout2p) + 1024;
-        // work counter of this launch: one of 64 slots taken in rotation, zeroed on the launch's
-        // stream (launches in flight at the same time on different streams need different slots)
-        static std::atomic<unsigned> next_slot{0};
-        void* work_base = nullptr;
-        if ((e = cudaGetSymbolAddress(&work_base, g_work)) != cudaSuccess) return (int)e;
-        unsigned long long* work_counter = (unsigned long long*)work_base + (next_slot.fetch_add(1) & 63u);
-        if ((e = cudaMemsetAsync(work_counter, 0, sizeof(unsigned long long), st)) != cudaSuccess) return (int)e;
-        const unsigned ctas = (unsigned)(n_items < n_sm ? n_items : n_sm);
-        if (dtype == ATTN_B200_BF16) {
-            if ((e = cudaFuncSetAttribute(prefill_tc2p_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_p)) != cudaSuccess)
-                return (int)e;
-            prefill_tc2p_kernel<__nv_bfloat16><<<ctas, THREADS2, smem_p, st>>>(mq, mk, mv, p, n_items, work_counter);
-        } else {
-            if ((e = cudaFuncSetAttribute(prefill_tc2p_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_p)) != cudaSuccess)
-                return (int)e;
-            prefill_tc2p_kernel<__half><<<ctas, THREADS2, smem_p, st>>>(mq, mk, mv, p, n_items, work_counter);
-        }
-        return (int)cudaGetLastError();
-    }
-    const int smem = (int)sizeof(SmemLayout2) + 1024;
-    dim3 grid(p.n_qtiles, H, B);
-    if (dtype == ATTN_B200_BF16) {
-        if ((e = cudaFuncSetAttribute(prefill_tc2_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) != cudaSuccess)
-            return (int)e;
-        prefill_tc2_kernel<__nv_bfloat16><<<grid, THREADS2, smem, st>>>(mq, mk, mv, p);
-    } else {
-        if ((e = cudaFuncSetAttribute(prefill_tc2_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) != cudaSuccess)
-            return (int)e;
-        prefill_tc2_kernel<__half><<<grid, THREADS2, smem, st>>>(mq, mk, mv, p);
-    }
+    DeviceState d;
+    LaunchState* slot = nullptr;
+    if ((rc = device_state(&d)) || (rc = take_launch_slot(d, st, &slot))) return rc;
+    Params p{offsets, out, B, H, n_tokens, (max_len + 2 * BM - 1) / (2 * BM), scale * kLog2e, out_f32, err_flag,
+             &slot->abort};
+    const int64_t row_bytes = (int64_t)H * HD * (out_f32 ? 4 : 2);
+    zero_uncovered_rows_kernel<<<64, 256, 0, st>>>(out, offsets, B, n_tokens, max_len, row_bytes, err_flag);
+    const int64_t n_items = (((int64_t)H * B + ITEM_GROUP - 1) / ITEM_GROUP) * ITEM_GROUP * p.n_qtiles;
+    if (n_items == 0) return (int)cudaGetLastError();
+    const int smem_p = (int)sizeof(SmemLayout2p) + 1024;
+    const unsigned ctas = (unsigned)(n_items < d.n_sm ? n_items : d.n_sm);
+    if (dtype == ATTN_B200_BF16)
+        prefill_tc2p_kernel<__nv_bfloat16><<<ctas, THREADS2, smem_p, st>>>(mq, mk, mv, p, n_items, &slot->work);
+    else
+        prefill_tc2p_kernel<__half><<<ctas, THREADS2, smem_p, st>>>(mq, mk, mv, p, n_items, &slot->work);
     return (int)cudaGetLastError();
 }
 
@@ -1152,24 +1035,20 @@ int paged_prefill_tc_launch_impl(const void* q, const void* k_cache, const void*
     CUtensorMap mq;
     int rc = make_map(&mq, q, n_q_tokens, H, dtype);
     if (rc) return rc;
+    DeviceState d;
+    LaunchState* slot = nullptr;
+    if ((rc = device_state(&d)) || (rc = take_launch_slot(d, st, &slot))) return rc;
     const int smem = (int)sizeof(SmemLayoutPg) + 1024;
-    Params p{q_offsets, out, B, H, n_q_tokens, (max_q_len + 2 * BM - 1) / (2 * BM), scale * kLog2e, 0, err_flag};
+    Params p{q_offsets, out, B, H, n_q_tokens, (max_q_len + 2 * BM - 1) / (2 * BM), scale * kLog2e, 0, err_flag,
+             &slot->abort};
     PagedTcParams pg{slots, kv_offsets, q_offsets, k_cache, v_cache, Hkv, n_kv_tokens, n_slots};
+    zero_uncovered_rows_kernel<<<64, 256, 0, st>>>(out, q_offsets, B, n_q_tokens, max_q_len, (int64_t)H * HD * 2, err_flag);
+    if (p.n_qtiles == 0) return (int)cudaGetLastError();
     dim3 grid(p.n_qtiles, H, B);
-    void* abort_addr = nullptr;
-    cudaError_t e = cudaGetSymbolAddress(&abort_addr, g_abort);
-    if (e != cudaSuccess) return (int)e;
-    if ((e = cudaMemsetAsync(abort_addr, 0, sizeof(int), st)) != cudaSuccess) return (int)e;
-    zero_tail_kernel<<<64, 256, 0, st>>>(out, q_offsets, B, n_q_tokens, (int64_t)H * HD * 2);
-    if (dtype == ATTN_B200_BF16) {
-        if ((e = cudaFuncSetAttribute(paged_prefill_tc_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) != cudaSuccess)
-            return (int)e;
+    if (dtype == ATTN_B200_BF16)
         paged_prefill_tc_kernel<__nv_bfloat16><<<grid, THREADS_PG, smem, st>>>(mq, p, pg);
-    } else {
-        if ((e = cudaFuncSetAttribute(paged_prefill_tc_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) != cudaSuccess)
-            return (int)e;
+    else
         paged_prefill_tc_kernel<__half><<<grid, THREADS_PG, smem, st>>>(mq, p, pg);
-    }
     return (int)cudaGetLastError();
 }
 

@@ -87,6 +87,10 @@ rope_write_kv_kernel(const RopeKvParams p) {
     uint4* qrow = p.q + token * p.hq * hv;
     uint4* krow = p.k + token * p.hk * hv;
     const uint4* vrow = p.v + token * p.hk * hv;
+    // A token with a bad position is left alone altogether (q and k unrotated, nothing appended): a
+    // pool row holding the new v beside a stale or unrotated k would be worse than a missing row.
+    // A token with a good position and a bad slot is rotated in place and not appended.
+    if (!pos_ok) return;
     auto store_cache = [&](void* cache, const float* scale, int head, int vec_in_row, const uint4& val) {
         if (!slot_ok) return;
         const int64_t vec = slot * p.hk * hv + vec_in_row;          // in 8-element units
@@ -114,7 +118,6 @@ rope_write_kv_kernel(const RopeKvParams p) {
         const int head = r / pass_k, chunk = 2 * cph + (r - head * pass_k);
         store_cache(p.k_cache, p.k_scale, head, head * hv + chunk, krow[head * hv + chunk]);
     }
-    if (!pos_ok) return;
     // ---- rotated dims of q and k: a thread owns a chunk and its partner chunk (both read before either is written)
     const uint4* cosr = p.cos + (int64_t)pos * cph;
     const uint4* sinr = p.sin + (int64_t)pos * cph;

@@ -10,8 +10,15 @@ namespace tc {
 
 constexpr long long WAIT_CYCLES = 2000000000LL;
 
-// set by the first CTA whose wait expired; reset by the launcher before every launch
-static __device__ int g_abort;
+// What a bounded wait needs in order to give up cleanly, kept in shared memory so that the waits
+// carry one pointer: the CTA's abort word (the CTA's other roles leave their loops), the launch's
+// abort word (global memory, one per launch in flight; CTAs of the same launch that start later
+// exit at once) and the caller's error flag.
+struct AbortBox {
+    volatile int abort;
+    int* launch_abort;
+    int32_t* err_flag;
+};
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -38,17 +45,20 @@ __device__ __forceinline__ bool mbar_test(void* bar, uint32_t parity) {
     return ok != 0;
 }
 // Bounded wait.  Returns false if the CTA is aborting or the limit ran out (then it raises the abort).
-__device__ __forceinline__ bool mbar_wait(void* bar, uint32_t parity, volatile int* cta_abort, int32_t* err_flag) {
+__device__ __noinline__ void raise_timeout(AbortBox* box) {
+    box->abort = 1;
+    atomicExch(box->launch_abort, 1);
+    if (box->err_flag) atomicOr(box->err_flag, ATTN_B200_FLAG_TIMEOUT);
+}
+__device__ __forceinline__ bool mbar_wait(void* bar, uint32_t parity, AbortBox* wc) {
     if (mbar_try(bar, parity)) return true;
     const long long t0 = clock64();
     int spins = 0;
     while (!mbar_try(bar, parity)) {
         if (((++spins) & 63) == 0) {
-            if (*cta_abort) return false;
+            if (wc->abort) return false;
             if (clock64() - t0 > WAIT_CYCLES) {
-                *cta_abort = 1;
-                atomicExch(&g_abort, 1);
-                if (err_flag) atomicOr(err_flag, ATTN_B200_FLAG_TIMEOUT);
+                raise_timeout(wc);
                 return false;
             }
         }
@@ -58,7 +68,7 @@ __device__ __forceinline__ bool mbar_wait(void* bar, uint32_t parity, volatile i
 
 // Same contract, but polls with the non-suspending test_wait: for the single MMA-issuing thread,
 // which has nothing else to do and whose reaction time is on the critical path.
-__device__ __forceinline__ bool mbar_wait_spin(void* bar, uint32_t parity, volatile int* cta_abort, int32_t* err_flag) {
+__device__ __forceinline__ bool mbar_wait_spin(void* bar, uint32_t parity, AbortBox* wc) {
     const uint32_t addr = smem_u32(bar);
     long long t0 = 0;
     for (int spins = 0;; ++spins) {
@@ -67,12 +77,10 @@ __device__ __forceinline__ bool mbar_wait_spin(void* bar, uint32_t parity, volat
                      : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
         if (ok) return true;
         if ((spins & 255) == 255) {
-            if (*cta_abort) return false;
+            if (wc->abort) return false;
             if (t0 == 0) t0 = clock64();
             else if (clock64() - t0 > WAIT_CYCLES) {
-                *cta_abort = 1;
-                atomicExch(&g_abort, 1);
-                if (err_flag) atomicOr(err_flag, ATTN_B200_FLAG_TIMEOUT);
+                raise_timeout(wc);
                 return false;
             }
         }

@@ -94,16 +94,19 @@ class KvSplitExchange:
     Set-up (collective over ``group``): a symmetric buffer ``[2, G, B, H, D+2]`` fp32 (two halves used
     on alternate steps, so a rank that is one step ahead never overwrites rows a slower peer is
     still combining) and ``G`` arrival counters per rank, mapped into every process with
-    ``torch.distributed._symmetric_memory``.  Per step: local partial rows (two kernels), one push
-    kernel (stores into every rank's slot ``[parity, my_rank]`` + one system-scope atomic per CTA on
-    that rank's counter for me), one wait kernel (bounded; raises ``FLAG_TIMEOUT`` in ``err_flag``;
-    it takes the arrivals it has waited for off the counters again, so every step has the same
-    arguments), then the usual LSE combine over the gathered rows.  No host synchronisation, no NCCL
-    call.  :meth:`capture` records the step for each of the two buffer halves as a CUDA graph and
-    :meth:`replay` launches them alternately.
+    ``torch.distributed._symmetric_memory``.
+
+    ``fused=True`` (default), three launches per step: the partial kernel; the local combine, which
+    stores each (sequence, head) row straight into every rank's slot ``[parity, my_rank]`` and bumps
+    that rank's counter for me; the final combine, whose CTAs wait for the counters themselves
+    (bounded; ``FLAG_TIMEOUT`` in ``err_flag``) and whose last CTA takes the arrivals off again.
+    ``fused=False``, five launches: partial, local combine, a push kernel, a one-warp wait kernel,
+    final combine.  Either way the counters return to where they were, so every step has the same
+    arguments: :meth:`capture` records the step for each of the two buffer halves as a CUDA graph and
+    :meth:`replay` launches them alternately.  No host synchronisation, no NCCL call.
     """
 
-    def __init__(self, batch: int, num_heads: int, head_dim: int, device, group=None):
+    def __init__(self, batch: int, num_heads: int, head_dim: int, device, group=None, fused: bool = True):
         import ctypes
         import torch.distributed._symmetric_memory as symm
         from . import _lib
@@ -133,22 +136,56 @@ class KvSplitExchange:
         self.ctas_per_push = _lib.lib.attn_b200_peer_push_ctas(self.row_bytes)
         self.step = 0
         self.err_flag = torch.zeros(1, dtype=torch.int32, device=device)
+        self.fused = fused
+        self._done = self.flags[31:]            # local scratch of the fused wait (never written by peers)
+        self._ws = None
 
     def decode(self, Q, K, V, K_cache_local, V_cache_local, local_indices, local_offsets, *, scale=None,
                k_scale=None, v_scale=None, chunk=None, _parity=None) -> torch.Tensor:
         from . import ops
         lib, check = self._lib.lib, self._lib.check
-        part = ops.paged_decode_partial(Q, K_cache_local, V_cache_local, local_indices, local_offsets, self.H,
-                                        scale=scale, chunk=chunk, k_scale=k_scale, v_scale=v_scale)
         parity = self.step & 1 if _parity is None else _parity
         if _parity is None:
             self.step += 1
         stream = torch.cuda.current_stream().cuda_stream
+        if self.fused:
+            return self._decode_fused(Q, K, V, K_cache_local, V_cache_local, local_indices, local_offsets, parity,
+                                      scale, k_scale, v_scale, chunk, stream)
+        part = ops.paged_decode_partial(Q, K_cache_local, V_cache_local, local_indices, local_offsets, self.H,
+                                        scale=scale, chunk=chunk, k_scale=k_scale, v_scale=v_scale)
         check(lib.attn_b200_peer_push(part.data_ptr(), self.row_bytes, self._dst[parity], self._flag, self.G, stream),
               "peer_push")
         check(lib.attn_b200_wait_flags_consume(self.flags.data_ptr(), self.G, self.ctas_per_push,
                                                self.err_flag.data_ptr(), stream), "wait_flags_consume")
         return ops.lse_combine(self.parts[parity], Q, K, V, num_heads=self.H, scale=scale)
+
+    def _decode_fused(self, Q, K, V, Kc, Vc, ci, off, parity, scale, k_scale, v_scale, chunk, stream):
+        import math
+        from . import ops
+        lib, check = self._lib.lib, self._lib.check
+        B, H, D = self.B, self.H, self.D
+        Hkv = Kc.size(1) // D
+        kvd = ops._kv_code(Kc, Q)
+        qd = ops._dtype_code(Q, "Q")
+        T = ci.numel()
+        if scale is None:
+            scale = 1.0 / math.sqrt(D)
+        if chunk is None:
+            chunk = ops.pick_chunk(B, Hkv, D, T, Q.device, group=H // Hkv, kv_dtype=kvd)
+        need = ops.decode_workspace_bytes(B, H, D, T, chunk)
+        if self._ws is None or self._ws.numel() < need:
+            self._ws = torch.empty(need, dtype=torch.uint8, device=Q.device)
+        check(lib.attn_b200_paged_decode_partial_push(
+            Q.data_ptr(), Kc.data_ptr(), Vc.data_ptr(), ci.data_ptr(), off.data_ptr(), self._ws.data_ptr(),
+            self._ws.numel(), B, H, Hkv, D, T, Kc.size(0), 1, 0, chunk, float(scale), ops._ptr(k_scale),
+            ops._ptr(v_scale), qd, kvd, self._dst[parity], self._flag, self.G, self.err_flag.data_ptr(), stream),
+            "paged_decode_partial_push")
+        out = torch.empty_like(Q)
+        check(lib.attn_b200_lse_combine_wait(
+            self.parts[parity].data_ptr(), self.G, Q.data_ptr(), K.data_ptr(), V.data_ptr(), out.data_ptr(), B, H,
+            K.size(1) // D, D, float(scale), qd, self.flags.data_ptr(), self._done.data_ptr(),
+            self.err_flag.data_ptr(), stream), "lse_combine_wait")
+        return out
 
     def capture(self, Q, K, V, K_cache_local, V_cache_local, local_indices, local_offsets, **kw) -> None:
         """Record the step on these (static) tensors as two CUDA graphs, one per buffer half.  The

@@ -133,13 +133,31 @@ def decode_workspace_bytes(B: int, H: int, D: int, n_tokens: int, chunk: int) ->
     return lib.attn_b200_paged_decode_workspace_bytes(B, H, D, n_tokens, chunk)
 
 
+def decode_ticket_bytes(B: int, H: int) -> int:
+    """Size of the ticket area at the end of a decode workspace (zero before the first fused call)."""
+    return lib.attn_b200_paged_decode_ticket_bytes(B, H)
+
+
+def fused_decode_supported(q_dtype, H: int, Hkv: int, D: int, block_size: int = 1) -> bool:
+    """Whether the single-launch decode (``fused=True``) exists for this case."""
+    return (q_dtype in (torch.float16, torch.bfloat16) and H == Hkv and block_size == 1 and D in (64, 128, 256))
+
+
+def new_decode_workspace(B: int, H: int, D: int, n_tokens: int, chunk: int, device) -> torch.Tensor:
+    """A workspace ready for fused and two-launch calls alike (ticket area zeroed)."""
+    need = decode_workspace_bytes(B, H, D, n_tokens, chunk)
+    ws = torch.empty(need, dtype=torch.uint8, device=device)
+    ws[need - decode_ticket_bytes(B, H):].zero_()
+    return ws
+
+
 def paged_kv_attention_forward(Q, K, V, K_cache, V_cache, cache_indices, offsets, num_heads: int, *,
                                scale: Optional[float] = None, return_sp: bool = True,
                                chunk: Optional[int] = None, k_scale=None, v_scale=None,
                                max_context_len: Optional[int] = None, workspace: Optional[torch.Tensor] = None,
                                out: Optional[torch.Tensor] = None,
                                err_flag: Optional[torch.Tensor] = None, stages: int = 3,
-                               block_size: int = 1) -> List[torch.Tensor]:
+                               block_size: int = 1, fused: bool = False) -> List[torch.Tensor]:
     """KV-paged single-query attention, block_size = 1 (paged_attention_kernel.cu:237-294).
 
     Q, K, V ``[B, H*D]`` (the current token); K_cache, V_cache ``[slots, H*D]``; cache_indices
@@ -156,6 +174,10 @@ def paged_kv_attention_forward(Q, K, V, K_cache, V_cache, cache_indices, offsets
     D`` must divide ``num_heads``); query head h reads KV head ``h // (num_heads // Hkv)``.
     ``block_size > 1``: ``cache_indices`` is a block table int32 ``[B, max_blocks]`` and token t of
     sequence b lives in pool row ``cache_indices[b, t // block_size] * block_size + t % block_size``.
+    ``fused=True`` runs the step as ONE launch (the partial kernel's last CTA per sequence and head
+    group does the combine; see :func:`fused_decode_supported` for the cases it exists for).  A caller
+    ``workspace`` must then have its last :func:`decode_ticket_bytes` bytes zeroed once before the
+    first fused call (the kernel leaves them zero); S and P are not produced.
     """
     for t, n in ((Q, "Q"), (K, "K"), (V, "V"), (K_cache, "K_cache"), (V_cache, "V_cache")):
         _check_input(t, n)
@@ -198,8 +220,17 @@ def paged_kv_attention_forward(Q, K, V, K_cache, V_cache, cache_indices, offsets
         if chunk is None:
             chunk = pick_chunk(B, Hkv, D, T, dev, group=H // Hkv, kv_dtype=kvd)
         need = decode_workspace_bytes(B, H, D, T, chunk)
+        if fused:
+            if return_sp:
+                raise RuntimeError("fused=True does not produce S and P: pass return_sp=False")
+            if not fused_decode_supported(Q.dtype, H, Hkv, D, block_size):
+                raise RuntimeError("fused=True needs multi-head attention (Hkv == num_heads), block_size 1, "
+                                   "float16/bfloat16 queries and head_dim 64, 128 or 256")
+            stages = 4
         if workspace is None:
             workspace = torch.empty(need, dtype=torch.uint8, device=dev)
+            if fused:
+                workspace[need - decode_ticket_bytes(B, H):].zero_()
         elif workspace.numel() * workspace.element_size() < need:
             raise RuntimeError(f"workspace too small: {need} bytes needed")
         O = torch.empty_like(Q) if out is None else out
@@ -224,9 +255,52 @@ def paged_kv_attention_forward(Q, K, V, K_cache, V_cache, cache_indices, offsets
     return [S, P, O]
 
 
+class _StepArena:
+    """One device buffer and one pinned host mirror holding all per-step inputs of a captured decode
+    step, so that a step needs a single host->device copy.  ``fields``: name -> (shape, dtype)."""
+
+    def __init__(self, fields, device):
+        self.names, starts, sizes = [], [0], []
+        for name, (shape, dtype) in fields.items():
+            n = math.prod(shape) * torch.empty(0, dtype=dtype).element_size()
+            self.names.append(name)
+            sizes.append(n)
+            starts.append((starts[-1] + n + 255) // 256 * 256)
+        self.starts, self.sizes = starts, sizes
+        self.dev = torch.zeros(starts[-1], dtype=torch.uint8, device=device)
+        self.host = torch.zeros(starts[-1], dtype=torch.uint8).pin_memory()
+        self.d, self.h = {}, {}
+        for i, (name, (shape, dtype)) in enumerate(fields.items()):
+            for buf, out in ((self.dev, self.d), (self.host, self.h)):
+                out[name] = buf[starts[i]:starts[i] + sizes[i]].view(dtype).view(*shape)
+
+    def start_of(self, name: str) -> int:
+        return self.starts[self.names.index(name)]
+
+    def upload(self, end: Optional[int] = None) -> None:
+        if end is None:
+            self.dev.copy_(self.host, non_blocking=True)
+        else:
+            self.dev[:end].copy_(self.host[:end], non_blocking=True)
+
+
+def _capture(device, call):
+    """Run ``call`` once on a side stream (module load, attribute set-up), then record it."""
+    with torch.cuda.device(device):
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            call()
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            call()
+    return graph
+
+
 class PagedDecodeGraph:
-    """A paged decode step captured in a CUDA graph: one graph launch per step instead of two kernel
-    launches plus the Python wrapper, which is what bounds small batches (a B=8 step is ~25 us of
+    """A paged decode step captured in a CUDA graph: one graph launch per step instead of kernel
+    launches plus the Python wrapper, which is what bounds small batches (a B=8 step is ~15 us of
     GPU work).  Not in the reference; it is how a serving loop would call this path.
 
     The kernels take sequence lengths from the device-side ``offsets`` and derive their grid from
@@ -235,65 +309,130 @@ class PagedDecodeGraph:
     into the static tensors (``q``, ``k``, ``v``, ``cache_indices``, ``offsets``) — or into their
     pinned host mirrors (``host_q`` ...) followed by :meth:`upload`, one copy for all five — call
     :meth:`replay`, read ``out``.  The KV pools are captured by address.
+
+    ``head_dim`` must be given for grouped-query pools (``K_cache.size(1) == Hkv * head_dim`` with
+    ``Hkv < num_heads``); it defaults to ``K_cache.size(1) // num_heads`` (multi-head attention).
+    Multi-head 16-bit steps are captured in the fused single-launch form unless ``fused=False``.
     """
 
     def __init__(self, K_cache, V_cache, batch: int, num_heads: int, max_tokens: int, *, dtype=None,
-                 scale: Optional[float] = None, chunk: Optional[int] = None, k_scale=None, v_scale=None):
+                 head_dim: Optional[int] = None, scale: Optional[float] = None, chunk: Optional[int] = None,
+                 k_scale=None, v_scale=None, fused: Optional[bool] = None):
         dev = K_cache.device
-        dim = K_cache.size(1)
         dtype = dtype or (K_cache.dtype if K_cache.dtype in _DT else torch.float16)
-        self.H, self.max_tokens = num_heads, max_tokens
-        # one device arena (and one pinned host mirror) for all per-step inputs, so that a step
-        # needs a single host->device copy: [q | k | v | cache_indices | offsets]
-        es = torch.empty(0, dtype=dtype).element_size()
-        sizes = [batch * dim * es] * 3 + [max_tokens * 4, batch * 4]
-        starts = [0]
-        for n in sizes:
-            starts.append((starts[-1] + n + 255) // 256 * 256)
-        self.arena = torch.zeros(starts[-1], dtype=torch.uint8, device=dev)
-        self.host_arena = torch.zeros(starts[-1], dtype=torch.uint8).pin_memory()
-
-        def views(buf):
-            qkv = [buf[starts[i]:starts[i] + sizes[i]].view(dtype).view(batch, dim) for i in range(3)]
-            ci = buf[starts[3]:starts[3] + sizes[3]].view(torch.int32)
-            off = buf[starts[4]:starts[4] + sizes[4]].view(torch.int32)
-            return (*qkv, ci, off)
-        self.q, self.k, self.v, self.cache_indices, self.offsets = views(self.arena)
-        self.host_q, self.host_k, self.host_v, self.host_cache_indices, self.host_offsets = views(self.host_arena)
-        self._ci_start = starts[3]
-        self.out = torch.zeros(batch, dim, dtype=dtype, device=dev)
-        D = dim // num_heads
-        self.chunk = chunk or pick_chunk(batch, num_heads, D, max_tokens, dev)
-        self.workspace = torch.empty(decode_workspace_bytes(batch, num_heads, D, max_tokens, self.chunk),
-                                     dtype=torch.uint8, device=dev)
-        self._kw = dict(scale=scale, return_sp=False, chunk=self.chunk, k_scale=k_scale, v_scale=v_scale,
-                        workspace=self.workspace, out=self.out)
+        H = num_heads
+        D = head_dim or K_cache.size(1) // H
+        if D <= 0 or K_cache.size(1) % D:
+            raise RuntimeError("K_cache.size(1) must be a multiple of head_dim")
+        Hkv = K_cache.size(1) // D
+        if H % Hkv:
+            raise RuntimeError("the pools' head count must divide num_heads (pass head_dim for grouped-query pools)")
+        self.H, self.Hkv, self.D, self.max_tokens = H, Hkv, D, max_tokens
+        self._arena = _StepArena({"q": ((batch, H * D), dtype), "k": ((batch, Hkv * D), dtype),
+                                  "v": ((batch, Hkv * D), dtype), "cache_indices": ((max_tokens,), torch.int32),
+                                  "offsets": ((batch,), torch.int32)}, dev)
+        d, h = self._arena.d, self._arena.h
+        self.q, self.k, self.v, self.cache_indices, self.offsets = (d[n] for n in self._arena.names)
+        self.host_q, self.host_k, self.host_v, self.host_cache_indices, self.host_offsets = (
+            h[n] for n in self._arena.names)
+        self.arena, self.host_arena = self._arena.dev, self._arena.host
+        self._ci_start = self._arena.start_of("cache_indices")
+        self.out = torch.zeros(batch, H * D, dtype=dtype, device=dev)
+        kvd = _kv_code(K_cache, self.q)
+        self.chunk = chunk or pick_chunk(batch, Hkv, D, max_tokens, dev, group=H // Hkv, kv_dtype=kvd)
+        self.fused = fused_decode_supported(dtype, H, Hkv, D) if fused is None else fused
+        self.workspace = new_decode_workspace(batch, H, D, max_tokens, self.chunk, dev)
+        kw = dict(scale=scale, return_sp=False, chunk=self.chunk, k_scale=k_scale, v_scale=v_scale,
+                  workspace=self.workspace, out=self.out, fused=self.fused)
         self._pools = (K_cache, V_cache)
-
-        def call():
-            paged_kv_attention_forward(self.q, self.k, self.v, K_cache, V_cache, self.cache_indices, self.offsets,
-                                       num_heads, **self._kw)
-
-        with torch.cuda.device(dev):
-            side = torch.cuda.Stream()
-            side.wait_stream(torch.cuda.current_stream())
-            with torch.cuda.stream(side):           # warm-up outside capture (module load, attribute set-up)
-                call()
-            torch.cuda.current_stream().wait_stream(side)
-            self.graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(self.graph):
-                call()
+        self.graph = _capture(dev, lambda: paged_kv_attention_forward(
+            self.q, self.k, self.v, K_cache, V_cache, self.cache_indices, self.offsets, H, **kw))
 
     def upload(self, n_tokens: Optional[int] = None) -> None:
         """Copy the pinned host mirror (``host_q`` ... ``host_offsets``) to the device arena in one
         transfer; with ``n_tokens`` the unused tail of the slot table is skipped (offsets, which sit
         after it, then go in a second small copy)."""
         if n_tokens is None or n_tokens >= self.max_tokens:
-            self.arena.copy_(self.host_arena, non_blocking=True)
+            self._arena.upload()
         else:
-            end = self._ci_start + 4 * n_tokens
-            self.arena[:end].copy_(self.host_arena[:end], non_blocking=True)
+            self._arena.upload(self._ci_start + 4 * n_tokens)
             self.offsets.copy_(self.host_offsets, non_blocking=True)
+
+    def replay(self) -> torch.Tensor:
+        self.graph.replay()
+        return self.out
+
+
+class DecodeStepGraph:
+    """The whole decode step of a serving loop in one CUDA graph: rotary embedding of the current
+    token's q and k, append of the rotated k and of v to the KV pools, paged attention over the
+    cached tokens plus the current one, combine.  It is the caller-side sequence around the
+    reference's operator, which receives the current token's k, v as arguments
+    (paged_attention_kernel.cu:137-146, 179-185) and leaves both the rotation and the append to its
+    caller.
+
+    Per step the caller fills the pinned host mirrors ``host["q"|"k"|"v"]`` (``[batch, H*D]`` /
+    ``[batch, Hkv*D]``, un-rotated), ``host["positions"]`` (int32 ``[batch]``), ``host["new_slots"]``
+    (int32 ``[batch]``: the pool row that receives each sequence's current token),
+    ``host["cache_indices"]`` (int32, the slots of the tokens cached BEFORE this step, concatenated)
+    and ``host["offsets"]`` (int32 ``[batch]``, inclusive cumulative counts of those), then calls
+    :meth:`upload` and :meth:`replay`.  ``out`` holds the attention output; ``q``/``k`` on the device
+    hold the rotated values.  For the next step the caller appends ``new_slots[b]`` to sequence b's
+    slots.  One captured graph serves every step whose cached tokens fit ``max_tokens``.
+    With float8 pools pass ``k_scale``/``v_scale`` (float32 ``[Hkv]``).
+    """
+
+    def __init__(self, K_cache, V_cache, cos, sin, batch: int, num_heads: int, head_dim: int, max_tokens: int, *,
+                 dtype=None, scale: Optional[float] = None, chunk: Optional[int] = None, k_scale=None, v_scale=None,
+                 fused: Optional[bool] = None):
+        dev = K_cache.device
+        dtype = dtype or (K_cache.dtype if K_cache.dtype in _DT else torch.float16)
+        H, D = num_heads, head_dim
+        if K_cache.size(1) % D:
+            raise RuntimeError("K_cache.size(1) must be a multiple of head_dim")
+        Hkv = K_cache.size(1) // D
+        if H % Hkv:
+            raise RuntimeError("the pools' head count must divide num_heads")
+        self.H, self.Hkv, self.D, self.max_tokens = H, Hkv, D, max_tokens
+        self._arena = _StepArena({"q": ((batch, H * D), dtype), "k": ((batch, Hkv * D), dtype),
+                                  "v": ((batch, Hkv * D), dtype), "positions": ((batch,), torch.int32),
+                                  "new_slots": ((batch,), torch.int32), "offsets": ((batch,), torch.int32),
+                                  "cache_indices": ((max_tokens,), torch.int32)}, dev)
+        self.dev_in, self.host = self._arena.d, self._arena.h
+        self.q, self.k = self.dev_in["q"], self.dev_in["k"]
+        self.out = torch.zeros(batch, H * D, dtype=dtype, device=dev)
+        self.err_flag = torch.zeros(1, dtype=torch.int32, device=dev)
+        kvd = _kv_code(K_cache, self.q)
+        self.chunk = chunk or pick_chunk(batch, Hkv, D, max_tokens, dev, group=H // Hkv, kv_dtype=kvd)
+        self.fused = fused_decode_supported(dtype, H, Hkv, D) if fused is None else fused
+        self.workspace = new_decode_workspace(batch, H, D, max_tokens, self.chunk, dev)
+        self._keep = (K_cache, V_cache, cos, sin, k_scale, v_scale)
+        d = self.dev_in
+
+        def step():
+            rope_and_cache_write(d["q"], d["k"], d["v"], d["positions"], cos, sin, d["new_slots"], K_cache, V_cache,
+                                 D, k_scale=k_scale, v_scale=v_scale, err_flag=self.err_flag)
+            paged_kv_attention_forward(d["q"], d["k"], d["v"], K_cache, V_cache, d["cache_indices"], d["offsets"], H,
+                                       scale=scale, return_sp=False, chunk=self.chunk, k_scale=k_scale,
+                                       v_scale=v_scale, workspace=self.workspace, out=self.out,
+                                       err_flag=self.err_flag, fused=self.fused)
+
+        # the warm-up run inside _capture executes a real step on whatever the arena holds (zeros:
+        # position 0, slot 0, no cached tokens): the caller's first upload overwrites all of it, but
+        # pool row 0 receives one bogus append, so put it back afterwards
+        row0 = (K_cache[0].clone(), V_cache[0].clone())
+        self.graph = _capture(dev, step)
+        K_cache[0].copy_(row0[0])
+        V_cache[0].copy_(row0[1])
+        self.err_flag.zero_()
+
+    def upload(self, n_tokens: Optional[int] = None) -> None:
+        """One host->device copy of all per-step inputs; ``n_tokens`` (cached tokens this step) skips the
+        unused tail of the slot table, which is the last field of the arena."""
+        if n_tokens is None or n_tokens >= self.max_tokens:
+            self._arena.upload()
+        else:
+            self._arena.upload(self._arena.start_of("cache_indices") + 4 * n_tokens)
 
     def replay(self) -> torch.Tensor:
         self.graph.replay()
@@ -302,11 +441,16 @@ class PagedDecodeGraph:
 
 class HostStagedDecoder:
     """Paged decode whose per-step inputs live in pinned HOST memory, with the uploads overlapped
-    with compute: the batch is cut into ``n_groups`` runs of sequences with about equal token
-    counts; while group g is decoded, group g+1's q/k/v rows, slot-table slice and offsets travel
-    on a copy stream, and each group's output rows go back as soon as they exist.  Only the first
-    group's upload and the last group's download are exposed.  (The slot table is the bulk of the
-    traffic: 4 bytes per context token per step.)
+    with compute.  (The slot table is the bulk of the traffic: 4 bytes per context token per step.)
+
+    Two forms of overlap.  Within a step, the batch is cut into ``n_groups`` runs of sequences with
+    about equal token counts; while group g is decoded, group g+1's q/k/v rows, slot-table slice and
+    offsets travel on a copy stream, and each group's output rows go back as soon as they exist.
+    Across steps, a decode loop knows the NEXT step's slot table while the current step runs (it is
+    this step's table plus one slot per sequence): pass it as ``next_table=(cache_indices, offsets)``
+    and it is uploaded into the second of two device buffers during this step's kernels; the next
+    call, given those same host tensors, finds its table already resident, uploads only q/k/v and
+    runs the batch as one group.
 
     ``Q, K, V`` pinned ``[B, H*D]``, ``cache_indices`` pinned int32 ``[T]``, ``offsets`` pinned int32 ``[B]``
     (inclusive cumulative lengths), ``out`` pinned ``[B, H*D]``.  The KV pools stay on the device.
@@ -321,14 +465,19 @@ class HostStagedDecoder:
         dim_kv = K_cache.size(1)
         self.dim_q = None
         self.dtype = dtype
-        self.d_ci = torch.empty(max_tokens, dtype=torch.int32, device=dev)
-        self.d_off = torch.empty(max_batch, dtype=torch.int32, device=dev)
+        # two table buffers: one in use by the running step, one receiving the next step's table
+        self.d_ci = [torch.empty(max_tokens, dtype=torch.int32, device=dev) for _ in range(2)]
+        self.d_off = [torch.empty(max_batch, dtype=torch.int32, device=dev) for _ in range(2)]
         self.h_off = torch.empty(max_batch, dtype=torch.int32).pin_memory()     # offsets rebased per group
         self.d_q = self.d_k = self.d_v = self.d_o = None
         self.max_batch, self.dim_kv = max_batch, dim_kv
+        self.cur = 0                 # table buffer of the running step
+        self._staged = None          # (cache_indices.data_ptr(), offsets.data_ptr(), T) resident in buffer 1 - cur
         with torch.cuda.device(dev):
             self.copy_stream = torch.cuda.Stream()
             self.events = [torch.cuda.Event() for _ in range(n_groups)]
+            self.table_event = torch.cuda.Event()
+            self.done_event = torch.cuda.Event()
 
     def _ensure(self, dim_q):
         if self.dim_q != dim_q:
@@ -339,43 +488,67 @@ class HostStagedDecoder:
             self.d_v = torch.empty(B, self.dim_kv, dtype=self.dtype, device=dev)
             self.d_o = torch.empty(B, dim_q, dtype=self.dtype, device=dev)
 
-    def __call__(self, Q, K, V, cache_indices, offsets, out) -> None:
+    def __call__(self, Q, K, V, cache_indices, offsets, out, next_table=None) -> None:
         """Enqueues everything; returns after the last output row has been copied (it synchronises
         the compute stream once, at the end)."""
         B = Q.size(0)
         self._ensure(Q.size(1))
-        ends = offsets[:B].tolist()
-        T = ends[-1] if B else 0
-        # group boundaries (sequence indices) at about equal token counts
-        bounds, g = [0], 1
-        for b, e in enumerate(ends):
-            if g < self.n_groups and e >= T * g / self.n_groups and b + 1 < B:
-                bounds.append(b + 1)
-                g += 1
-        bounds.append(B)
         cur = torch.cuda.current_stream(self.dev)
+        key = (cache_indices.data_ptr(), offsets.data_ptr(), cache_indices.numel())
+        resident = self._staged == key
+        if resident:
+            self.cur ^= 1
+        self._staged = None
+        d_ci, d_off = self.d_ci[self.cur], self.d_off[self.cur]
         self.copy_stream.wait_stream(cur)           # staging buffers free again
-        spans = []
-        with torch.cuda.stream(self.copy_stream):
-            for i in range(len(bounds) - 1):
-                b0, b1 = bounds[i], bounds[i + 1]
-                t0 = ends[b0 - 1] if b0 else 0
-                t1 = ends[b1 - 1]
-                self.h_off[b0:b1] = offsets[b0:b1] - t0
-                self.d_q[b0:b1].copy_(Q[b0:b1], non_blocking=True)
-                self.d_k[b0:b1].copy_(K[b0:b1], non_blocking=True)
-                self.d_v[b0:b1].copy_(V[b0:b1], non_blocking=True)
-                self.d_ci[t0:t1].copy_(cache_indices[t0:t1], non_blocking=True)
-                self.d_off[b0:b1].copy_(self.h_off[b0:b1], non_blocking=True)
-                self.events[i].record(self.copy_stream)
-                spans.append((b0, b1, t0, t1))
+        if resident:
+            T = cache_indices.numel()
+            with torch.cuda.stream(self.copy_stream):
+                self.d_q[:B].copy_(Q, non_blocking=True)
+                self.d_k[:B].copy_(K, non_blocking=True)
+                self.d_v[:B].copy_(V, non_blocking=True)
+                self.events[0].record(self.copy_stream)
+            spans = [(0, B, 0, T)]
+            cur.wait_event(self.table_event)        # the table upload of the previous call
+        else:
+            ends = offsets[:B].tolist()
+            T = ends[-1] if B else 0
+            # group boundaries (sequence indices) at about equal token counts
+            bounds, g = [0], 1
+            for b, e in enumerate(ends):
+                if g < self.n_groups and e >= T * g / self.n_groups and b + 1 < B:
+                    bounds.append(b + 1)
+                    g += 1
+            bounds.append(B)
+            spans = []
+            with torch.cuda.stream(self.copy_stream):
+                for i in range(len(bounds) - 1):
+                    b0, b1 = bounds[i], bounds[i + 1]
+                    t0 = ends[b0 - 1] if b0 else 0
+                    t1 = ends[b1 - 1]
+                    self.h_off[b0:b1] = offsets[b0:b1] - t0
+                    self.d_q[b0:b1].copy_(Q[b0:b1], non_blocking=True)
+                    self.d_k[b0:b1].copy_(K[b0:b1], non_blocking=True)
+                    self.d_v[b0:b1].copy_(V[b0:b1], non_blocking=True)
+                    d_ci[t0:t1].copy_(cache_indices[t0:t1], non_blocking=True)
+                    d_off[b0:b1].copy_(self.h_off[b0:b1], non_blocking=True)
+                    self.events[i].record(self.copy_stream)
+                    spans.append((b0, b1, t0, t1))
+        if next_table is not None:                  # travels while this step's kernels run
+            nci, noff = next_table
+            with torch.cuda.stream(self.copy_stream):
+                self.d_ci[self.cur ^ 1][:nci.numel()].copy_(nci, non_blocking=True)
+                self.d_off[self.cur ^ 1][:noff.numel()].copy_(noff, non_blocking=True)
+                self.table_event.record(self.copy_stream)
+            self._staged = (nci.data_ptr(), noff.data_ptr(), nci.numel())
         for i, (b0, b1, t0, t1) in enumerate(spans):
             cur.wait_event(self.events[i])
             paged_kv_attention_forward(self.d_q[b0:b1], self.d_k[b0:b1], self.d_v[b0:b1], self.Kc, self.Vc,
-                                       self.d_ci[t0:t1], self.d_off[b0:b1], self.H, return_sp=False,
+                                       d_ci[t0:t1], d_off[b0:b1], self.H, return_sp=False,
                                        out=self.d_o[b0:b1], **self.kw)
             out[b0:b1].copy_(self.d_o[b0:b1], non_blocking=True)
-        cur.synchronize()
+        self.done_event.record(cur)
+        self.done_event.synchronize()
 
 
 def paged_decode_partial(Q, K_cache, V_cache, cache_indices, offsets, num_heads: int, *,
@@ -505,7 +678,8 @@ def paged_attention_forward(Q, K, V, offsets, num_heads: int, *, scale: Optional
             max_seqlen = int(lens.max().item()) if B > 0 else 0
         out_f32 = out_dtype == torch.float32 and Q.dtype != torch.float32
         # the reference zero-fills O (zeros_like, :209).  The tensor-core path writes every row itself
-        # (rows past offsets[-1] are zeroed by a small kernel), so it skips the up-front memset
+        # (rows no query tile covers - past offsets[-1], or beyond an understated max_seqlen - are
+        # zeroed by a small kernel of the same launch), so it skips the up-front memset
         tc_path = (not return_sp and not force_generic and D == 128 and Q.dtype in (torch.float16, torch.bfloat16))
         O = (torch.empty if tc_path else torch.zeros)(Q.shape, dtype=torch.float32 if out_f32 else Q.dtype,
                                                       device=dev)

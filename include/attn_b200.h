@@ -10,7 +10,12 @@
  *  - `stream` is a cudaStream_t passed as void*; all work is enqueued on it, no call synchronises.
  *  - Return value: 0 = ok; negative = argument error (ATTN_B200_E*); positive = cudaError_t of
  *    a failed launch.  attn_b200_strerror() renders either.
- *  - The library owns no memory: outputs and scratch are allocated by the caller.
+ *  - Outputs and scratch are allocated by the caller; no entry point allocates or frees device memory.
+ *    The library's device image holds three small fixed arrays of its own (every device that loads
+ *    it carries them until the process exits): 64 launch-state slots of 16 bytes for the tensor-core
+ *    prefill kernels (work counter + abort word, taken in rotation, so at most 64 such launches may
+ *    be in flight at once), and the ATTN_B200_STATIC_SCRATCH_BYTES array that only
+ *    attn_b200_paged_decode_static_scratch uses.
  *  - `err_flag` (optional, may be NULL): device int32 that kernels OR a bit into when they meet an
  *    out-of-range slot / position; the offending row is skipped, never dereferenced.
  */
@@ -109,10 +114,18 @@ ATTN_B200_API int attn_b200_rope_write_kv(void* q, void* k, const void* v, const
  * global grid; each (chunk, head) is reduced by one warp into an (m, l, o) partial in
  * `workspace`, then attn_b200_lse_combine-style reduction folds the partials and the new token.
  * `chunk` must be a multiple of 32 in [32, 2048]; use attn_b200_paged_decode_pick_chunk.
- * `workspace` needs attn_b200_paged_decode_workspace_bytes(...) bytes, 16-byte aligned; it needs
- * no initialisation and holds nothing between calls.
+ * `workspace` needs attn_b200_paged_decode_workspace_bytes(...) bytes, 16-byte aligned.  Its last
+ * attn_b200_paged_decode_ticket_bytes(B, H) bytes are the ticket counters of the fused form
+ * (`stages` = 4), the only part that carries a requirement: zero before the first fused call; every
+ * fused call leaves them zero again.  The rest needs no initialisation and holds nothing between calls.
  * `stages`: 3 runs both kernels (the normal call); 1 runs only the partial kernel, 2 only the
- * combine kernel (same arguments) so that a profiler or benchmark can put events between them.
+ * combine kernel (same arguments) so that a profiler or benchmark can put events between them;
+ * 4 is the fused single launch: each CTA of the partial kernel publishes its rows and takes a
+ * ticket, and the CTA that draws a (sequence, head group)'s last ticket folds that group's rows
+ * and the new token and writes `out` (nobody waits for anybody).  It exists for multi-head
+ * attention (n_kv_heads == H) with a per-token table (block_size == 1), 16-bit q, head_dim 64 /
+ * 128 / 256 and S == NULL; anything else returns ATTN_B200_ESHAPE.  It pays when the step is a
+ * few microseconds long (small batches), where the second launch is a third of the step.
  * Extensions beyond the reference (which is multi-head, block_size = 1):
  *   n_kv_heads  KV heads (H % n_kv_heads == 0); k_new, v_new, k_cache, v_cache then have n_kv_heads*D
  *               columns and query head h reads KV head h / (H / n_kv_heads).  Pass H for MHA.
@@ -129,6 +142,8 @@ ATTN_B200_API int attn_b200_paged_decode(const void* q, const void* k_new, const
                            int32_t* err_flag, void* stream);
 
 ATTN_B200_API size_t attn_b200_paged_decode_workspace_bytes(int B, int H, int D, int64_t n_tokens, int chunk);
+/* Size of the ticket area at the END of the workspace (see `stages` = 4). */
+ATTN_B200_API size_t attn_b200_paged_decode_ticket_bytes(int B, int H);
 /* Heuristic chunk length: enough (chunk, head-group) work items to fill `sm_count` SMs. */
 ATTN_B200_API int attn_b200_paged_decode_pick_chunk(int B, int H, int D, int64_t n_tokens, int sm_count);
 /* The same for grouped-query heads: `group` query heads per KV head, `kv_dtype` of the pools.  Groups
@@ -177,17 +192,45 @@ ATTN_B200_API int attn_b200_wait_flags(const int32_t* flags, int n_flags, int32_
 ATTN_B200_API int attn_b200_wait_flags_consume(int32_t* flags, int n_flags, int32_t count, int32_t* err_flag,
                                                void* stream);
 
+/* The KV-split exchange in three launches instead of five (no counterpart in the reference).
+ * attn_b200_paged_decode_partial_push = attn_b200_paged_decode_partial whose second stage stores
+ * each (b, h) row [o[D], m, l] straight into peer_dst[g] ([B, H, D+2] float, this rank's slot of
+ * peer g's gather buffer, g < n_peers <= 16; host arrays of device pointers valid in this process)
+ * with plain stores and then adds 1 per (b, h) to *peer_flag[g] (system-scope): a step adds B*H to
+ * each counter.  attn_b200_lse_combine_wait = attn_b200_lse_combine whose CTAs first wait, each by
+ * itself and bounded (about a second, then ATTN_B200_FLAG_TIMEOUT in *err_flag and the kernel goes
+ * on and ends), until flags[i] >= B*H for every i < n_parts; the last CTA past the wait takes B*H
+ * off every counter again (arrivals of a peer already one step ahead stay) using *done_counter
+ * (an int32 of the caller's, zero before the first call, left zero), so every step has the same
+ * arguments and can be replayed from a CUDA graph.  16-bit q only. */
+ATTN_B200_API int attn_b200_paged_decode_partial_push(
+    const void* q, const void* k_cache, const void* v_cache, const int32_t* slots, const int32_t* offsets,
+    void* workspace, size_t workspace_bytes, int B, int H, int n_kv_heads, int D, int64_t n_tokens, int64_t n_slots,
+    int block_size, int max_blocks, int chunk, float scale, const float* k_scale, const float* v_scale, int q_dtype,
+    int kv_dtype, float* const* peer_dst, int32_t* const* peer_flag, int n_peers, int32_t* err_flag, void* stream);
+ATTN_B200_API int attn_b200_lse_combine_wait(const float* parts, int n_parts, const void* q, const void* k_new,
+                                             const void* v_new, void* out, int B, int H, int n_kv_heads, int D,
+                                             float scale, int q_dtype, int32_t* flags, int32_t* done_counter,
+                                             int32_t* err_flag, void* stream);
+
 /* Paged decode that allocates nothing and needs no scratch from the caller.
  * (No counterpart in the reference: its launcher allocates S, P and O itself with torch::zeros.)
  * For hosts that cannot call cudaMalloc — an engine that gave all free HBM to its own KV pool, or
  * a decode loop that cannot take the device-wide synchronisation an allocation implies.  Same
- * arguments and result as attn_b200_paged_decode without workspace/S/P/uniform_ctx/stages; the
- * split-KV partial rows go to a fixed ATTN_B200_STATIC_SCRATCH_BYTES array inside the library's
- * device image (every device that loads the library holds it until the process exits).
+ * arguments and result as attn_b200_paged_decode without workspace/S/P/uniform_ctx/stages and for
+ * multi-head attention with a per-token slot table only (it passes n_kv_heads = H, block_size = 1:
+ * no grouped-query pools, no block tables); the split-KV partial rows go to a fixed
+ * ATTN_B200_STATIC_SCRATCH_BYTES array inside the library's device image (every device that loads
+ * the library holds it until the process exits).
  *  - Returns ATTN_B200_ETOOLARGE when attn_b200_paged_decode_workspace_bytes(B, H, D, n_tokens,
  *    chunk) exceeds ATTN_B200_STATIC_SCRATCH_BYTES; a larger `chunk` (up to 2048) lowers the need.
  *  - The first call on each device looks the array's device address up (cudaGetSymbolAddress, with
- *    that device current) and keeps it; make that first call outside any stream capture.
+ *    that device current) and keeps it; make that first call outside any stream capture.  With
+ *    CUDA's lazy module loading that look-up is also the moment the 16 MiB array is materialised on
+ *    the device: a host that is about to hand all free HBM to its own pool must make this first
+ *    call BEFORE it does so, or the look-up fails for lack of memory.
+ *  - The address is kept per CURRENT device: the device that is current at the call must be the one
+ *    that owns `stream` and the pointers.
  *  - All calls on a device share the one array.  Nothing in it has to be cleared between calls (a
  *    call only reads rows it wrote itself), but two calls that overlap on the GPU — different
  *    streams, no ordering between them — race on it: serialise them.

@@ -13,6 +13,11 @@ for p in (ROOT, os.path.join(ROOT, "attention_impl_b200", "dropin")):
         sys.path.insert(0, p)
 
 
+# the reference's own test files (fetched, not committed) are run by test_reference_suite_gpu.py in a
+# child process, never collected into this suite
+collect_ignore_glob = ["reference_suite/*"]
+
+
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run on the B200 box)")
 

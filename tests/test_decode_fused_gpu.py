@@ -1,0 +1,263 @@
+"""GPU: the single-launch (fused combine) decode, the software-pipelined multi-head kernel behind
+short units, the captured decode steps, and the host-staged decoder with a prefetched slot table.
+
+Every case goes through the drop-in modules / the C ABI and is compared with the CPU oracle
+(fp16: <= 2e-3 max-abs against the fp32-evaluated oracle; bf16: its output rounding added; e4m3
+KV: <= 2e-2 relative against the oracle on dequantised KV).
+"""
+import pytest
+import torch
+
+from oracle import attention_oracle as orc
+from helpers import decode_inputs, uniform_lens
+
+pytestmark = pytest.mark.gpu
+
+TOL16 = 2e-3
+
+
+def _fused(inp, H, chunk, **kw):
+    import attention_impl_b200 as A
+    Q, K, V, Kc, Vc, ci, off = [t.cuda() for t in inp]
+    _, _, O = A.paged_kv_attention_forward(Q, K, V, Kc, Vc, ci, off, H, return_sp=False, chunk=chunk, fused=True, **kw)
+    torch.cuda.synchronize()
+    return O.cpu()
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("H,D", [(32, 128), (3, 128), (24, 128), (8, 64), (5, 64), (4, 256), (1, 256)])
+@pytest.mark.parametrize("chunk", [32, 64, 256])
+def test_fused_decode_ragged(dtype, H, D, chunk):
+    """Ragged lengths incl. empty sequences (first, middle, last, adjacent), chunk-boundary lengths,
+    head counts that leave warps of the last head group without heads; chunks on both sides of the
+    pipelined / plain kernel split."""
+    lens = [0, 1, 31, 32, 33, 64, 0, 0, 100, 257, 5, 96, 0]
+    inp = decode_inputs(len(lens), H, D, lens, 1024, dtype, seed=H * 100 + D + chunk)
+    O = _fused(inp, H, chunk)
+    _, _, O32 = orc.paged_decode(*inp, H, compute_dtype=torch.float32)
+    tol = TOL16 if dtype == torch.float16 else 1.6e-2
+    assert torch.isfinite(O).all()
+    assert (O.float() - O32.float()).abs().max() <= tol
+
+
+def test_fused_decode_small_batch_workload_matches_two_launch_form():
+    """B=8, H=32, D=128, ctx ~ U[128,1024]: fused against the oracle and against the two-kernel form."""
+    import attention_impl_b200 as A
+    B, H, D = 8, 32, 128
+    lens = uniform_lens(B, 128, 1024, seed=1)
+    inp = decode_inputs(B, H, D, lens, 16384, torch.float16, seed=1001)
+    O = _fused(inp, H, None)
+    _, _, O32 = orc.paged_decode(*inp, H, compute_dtype=torch.float32)
+    assert (O.float() - O32.float()).abs().max() <= TOL16
+    _, _, O2 = A.paged_kv_attention_forward(*[t.cuda() for t in inp], H, return_sp=False)
+    assert (O.float() - O2.cpu().float()).abs().max() <= 5e-4     # same partial rows, other summation order
+
+
+def test_fused_decode_leaves_its_tickets_clean():
+    """One workspace, three fused calls with different batches: the ticket area must be zero after
+    every call (each call's last CTAs reset what they counted)."""
+    import attention_impl_b200 as A
+    B, H, D, cap = 6, 16, 128, 4096
+    chunk = 32
+    ws = A.ops.new_decode_workspace(B, H, D, cap, chunk, "cuda")
+    tail = A.ops.decode_ticket_bytes(B, H)
+    for seed in (3, 4, 5):
+        lens = uniform_lens(B, 0, 600, seed=seed)
+        Q, K, V, Kc, Vc, ci, off = decode_inputs(B, H, D, lens, 8192, torch.float16, seed=seed)
+        ci_cap = torch.zeros(cap, dtype=torch.int32)
+        ci_cap[: ci.numel()] = ci
+        _, _, O = A.paged_kv_attention_forward(Q.cuda(), K.cuda(), V.cuda(), Kc.cuda(), Vc.cuda(), ci_cap.cuda(),
+                                               off.cuda(), H, return_sp=False, chunk=chunk, workspace=ws, fused=True)
+        torch.cuda.synchronize()
+        assert int(ws[-tail:].view(torch.int32).abs().sum().item()) == 0
+        _, _, O32 = orc.paged_decode(Q, K, V, Kc, Vc, ci, off, H, compute_dtype=torch.float32)
+        assert (O.cpu().float() - O32.float()).abs().max() <= TOL16
+
+
+def test_fused_decode_fp8_kv():
+    B, H, D = 6, 8, 128
+    lens = uniform_lens(B, 0, 2000, seed=11)
+    Q, K, V, Kc, Vc, ci, off = decode_inputs(B, H, D, lens, 16384, torch.float16, seed=12)
+    K8, ks = orc.quantize_e4m3_per_head(Kc, H)
+    V8, vs = orc.quantize_e4m3_per_head(Vc, H)
+    Kd, Vd = orc.dequantize_e4m3_per_head(K8, ks, H), orc.dequantize_e4m3_per_head(V8, vs, H)
+    _, _, Oref = orc.paged_decode(Q.float(), K.float(), V.float(), Kd, Vd, ci, off, H)
+    for chunk in (32, 512):
+        O = _fused((Q, K, V, K8, V8, ci, off), H, chunk, k_scale=ks.cuda(), v_scale=vs.cuda())
+        assert (O.float() - Oref).norm() / Oref.norm() <= 2e-2
+        assert (O.float() - Oref).abs().max() <= 2e-2 * Oref.abs().max()
+
+
+def test_fused_decode_rejects_what_it_does_not_cover():
+    import attention_impl_b200 as A
+    lens = [5, 9]
+    Q, K, V, Kc, Vc, ci, off = [t.cuda() for t in decode_inputs(2, 8, 128, lens, 64, torch.float16, seed=1)]
+    with pytest.raises(RuntimeError, match="fused=True"):
+        A.paged_kv_attention_forward(Q, K, V, Kc, Vc, ci, off, 8, fused=True)                    # S and P requested
+    with pytest.raises(RuntimeError, match="fused=True"):
+        A.paged_kv_attention_forward(Q.float(), K.float(), V.float(), Kc.float(), Vc.float(), ci, off, 8,
+                                     return_sp=False, fused=True)                               # fp32
+    # straight through the C ABI: grouped-query pools with stages = 4
+    from attention_impl_b200 import _lib
+    ws = A.ops.new_decode_workspace(2, 8, 128, 14, 32, "cuda")
+    rc = _lib.lib.attn_b200_paged_decode(Q.data_ptr(), K.data_ptr(), V.data_ptr(), Kc.data_ptr(), Vc.data_ptr(),
+                                         ci.data_ptr(), off.data_ptr(), Q.data_ptr(), ws.data_ptr(), ws.numel(), None,
+                                         None, 0, 2, 8, 4, 128, 14, 64, 0, 1, 0, 32, 1.0, None, None, _lib.F16, _lib.F16,
+                                         4, None, None)
+    assert rc == -3
+
+
+@pytest.mark.parametrize("chunk", [32, 64, 128])
+def test_pipelined_kernel_with_scores_and_probabilities(chunk):
+    """The two-launch form with S and P requested also runs the pipelined kernel on short units."""
+    import lm_ops
+    lens = [0, 3, 4, 5, 36, 131, 260]
+    B, H, D = len(lens), 8, 128
+    inp = decode_inputs(B, H, D, lens, 1024, torch.float16, seed=chunk)
+    S, P, O = lm_ops.paged_kv_attention_forward(*[t.cuda() for t in inp], H, chunk=chunk)
+    S32, P32, O32 = orc.paged_decode(*inp, H, compute_dtype=torch.float32)
+    assert (O.cpu().float() - O32.float()).abs().max() <= TOL16
+    assert (S.cpu() - S32).abs().max() < 3e-3
+    assert (P.cpu() - P32).abs().max() < 2e-4
+
+
+def test_decode_graph_grouped_query_pools():
+    """A captured step over pools with fewer KV heads than query heads (head_dim given explicitly)."""
+    import attention_impl_b200 as A
+    B, H, Hkv, D, cap = 4, 16, 4, 128, 4096
+    g = torch.Generator().manual_seed(5)
+    Kc, Vc = (torch.randn(8192, Hkv * D, generator=g).half().cuda() for _ in range(2))
+    graph = A.PagedDecodeGraph(Kc, Vc, B, H, cap, head_dim=D)
+    assert graph.q.shape == (B, H * D) and graph.k.shape == (B, Hkv * D) and not graph.fused
+    for seed in (1, 2):
+        lens = uniform_lens(B, 1, 900, seed=seed)
+        gg = torch.Generator().manual_seed(seed)
+        Q = torch.randn(B, H * D, generator=gg).half()
+        K, V = (torch.randn(B, Hkv * D, generator=gg).half() for _ in range(2))
+        ci = torch.randperm(8192, generator=gg)[: sum(lens)].int()
+        off = torch.tensor(lens).cumsum(0).int()
+        graph.host_q.copy_(Q); graph.host_k.copy_(K); graph.host_v.copy_(V)
+        graph.host_cache_indices[: ci.numel()].copy_(ci); graph.host_offsets.copy_(off)
+        graph.upload(ci.numel())
+        O = graph.replay().clone()
+        _, _, O32 = orc.paged_decode(Q, K, V, Kc.cpu(), Vc.cpu(), ci, off, H, compute_dtype=torch.float32)
+        assert (O.cpu().float() - O32.float()).abs().max() <= TOL16
+    with pytest.raises(RuntimeError, match="head count"):
+        A.PagedDecodeGraph(Kc, Vc, B, 6, cap, head_dim=D)
+
+
+@pytest.mark.parametrize("fp8", [False, True])
+def test_decode_step_graph_three_growing_steps(fp8):
+    """RoPE -> cache append -> attention -> combine replayed from one graph for three consecutive
+    steps of growing sequences; every step's output and the pool rows it wrote are compared with
+    the oracle (rope + scatter + paged_decode)."""
+    import attention_impl_b200 as A
+    B, H, D, n_slots, max_pos = 5, 8, 128, 4096, 2048
+    g = torch.Generator().manual_seed(77)
+    lens = [0, 1, 70, 300, 33]
+    Kc, Vc = (torch.randn(n_slots, H * D, generator=g).half() for _ in range(2))
+    cos, sin = orc.rope_tables(D, max_pos)
+    perm = torch.randperm(n_slots - 1, generator=g) + 1           # slot 0 stays out of use
+    seq_slots, nxt = [], 0
+    for n in lens:
+        seq_slots.append(perm[nxt:nxt + n].tolist())
+        nxt += n
+    if fp8:
+        K8, ks = orc.quantize_e4m3_per_head(Kc, H)
+        V8, vs = orc.quantize_e4m3_per_head(Vc, H)
+        Kd, Vd = K8.cuda(), V8.cuda()
+        Kref, Vref = orc.dequantize_e4m3_per_head(K8, ks, H), orc.dequantize_e4m3_per_head(V8, vs, H)
+        kw = dict(k_scale=ks.cuda(), v_scale=vs.cuda(), dtype=torch.float16)
+    else:
+        Kd, Vd = Kc.cuda(), Vc.cuda()
+        Kref, Vref = Kc.clone().float(), Vc.clone().float()
+        kw = {}
+    row0 = (Kd[0].clone(), Vd[0].clone())
+    step = A.DecodeStepGraph(Kd, Vd, cos.cuda(), sin.cuda(), B, H, D, max_tokens=1024, **kw)
+    assert torch.equal(Kd[0].view(torch.uint8), row0[0].view(torch.uint8))      # the capture's warm-up left no trace
+    assert torch.equal(Vd[0].view(torch.uint8), row0[1].view(torch.uint8))
+    for s in range(3):
+        q, k, v = (torch.randn(B, H * D, generator=g).half() for _ in range(3))
+        pos = torch.tensor([len(x) for x in seq_slots], dtype=torch.int32)
+        new = perm[nxt:nxt + B].int()
+        nxt += B
+        ci = torch.tensor([x for sl in seq_slots for x in sl], dtype=torch.int32)
+        off = torch.tensor([len(x) for x in seq_slots]).cumsum(0).int()
+        h = step.host
+        h["q"].copy_(q); h["k"].copy_(k); h["v"].copy_(v); h["positions"].copy_(pos); h["new_slots"].copy_(new)
+        h["cache_indices"][: ci.numel()].copy_(ci); h["offsets"].copy_(off)
+        step.upload(ci.numel())
+        O = step.replay().clone()
+        torch.cuda.synchronize()
+        assert int(step.err_flag.item()) == 0
+        # oracle: rotate, attend over the cache as it was BEFORE the append, then append
+        q_r, k_r = orc.rope(q, k, pos, cos, sin, D)
+        _, _, O_ref = orc.paged_decode(q_r.float(), k_r.float(), v.float(), Kref, Vref, ci, off, H)
+        if fp8:
+            assert (O.cpu().float() - O_ref).norm() / O_ref.norm() <= 2e-2
+            Kq = (k_r.float().reshape(B, H, D) / ks.view(1, H, 1)).to(torch.float8_e4m3fn).reshape(B, H * D)
+            Vq = (v.float().reshape(B, H, D) / vs.view(1, H, 1)).to(torch.float8_e4m3fn).reshape(B, H * D)
+            Kgot, Vgot = Kd[new.long().cuda()].cpu(), Vd[new.long().cuda()].cpu()
+            # same codes, except where x / scale and x * (1 / scale) fall on either side of a rounding boundary
+            for got, exp in ((Kgot, Kq), (Vgot, Vq)):
+                dcode = (got.view(torch.uint8).int() - exp.view(torch.uint8).int()).abs()
+                assert dcode.max() <= 1 and (dcode > 0).float().mean() < 0.01
+            Kref[new.long()] = orc.dequantize_e4m3_per_head(Kgot, ks, H)
+            Vref[new.long()] = orc.dequantize_e4m3_per_head(Vgot, vs, H)
+        else:
+            assert (O.cpu().float() - O_ref).abs().max() <= TOL16
+            assert torch.equal(step.q.cpu(), q_r) and torch.equal(step.k.cpu(), k_r)
+            assert torch.equal(Kd[new.long().cuda()].cpu(), k_r) and torch.equal(Vd[new.long().cuda()].cpu(), v)
+            Kref[new.long()] = k_r.float()
+            Vref[new.long()] = v.float()
+        for b in range(B):
+            seq_slots[b].append(int(new[b]))
+
+
+def test_host_staged_decoder_with_prefetched_table():
+    """The next step's slot table travels during the current step; three steps of growing sequences."""
+    import attention_impl_b200 as A
+    B, H, D = 7, 8, 128
+    g = torch.Generator().manual_seed(9)
+    Kc, Vc = (torch.randn(8192, H * D, generator=g).half() for _ in range(2))
+    Kd, Vd = Kc.cuda(), Vc.cuda()
+    lens0 = uniform_lens(B, 1, 500, seed=3)
+    perm = torch.randperm(8192, generator=g)
+    tables = []
+    for s in range(3):
+        lens = [n + s for n in lens0]
+        ci = perm[1000 * s: 1000 * s + sum(lens)].int().pin_memory()      # a different table every step
+        off = torch.tensor(lens).cumsum(0).int().pin_memory()
+        tables.append((ci, off))
+    dec = A.HostStagedDecoder(Kd, Vd, H, B, max(t[0].numel() for t in tables), n_groups=2)
+    out = torch.empty(B, H * D, dtype=torch.float16).pin_memory()
+    for s, (ci, off) in enumerate(tables):
+        Q, K, V = (torch.randn(B, H * D, generator=g).half().pin_memory() for _ in range(3))
+        dec(Q, K, V, ci, off, out, next_table=tables[s + 1] if s + 1 < len(tables) else None)
+        _, _, O32 = orc.paged_decode(Q, K, V, Kc, Vc, ci, off, H, compute_dtype=torch.float32)
+        assert (out.float() - O32.float()).abs().max() <= TOL16, f"step {s}"
+
+
+@pytest.mark.parametrize("Hq,Hkv", [(8, 8), (16, 4)])
+def test_fp8_decode_long_context_absmax_scales(Hq, Hkv):
+    """One 40 000-token sequence, K/V ~ N(0,1) quantised to e4m3 with per-head absmax scales (codes
+    up to +-448), multi-head kernel and the grouped-query tensor-core kernel: <= 2e-2 relative and
+    <= 2e-2 of max |O| against the oracle on dequantised KV."""
+    import lm_ops
+    D, n = 128, 40_000
+    g = torch.Generator().manual_seed(Hq)
+    Q = torch.randn(1, Hq * D, generator=g).half()
+    K, V = (torch.randn(1, Hkv * D, generator=g).half() for _ in range(2))
+    Kc, Vc = (torch.randn(n + 100, Hkv * D, generator=g) for _ in range(2))
+    K8, ks = orc.quantize_e4m3_per_head(Kc, Hkv)
+    V8, vs = orc.quantize_e4m3_per_head(Vc, Hkv)
+    assert int(K8.view(torch.uint8).max()) >= 0x7E - 0 and float(K8.float().abs().max()) == 448.0
+    ci = torch.randperm(n + 100, generator=g)[:n].int()
+    off = torch.tensor([n]).int()
+    Kd, Vd = orc.dequantize_e4m3_per_head(K8, ks, Hkv), orc.dequantize_e4m3_per_head(V8, vs, Hkv)
+    _, _, Oref = orc.paged_decode(Q.float(), K.float(), V.float(), Kd, Vd, ci, off, Hq)
+    _, _, O = lm_ops.paged_kv_attention_forward(Q.cuda(), K.cuda(), V.cuda(), K8.cuda(), V8.cuda(), ci.cuda(),
+                                                off.cuda(), Hq, return_sp=False, k_scale=ks.cuda(), v_scale=vs.cuda())
+    err = O.cpu().float() - Oref
+    assert err.norm() / Oref.norm() <= 2e-2
+    assert err.abs().max() <= 2e-2 * Oref.abs().max()

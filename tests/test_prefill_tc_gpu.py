@@ -1,10 +1,10 @@
 """GPU: tensor-core (tcgen05) packed causal prefill vs the CPU oracle.
 
-Tolerances.  The kernel rounds P to the input type before P·V (as every flash-style kernel does):
-for fp16 that is 2^-12 relative per probability and the fp32-output result stays within 2e-3
-max-abs of the fp32-evaluated oracle; for bf16 P carries 2^-9, so short rows (a few keys with
-large probabilities) reach ~4e-3·|v|max and the bound used is 1e-2 for fp32 output and 2 bf16 ulp
-(1.6e-2 at |O| < 2) for bf16 output.
+Tolerances.  With fp32 output the kernel is within 2e-3 max-abs of the fp32-evaluated oracle for
+fp16 AND bf16 inputs.  P is rounded to the input type before P·V (2^-12 per probability for fp16,
+2^-9 for bf16); over many keys that averages out, and the first 256 rows of every sequence, which
+see few keys, carry P as two terms (hi + lo).  A bf16 OUTPUT adds its own rounding (half an ulp is
+3.9e-3 at |O| >= 1), so bf16-out is held to 2 bf16 ulp (1.6e-2 at |O| < 2).
 """
 import pytest
 import torch
@@ -32,10 +32,10 @@ def test_prefill_tc_fp32_out_vs_fp32_oracle(dtype, lens):
     O = _run(Q, K, V, off, H, out_dtype=torch.float32)
     assert O.dtype == torch.float32
     O32 = orc.packed_prefill(Q, K, V, off, H, compute_dtype=torch.float32, out_dtype=torch.float32)
-    tol = 2e-3 if dtype == torch.float16 else 1e-2
+    tol = 2e-3
     assert (O - O32).abs().max() <= tol
     # typical error is far below the bound
-    assert (O - O32).abs().mean() <= tol / 20
+    assert (O - O32).abs().mean() <= tol / 10
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
@@ -60,7 +60,46 @@ def test_prefill_tc_many_heads_and_sequences():
     Q, K, V, off = prefill_inputs(lens, H, 128, torch.bfloat16, seed=11)
     O = _run(Q, K, V, off, H, out_dtype=torch.float32)
     O32 = orc.packed_prefill(Q, K, V, off, H, compute_dtype=torch.float32, out_dtype=torch.float32)
-    assert (O - O32).abs().max() <= 1e-2
+    assert (O - O32).abs().max() <= 2e-3
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_prefill_tc_workload_sized_sequences_vs_oracle(dtype):
+    """Two whole sequences at the top of the workload's length range (3500 and 4096 tokens), fp32
+    output against the fp32-evaluated oracle: the stated 2e-3, with the distribution beside it."""
+    lens = [3500, 4096]
+    H = 4
+    Q, K, V, off = prefill_inputs(lens, H, 128, dtype, seed=31)
+    O = _run(Q, K, V, off, H, out_dtype=torch.float32)
+    O32 = orc.packed_prefill(Q, K, V, off, H, compute_dtype=torch.float32, out_dtype=torch.float32)
+    err = (O - O32).abs()
+    assert err.max() <= 2e-3
+    assert torch.quantile(err.flatten()[:: 7], 0.999) <= 5e-4 and err.mean() <= 1e-4
+
+
+def test_prefill_tc_understated_max_seqlen_is_flagged_and_rows_are_zero():
+    """max_seqlen below the longest sequence: the rows that no query tile covers come back as zeros
+    (never uninitialised memory) and the kernel raises the bad-offsets flag; covered rows are right."""
+    import lm_ops
+    lens = [700, 100]
+    H = 2
+    Q, K, V, off = prefill_inputs(lens, H, 128, torch.float16, seed=3)
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    O = lm_ops.packed_attention(Q.cuda(), K.cuda(), V.cuda(), off.cuda(), H, return_sp=False, max_seqlen=300,
+                                out_dtype=torch.float32, err_flag=flag)[2].cpu()
+    assert int(flag.item()) == 4
+    O32 = orc.packed_prefill(Q, K, V, off, H, compute_dtype=torch.float32, out_dtype=torch.float32)
+    assert O[512:700].abs().sum().item() == 0                 # 300 rounds up to 512 covered rows
+    assert (O[:512] - O32[:512]).abs().max() <= 2e-3 and (O[700:] - O32[700:]).abs().max() <= 2e-3
+
+
+def test_prefill_all_sequences_empty_gives_zeros():
+    import lm_ops
+    Q = torch.randn(50, 256, dtype=torch.float16, device="cuda")
+    off = torch.zeros(3, dtype=torch.int32, device="cuda")
+    for kw in ({}, {"force_generic": True}):
+        O = lm_ops.packed_attention(Q, Q.clone(), Q.clone(), off, 2, return_sp=False, **kw)[2]
+        assert O.shape == Q.shape and O.abs().sum().item() == 0
 
 
 def test_prefill_tc_rows_sum_property_at_workload_lengths():

@@ -37,26 +37,4 @@ def test_fewer_items_than_sms_and_exact_tile_multiples():
     Q, K, V, off = prefill_inputs(lens, H, 128, torch.bfloat16, seed=17)
     O = _run(Q, K, V, off, H, out_dtype=torch.float32)
     O32 = orc.packed_prefill(Q, K, V, off, H, compute_dtype=torch.float32, out_dtype=torch.float32)
-    assert (O - O32).abs().max() <= 1e-2
-
-
-def test_pair_kernel_matches_persistent_kernel_bitwise():
-    """The two kernels run the same arithmetic in the same order per row: identical bits.  The kernel is
-    chosen once per process (environment variable), so the pair kernel runs in a child process."""
-    import os, subprocess, sys, tempfile
-    lens = [700, 33, 1500, 256, 90]
-    H = 4
-    Q, K, V, off = prefill_inputs(lens, H, 128, torch.bfloat16, seed=23)
-    O = _run(Q, K, V, off, H)
-    with tempfile.TemporaryDirectory() as d:
-        torch.save((Q, K, V, off), os.path.join(d, "in.pt"))
-        code = (
-            "import sys, torch; sys.path[:0] = %r\n"
-            "import lm_ops\n"
-            "Q, K, V, off = torch.load(%r)\n"
-            "O = lm_ops.packed_attention(Q.cuda(), K.cuda(), V.cuda(), off.cuda(), %d, return_sp=False)[2]\n"
-            "torch.save(O.cpu(), %r)\n" % (sys.path, os.path.join(d, "in.pt"), H, os.path.join(d, "out.pt")))
-        env = dict(os.environ, ATTN_B200_PREFILL_VERSION="2")
-        subprocess.run([sys.executable, "-c", code], check=True, env=env, timeout=300)
-        O2 = torch.load(os.path.join(d, "out.pt"))
-    assert torch.equal(O, O2)
+    assert (O - O32).abs().max() <= 2e-3

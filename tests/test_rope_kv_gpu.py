@@ -84,3 +84,26 @@ def test_rope_write_kv_bad_slot_flagged():
     A.rope_and_cache_write(q.cuda(), k.cuda(), v.cuda(), pos.cuda(), cos.cuda(), sin.cuda(), sl.cuda(), Kc, Vc, 64,
                            err_flag=flag)
     assert int(flag.item()) & 1
+
+
+def test_rope_write_kv_bad_position_leaves_token_and_slot_untouched():
+    """A position outside the table: the token's q and k stay un-rotated and NOTHING of it reaches
+    the pools (no new v beside a stale k); the other tokens are processed as usual."""
+    import attention_impl_b200 as A
+    N, H, hd, slots = 6, 2, 64, 32
+    q, k, v, pos, sl, cos, sin = _inputs(N, H, H, hd, hd, torch.float16, slots, seed=5)
+    pos[3] = 4096                      # one past the table
+    pos[5] = -1
+    Kc = torch.full((slots, H * hd), 7.0, dtype=torch.float16, device="cuda")
+    Vc = torch.full_like(Kc, -7.0)
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    qd, kd = q.cuda(), k.cuda()
+    A.rope_and_cache_write(qd, kd, v.cuda(), pos.cuda(), cos.cuda(), sin.cuda(), sl.cuda(), Kc, Vc, hd, err_flag=flag)
+    assert int(flag.item()) == 2
+    good = [0, 1, 2, 4]
+    q_ref, k_ref = orc.rope(q[good], k[good], pos[good], cos, sin, hd)
+    assert torch.equal(qd.cpu()[good], q_ref) and torch.equal(kd.cpu()[good], k_ref)
+    for t in (3, 5):
+        assert torch.equal(qd.cpu()[t], q[t]) and torch.equal(kd.cpu()[t], k[t])
+        assert (Kc[sl[t]] == 7.0).all() and (Vc[sl[t]] == -7.0).all()
+    assert torch.equal(Kc.cpu()[sl[good].long()], k_ref) and torch.equal(Vc.cpu()[sl[good].long()], v[good])

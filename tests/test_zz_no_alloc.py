@@ -3,25 +3,28 @@
 Collected last on purpose (file name), so a run that stops at the first failure has already run
 everything else.  The call goes straight through the C ABI with ctypes: the caller supplies the
 inputs and the output buffer, the library supplies the split-KV scratch from a fixed array in its
-device image.  It must agree with the regular entry point (which gets a torch-allocated
-workspace) on two calls in a row, the second with other inputs so that stale scratch contents
-from the first call would show.
+device image.  Both entry points run the same kernels on the same chunking, so their outputs must
+be bit-identical, on two calls in a row, the second with other inputs so that stale scratch
+contents from the first call would show; each is also held to the decode tolerance against the
+CPU oracle, so that a mix-up that hit both entry points alike would show too.
 """
 import pytest
 import torch
 
+from oracle import attention_oracle as orc
 from helpers import decode_inputs, uniform_lens
 
 pytestmark = pytest.mark.gpu
 
-TOL = 2e-3   # the fp16 decode tolerance used across the decode tests
+TOL = 2e-3   # the fp16 decode tolerance used across the decode tests (max-abs against the fp32-evaluated oracle)
 
 
 def _call_pair(seed, B, H, D, lo, hi, chunk):
     from attention_impl_b200 import _lib
     lib = _lib.lib
     lens = uniform_lens(B, lo, hi, seed=seed)
-    Q, K, V, Kc, Vc, ci, off = [t.cuda() for t in decode_inputs(B, H, D, lens, 16384, torch.float16, seed=seed)]
+    host = decode_inputs(B, H, D, lens, 16384, torch.float16, seed=seed)
+    Q, K, V, Kc, Vc, ci, off = [t.cuda() for t in host]
     T = ci.numel()
     scale = D ** -0.5
     stream = torch.cuda.current_stream().cuda_stream
@@ -39,17 +42,18 @@ def _call_pair(seed, B, H, D, lo, hi, chunk):
         out_new.data_ptr(), B, H, D, T, Kc.size(0), chunk, scale, None, None, _lib.F16, _lib.F16, None, stream),
         "paged_decode_static_scratch")
     torch.cuda.synchronize()
-    return out_ref.float().cpu(), out_new.float().cpu()
+    _, _, O32 = orc.paged_decode(*host, H, compute_dtype=torch.float32)
+    return out_ref.cpu(), out_new.cpu(), O32.float()
 
 
 def test_static_scratch_decode_matches_regular_entry_point_twice():
-    ref1, new1 = _call_pair(seed=31, B=8, H=32, D=128, lo=128, hi=1024, chunk=32)
-    assert torch.isfinite(new1).all()
-    assert (ref1 - new1).abs().max() <= TOL
+    ref1, new1, orc1 = _call_pair(seed=31, B=8, H=32, D=128, lo=128, hi=1024, chunk=32)
+    assert torch.equal(ref1, new1)
+    assert (new1.float() - orc1).abs().max() <= TOL
     # second call, different shapes and chunking: leftovers of the first call must not matter
-    ref2, new2 = _call_pair(seed=32, B=5, H=8, D=128, lo=1, hi=700, chunk=64)
-    assert torch.isfinite(new2).all()
-    assert (ref2 - new2).abs().max() <= TOL
+    ref2, new2, orc2 = _call_pair(seed=32, B=5, H=8, D=128, lo=1, hi=700, chunk=64)
+    assert torch.equal(ref2, new2)
+    assert (new2.float() - orc2).abs().max() <= TOL
 
 
 def test_static_scratch_rejects_sizes_beyond_its_limit():
