@@ -50,11 +50,6 @@ struct DecodeParams {
     int G;            // query heads per KV head
     int block_size;   // tokens per KV block; 1 = `slots` is a per-token table
     int max_blocks;   // block_size > 1: `slots` is a [B, max_blocks] block table
-    // fused combine (multi-head kernel only); tickets == nullptr: partial rows only
-    int32_t* tickets; // [B, head_groups] counters, zero on entry, left zero
-    const void* k_new;
-    const void* v_new;
-    void* out;
 };
 
 // Pool row of token `t` (absolute index in the token stream) of the unit's sequence, or -1.
@@ -62,7 +57,7 @@ __device__ __forceinline__ int token_slot(const DecodeParams& p, const struct Un
 
 struct Unit {
     int b;
-    int64_t seq_beg, seq_end, tbeg, tend;
+    int64_t seq_beg, tbeg, tend;
 };
 
 // beg(b) for b in [0, B]: start of sequence b in the token stream (beg(B) = total).
@@ -109,7 +104,6 @@ __device__ __forceinline__ bool resolve_unit(int64_t u, int B, int chunk, const 
     const int64_t tb = cell * chunk, te = tb + chunk;
     out.b = lo;
     out.seq_beg = seq_beg;
-    out.seq_end = seq_end;
     out.tbeg = tb > seq_beg ? tb : seq_beg;
     out.tend = te < seq_end ? te : seq_end;
     return out.tbeg < out.tend;
@@ -146,149 +140,40 @@ template <> struct RowChunk<__nv_fp8_e4m3, 16> {
     }
 };
 
-// ---------------------------------------------------------------------------------------------
-// Fused combine: the last CTA of a (sequence, head group) folds that group's partial rows itself.
-//
-// Every CTA that has written its partial rows publishes them (__threadfence) and takes a ticket
-// with one atomicAdd on the group's counter; the CTA that draws the last ticket (it knows how many
-// units the sequence has from the offsets) reads the group's rows back from L2, folds them and the
-// current token, and writes the final output.  No CTA ever waits for another one, so nothing can
-// hang, and the second launch and its re-read of the rows through a fresh grid go away: at batch 8
-// the combine launch was a third of the step.  The counters live in the tail of the caller's
-// workspace; they must be zero on entry and the last CTA leaves them zero again.
-// A warp's lanes keep the mapping of the main loop: lane `sub` of a row group owns EPL dims of the
-// group's head.  Rows were written by other SMs: they are read with ld.global.cg (L2).
-// ---------------------------------------------------------------------------------------------
-// What the epilogue needs of DecodeParams, passed by value: the epilogue is a real call (so that
-// its registers do not add to the streaming loop's), and a reference to the kernel's parameter
-// block would make every thread copy the block to its stack.
-struct FusedArgs {
-    const float* part;
-    const void* q;
-    const void* k_new;
-    const void* v_new;
-    void* out;
-    int32_t* tickets;
-    int H, chunk, head_groups;
-    float scale_log2;
-};
-
-template <typename QT, int D, int EPL>
-__device__ __forceinline__ void fused_combine_head(const FusedArgs p, int b, int h, bool h_ok, int sub,
-                                                   int64_t seq_beg, int64_t seq_end) {
-    constexpr int LPR = D / EPL, RS = D + 2;
-    const int64_t c0 = seq_beg / p.chunk;
-    const int count = seq_end > seq_beg ? (int)((seq_end - 1) / p.chunk - c0 + 1) : 0;
-    const int64_t ustride = (int64_t)p.H * RS;
-    const float* base = p.part + ((c0 + b) * p.H + h) * RS;          // unit i of the sequence: base + i * ustride
-    const int64_t qoff = ((int64_t)b * p.H + h) * D + sub * EPL;
-    const QT* qp = (const QT*)p.q + qoff;
-    const QT* kp = (const QT*)p.k_new + qoff;
-    const QT* vp = (const QT*)p.v_new + qoff;
-    float acc = 0.f;
-#pragma unroll
-    for (int i = 0; i < EPL; ++i) acc = fmaf(to_f32<QT>(qp[i]), to_f32<QT>(kp[i]), acc);
-    const float s_new = group_sum<LPR>(acc) * p.scale_log2;
-    float M = s_new;
-#pragma unroll 8
-    for (int i = 0; i < count; ++i) M = fmaxf(M, __ldcg(base + i * ustride + D));
-    float L = 0.f, o[EPL];
-#pragma unroll
-    for (int e = 0; e < EPL; ++e) o[e] = 0.f;
-#pragma unroll 4
-    for (int i = 0; i < count; ++i) {
-        const float* row = base + i * ustride;
-        const float2 ml = __ldcg(reinterpret_cast<const float2*>(row + D));
-        const float w = ml.x > -INFINITY ? exp2f(ml.x - M) : 0.f;
-        L = fmaf(ml.y, w, L);
-        const float2* src = reinterpret_cast<const float2*>(row + sub * EPL);
-#pragma unroll
-        for (int e = 0; e < EPL / 2; ++e) {
-            const float2 r = __ldcg(src + e);
-            o[2 * e] = fmaf(r.x, w, o[2 * e]);
-            o[2 * e + 1] = fmaf(r.y, w, o[2 * e + 1]);
-        }
-    }
-    const float w_new = exp2f(s_new - M);
-    L += w_new;
-    const float inv = 1.f / L;
-    if (!h_ok) return;
-    QT* dst = (QT*)p.out + qoff;
-#pragma unroll
-    for (int e = 0; e < EPL; ++e) dst[e] = from_f32<QT>(fmaf(w_new, to_f32<QT>(vp[e]), o[e]) * inv);
-}
-
-// Ticket + combine for a CTA whose warps own `HPW` adjacent heads each (h_raw = the lane's head,
-// `warp_on` = the warp has at least one head).  Called by every thread of the CTA.
-template <typename QT, int D, int EPL>
-__device__ __noinline__ void fused_combine_cta(const FusedArgs p, int b, int64_t seq_beg, int64_t seq_end, int hg,
-                                               int h, bool h_ok, bool warp_on, int sub) {
-    __shared__ int s_last;
-    if (seq_end <= seq_beg) {              // a sequence without cached tokens: no rows, no ticket (CTA-uniform)
-        if (warp_on) fused_combine_head<QT, D, EPL>(p, b, h, h_ok, sub, seq_beg, seq_end);
-        return;
-    }
-    __threadfence();                       // this thread's partial-row stores are visible device-wide
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        const int64_t c0 = seq_beg / p.chunk;
-        const int n_units = (int)((seq_end - 1) / p.chunk - c0 + 1);
-        int32_t* t = p.tickets + (int64_t)b * p.head_groups + hg;
-        const int last = atomicAdd(t, 1) == n_units - 1;
-        if (last) *t = 0;                  // every other CTA of the group has already drawn: leave the counter clean
-        s_last = last;
-        __threadfence();
-    }
-    __syncthreads();
-    if (!s_last || !warp_on) return;
-    fused_combine_head<QT, D, EPL>(p, b, h, h_ok, sub, seq_beg, seq_end);
-}
-
 // Multi-head attention with a per-token slot table (the reference's case and the benchmarked one).
 // The general kernel below (grouped-query heads, block tables) computes the same thing with G = 1,
 // block_size = 1, but measured 7 % slower on this path (6.40 vs 6.91 TB/s on a 15 GB fp16 case), so
 // the specialised form is kept.
 // The 32/LPR row groups of a warp take adjacent HEADS of one token, so a warp-wide load is one
 // contiguous 512-byte piece of a token's row and a CTA of 8 warps streams 4 KB per token; each
-// group keeps its own softmax state and nothing is merged across groups.
-//
-// PIPE = false: a tile is 8 tokens; its 8 K-row and 8 V-row loads are issued, then consumed.  With
-// many CTAs per SM in different phases the memory pipe stays full: this is the form for long units.
-// PIPE = true: a tile is 4 tokens and the loads of tile t+1 are issued BEFORE tile t is consumed
-// (two register sets).  For small batches the whole grid is one wave of CTAs that start together
-// and stay in step; without the overlap every SM alternates between "all loads in flight" and
-// "all warps computing", and DRAM idles in the second phase.
-template <typename QT, typename KVT, int D, bool PIPE>
-__global__ void __launch_bounds__(256, 2)      // two CTAs (16 warps) per SM: at most 128 registers
+// group keeps its own softmax state and nothing is merged across groups.  A tile is 8 tokens; its
+// 8 K-row and 8 V-row loads are issued, then consumed.  With many CTAs per SM in different phases
+// the memory pipe stays full: this is the form for long units (large batches, long contexts).
+template <typename QT, typename KVT, int D>
+__global__ void __launch_bounds__(256)
 paged_decode_mha_kernel(const DecodeParams p) {
     constexpr int EPL = 16 / (int)sizeof(KVT);   // elements per lane (one 16-byte slice)
     constexpr int LPR = D / EPL;                 // lanes per row
-    constexpr int HPW = 32 / LPR;                // heads per warp = rows per warp-wide load
-    constexpr int U = PIPE ? 4 : 8;              // tokens per tile = loads in flight per lane, tensor and register set
-    static_assert(LPR >= 1 && LPR <= 32, "unsupported head_dim");
+    constexpr int TPI = 32 / LPR;                // rows per warp-wide load
+    constexpr int U = 8;                         // loads in flight per lane and tensor = tokens per tile
+    constexpr int TILE = U;
+    constexpr int HPW = TPI;                     // heads per warp
+    static_assert(LPR >= 1 && LPR <= 32 && TILE <= 32, "unsupported head_dim");
 
     __shared__ int32_t s_off[kMaxStagedB];
+    // The combine kernel that follows is launched as a programmatic dependent: its CTAs may be
+    // scheduled (and run their prologue up to griddepcontrol.wait) while this grid still runs.
+    asm volatile("griddepcontrol.launch_dependents;");
     SeqBounds sb{stage_offsets(p, s_off), p.uniform_ctx, p.n_tokens};
 
     const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t u = blockIdx.x / p.head_groups;
-    const int hg = blockIdx.x % p.head_groups;
     const int sub = lane % LPR, grp = lane / LPR;
-    const int h_raw = (hg * warps + warp) * HPW + grp;
-    const bool warp_on = h_raw - grp < p.H;      // the warp has at least one head
-    const bool h_ok = h_raw < p.H;               // trailing groups of the last warp may have none
-    const int h = h_ok ? h_raw : p.H - 1;
+    const int h_raw = ((blockIdx.x % p.head_groups) * warps + warp) * HPW + grp;
     Unit un;
-    if (!resolve_unit(u, p.B, p.chunk, sb, un)) {      // CTA-uniform
-        // Fused combine: a sequence without cached tokens has no unit, hence no CTA that would
-        // write its output; the one id that resolves to it (cell = its start / chunk) does.
-        if (p.tickets && un.seq_beg == un.seq_end && u - un.b == un.seq_beg / p.chunk)
-            fused_combine_cta<QT, D, EPL>(FusedArgs{p.part, p.q, p.k_new, p.v_new, p.out, p.tickets, p.H, p.chunk,
-                                                    p.head_groups, p.scale_log2},
-                                          un.b, un.seq_beg, un.seq_end, hg, h, h_ok, warp_on, sub);
-        return;
-    }
-    if (warp_on) {
+    if (!resolve_unit(u, p.B, p.chunk, sb, un) || h_raw - grp >= p.H) return;
+    const bool h_ok = h_raw < p.H;               // trailing groups of the last warp may have no head
+    const int h = h_ok ? h_raw : p.H - 1;
     const int64_t row_bytes = (int64_t)p.H * D * sizeof(KVT);
     const char* kbase = (const char*)p.k_cache + ((int64_t)h * D + sub * EPL) * sizeof(KVT);
     const char* vbase = (const char*)p.v_cache + ((int64_t)h * D + sub * EPL) * sizeof(KVT);
@@ -301,7 +186,7 @@ paged_decode_mha_kernel(const DecodeParams p) {
     constexpr bool kFp8 = sizeof(KVT) == 1;
     float qf[kFp8 ? 1 : EPL];
     __half2 q2[kFp8 ? EPL / 2 : 1];
-    const float qs = p.scale_log2 * (p.k_scale ? p.k_scale[h] : 1.f);
+    float qs = p.scale_log2 * (p.k_scale ? p.k_scale[h] : 1.f);
     {
         const QT* qp = (const QT*)p.q + ((int64_t)un.b * p.H + h) * D + sub * EPL;
         if constexpr (kFp8) {
@@ -316,30 +201,41 @@ paged_decode_mha_kernel(const DecodeParams p) {
 #pragma unroll
     for (int i = 0; i < EPL; ++i) o[i] = 0.f;
 
-    // slots of `n` consecutive tokens from t0, one per lane (lanes >= n and tokens past the end: -1)
-    auto load_slots = [&](int64_t t0, int n) -> int {
+    auto load_slot = [&](int64_t t0) -> int {
         const int64_t t = t0 + lane;
         int s = -1;
-        if (lane < n && t < un.tend) {
+        if (lane < TILE && t < un.tend) {
             const int64_t v = p.slots ? (int64_t)p.slots[t] : t;
             if (v >= 0 && v < p.n_slots) s = (int)v;
             else if (p.err_flag) atomicOr(p.err_flag, ATTN_B200_FLAG_BAD_SLOT);
         }
         return s;
     };
-    // issue the K-row and V-row loads of the U tokens whose slots sit in lanes first..first+U-1 of `slots`
-    auto issue_tile = [&](uint4 (&kr)[U], uint4 (&vr)[U], int (&sl)[U], int slots, int first) {
+
+    int next_slot = load_slot(un.tbeg);
+    for (int64_t t0 = un.tbeg; t0 < un.tend; t0 += TILE) {
+        const int my_slot = next_slot;
+        uint4 kr[U], vr[U];
+        int sl[U];
 #pragma unroll
         for (int j = 0; j < U; ++j) {
-            sl[j] = __shfl_sync(0xffffffffu, slots, first + j);
-            kr[j] = sl[j] >= 0 ? ldg_stream128(kbase + (int64_t)sl[j] * row_bytes) : make_uint4(0, 0, 0, 0);
+            sl[j] = __shfl_sync(0xffffffffu, my_slot, j);
+            if (sl[j] >= 0) {
+                kr[j] = ldg_stream128(kbase + (int64_t)sl[j] * row_bytes);
+            } else {
+                kr[j] = make_uint4(0, 0, 0, 0);
+            }
         }
 #pragma unroll
-        for (int j = 0; j < U; ++j)
-            vr[j] = sl[j] >= 0 ? ldg_stream128(vbase + (int64_t)sl[j] * row_bytes) : make_uint4(0, 0, 0, 0);
-    };
-    // fold one tile (tokens t0 .. t0+U-1) into the running (m, l, o)
-    auto consume_tile = [&](const uint4 (&kr)[U], const uint4 (&vr)[U], const int (&sl)[U], int64_t t0) {
+        for (int j = 0; j < U; ++j) {
+            if (sl[j] >= 0) {
+                vr[j] = ldg_stream128(vbase + (int64_t)sl[j] * row_bytes);
+            } else {
+                vr[j] = make_uint4(0, 0, 0, 0);
+            }
+        }
+        if (t0 + TILE < un.tend) next_slot = load_slot(t0 + TILE);
+
         float s[U];
         float tmax = -INFINITY;
 #pragma unroll
@@ -367,11 +263,15 @@ paged_decode_mha_kernel(const DecodeParams p) {
             s[j] = sl[j] >= 0 ? acc : -INFINITY;
             tmax = fmaxf(tmax, s[j]);
         }
-        if (p.S && sub == 0 && h_ok) {
+        if (p.S) {
+            if (sub == 0) {
 #pragma unroll
-            for (int j = 0; j < U; ++j)
-                if (sl[j] >= 0)
-                    p.S[((int64_t)un.b * p.H + h) * p.sp_stride + (t0 + j - un.seq_beg)] = (double)(s[j] * kLn2);
+                for (int j = 0; j < U; ++j)
+                    if (sl[j] >= 0)
+                        if (h_ok)
+                            p.S[((int64_t)un.b * p.H + h) * p.sp_stride + (t0 + j - un.seq_beg)] =
+                                (double)(s[j] * kLn2);
+            }
         }
         const float m_new = fmaxf(m, tmax);
         if (m_new > -INFINITY) {  // at least one valid row so far
@@ -417,66 +317,17 @@ paged_decode_mha_kernel(const DecodeParams p) {
             }
             m = m_new;
         }
-    };
-
-    if constexpr (!PIPE) {
-        // slots are read once per tile by the warp (coalesced), the next tile's are prefetched
-        int next_slot = load_slots(un.tbeg, U);
-        for (int64_t t0 = un.tbeg; t0 < un.tend; t0 += U) {
-            const int my_slot = next_slot;
-            uint4 kr[U], vr[U];
-            int sl[U];
-            issue_tile(kr, vr, sl, my_slot, 0);
-            if (t0 + U < un.tend) next_slot = load_slots(t0 + U, U);
-            consume_tile(kr, vr, sl, t0);
-        }
-    } else {
-        // slots are read 32 tokens at a time (8 tiles), the next 32 one block ahead; tiles alternate
-        // between two register sets so that one tile's rows are always on their way
-        constexpr int TPB = 32 / U;                               // tiles per block of 32 slots
-        const int n_tiles = (int)((un.tend - un.tbeg + U - 1) / U);
-        int blk_cur = load_slots(un.tbeg, 32);
-        int blk_nxt = un.tbeg + 32 < un.tend ? load_slots(un.tbeg + 32, 32) : -1;
-        uint4 ka[U], va[U], kb[U], vb[U];
-        int sa[U], sbuf[U];
-        auto issue_at = [&](uint4 (&kr)[U], uint4 (&vr)[U], int (&sl)[U], int it) {   // `it` increases by one per call
-            if (it > 0 && it % TPB == 0) {
-                blk_cur = blk_nxt;
-                const int64_t tn = un.tbeg + (int64_t)(it / TPB + 1) * 32;
-                blk_nxt = tn < un.tend ? load_slots(tn, 32) : -1;
-            }
-            issue_tile(kr, vr, sl, blk_cur, (it % TPB) * U);
-        };
-        issue_at(ka, va, sa, 0);
-        for (int it = 0; it < n_tiles; it += 2) {
-            if (it + 1 < n_tiles) issue_at(kb, vb, sbuf, it + 1);
-            consume_tile(ka, va, sa, un.tbeg + (int64_t)it * U);
-            if (it + 2 < n_tiles) issue_at(ka, va, sa, it + 2);
-            if (it + 1 < n_tiles) consume_tile(kb, vb, sbuf, un.tbeg + (int64_t)(it + 1) * U);
-        }
     }
+    float* row = p.part + ((int64_t)u * p.H + h) * (D + 2);
     if (h_ok) {
-        float* row = p.part + ((int64_t)u * p.H + h) * (D + 2);
         const float vs = p.v_scale ? p.v_scale[h] : 1.f;
         float2* dst = reinterpret_cast<float2*>(row + sub * EPL);
 #pragma unroll
         for (int i = 0; i < EPL / 2; ++i) dst[i] = make_float2(o[2 * i] * vs, o[2 * i + 1] * vs);
         if (sub == 0) *reinterpret_cast<float2*>(row + D) = make_float2(m, l);
     }
-    }  // warp_on
-    if (p.tickets) {
-        // everything the epilogue needs is derived again from the block and thread indices, so that
-        // it keeps no register alive across the streaming loop
-        Unit un2;
-        resolve_unit(blockIdx.x / p.head_groups, p.B, p.chunk, sb, un2);
-        const int hg2 = blockIdx.x % p.head_groups;
-        const int hr2 = (hg2 * (blockDim.x >> 5) + (threadIdx.x >> 5)) * HPW + (threadIdx.x & 31) / LPR;
-        fused_combine_cta<QT, D, EPL>(FusedArgs{p.part, p.q, p.k_new, p.v_new, p.out, p.tickets, p.H, p.chunk,
-                                                p.head_groups, p.scale_log2},
-                                      un2.b, un2.seq_beg, un2.seq_end, hg2, hr2 < p.H ? hr2 : p.H - 1, hr2 < p.H,
-                                      hr2 - (int)((threadIdx.x & 31) / LPR) < p.H, (threadIdx.x & 31) % LPR);
-    }
 }
+
 
 // The 32/LPR row groups of a warp take ADJACENT KV HEADS of one token, so a warp-wide load is one
 // contiguous 512-byte piece of the token's row and a CTA of 8 warps streams 4 KB per token; each
@@ -834,6 +685,8 @@ lse_combine_kernel(const CombineParams p) {
     int64_t first, stride;
     int count;
     int64_t n_ctx = 0;
+    // (offsets, q and the new token are inputs of the step, not products of the partial kernel:
+    // they may be read before the grid dependency is resolved)
     if (p.n_parts > 0) {
         first = (int64_t)b * p.H + h;
         stride = (int64_t)p.B * p.H;
@@ -847,6 +700,18 @@ lse_combine_kernel(const CombineParams p) {
         stride = p.H;
         count = (int)(c1 - c0 + 1);
     }
+    float s_new = -INFINITY;
+    if (p.k_new) {
+        const QT* qp = (const QT*)p.q + ((int64_t)b * p.H + h) * D;
+        const QT* kp = (const QT*)p.k_new + ((int64_t)b * (p.H / p.G) + h / p.G) * D;
+        float acc = 0.f;
+        for (int d = lane; d < D; d += 32) acc = fmaf(to_f32<QT>(qp[d]), to_f32<QT>(kp[d]), acc);
+        s_new = group_sum<32>(acc) * p.scale_log2;
+    }
+    // Launched as a programmatic dependent of the partial kernel (see run_combine): the CTA may have
+    // started while that grid was still running; from here on its rows are needed.  Without such a
+    // launch relation the instruction returns at once.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     // global maximum (log2 domain) and denominator: the first 128 units stay in registers
     constexpr int KR = 4;
     float mr[KR], lr[KR];
@@ -859,15 +724,7 @@ lse_combine_kernel(const CombineParams p) {
     }
     float M = fmaxf(fmaxf(mr[0], mr[1]), fmaxf(mr[2], mr[3]));
     for (int i = lane + 32 * KR; i < count; i += 32) M = fmaxf(M, p.parts[(first + i * stride) * RS + D]);
-    float s_new = -INFINITY;
-    if (p.k_new) {
-        const QT* qp = (const QT*)p.q + ((int64_t)b * p.H + h) * D;
-        const QT* kp = (const QT*)p.k_new + ((int64_t)b * (p.H / p.G) + h / p.G) * D;
-        float acc = 0.f;
-        for (int d = lane; d < D; d += 32) acc = fmaf(to_f32<QT>(qp[d]), to_f32<QT>(kp[d]), acc);
-        s_new = group_sum<32>(acc) * p.scale_log2;
-        M = fmaxf(M, s_new);
-    }
+    if (p.k_new) M = fmaxf(M, s_new);
     M = group_max<32>(M);
     float L = 0.f;
 #pragma unroll
@@ -948,29 +805,14 @@ lse_combine_kernel(const CombineParams p) {
 // host side
 // ---------------------------------------------------------------------------------------------
 static inline int64_t max_units(int B, int64_t n_tokens, int chunk) { return n_tokens / chunk + B + 1; }
-constexpr int kPipeMaxChunk = 128;     // units up to this length run the software-pipelined multi-head kernel
-// workspace = [partial rows | fused-combine tickets int32 [B, H]] (one ticket per head group; H bounds their number)
-static inline size_t rows_bytes(int B, int H, int D, int64_t n_tokens, int chunk) {
-    return ((size_t)max_units(B, n_tokens, chunk) * H * (D + 2) * sizeof(float) + 15) & ~(size_t)15;
-}
-static inline size_t ticket_bytes(int B, int H) { return (size_t)B * H * sizeof(int32_t); }
-
 template <typename QT, typename KVT>
 static int launch_mha(const DecodeParams& p, int warps, int64_t n_units, cudaStream_t st) {
     const int64_t blocks = n_units * p.head_groups;
     if (blocks > 0x7fffffffLL) return ATTN_B200_ETOOLARGE;
-    // short units of 16-bit rows (small batches: the whole grid is about one wave of CTAs in step with
-    // each other) take the software-pipelined form; long ones, and e4m3 rows (whose pipelined form
-    // does not fit 128 registers), the plain form
-    auto go = [&](auto pipelined, auto plain) {
-        if (sizeof(KVT) == 2 && p.chunk <= kPipeMaxChunk) pipelined<<<(unsigned)blocks, warps * 32, 0, st>>>(p);
-        else plain<<<(unsigned)blocks, warps * 32, 0, st>>>(p);
-    };
-    constexpr bool kPipeBuilt = sizeof(KVT) == 2;      // the e4m3 pipelined form is never launched: do not build it
     switch (p.D) {
-        case 64: go(paged_decode_mha_kernel<QT, KVT, 64, kPipeBuilt>, paged_decode_mha_kernel<QT, KVT, 64, false>); break;
-        case 128: go(paged_decode_mha_kernel<QT, KVT, 128, kPipeBuilt>, paged_decode_mha_kernel<QT, KVT, 128, false>); break;
-        case 256: go(paged_decode_mha_kernel<QT, KVT, 256, kPipeBuilt>, paged_decode_mha_kernel<QT, KVT, 256, false>); break;
+        case 64: paged_decode_mha_kernel<QT, KVT, 64><<<(unsigned)blocks, warps * 32, 0, st>>>(p); break;
+        case 128: paged_decode_mha_kernel<QT, KVT, 128><<<(unsigned)blocks, warps * 32, 0, st>>>(p); break;
+        case 256: paged_decode_mha_kernel<QT, KVT, 256><<<(unsigned)blocks, warps * 32, 0, st>>>(p); break;
         default: return ATTN_B200_ESHAPE;
     }
     return (int)cudaGetLastError();
@@ -1105,22 +947,32 @@ static int run_combine(const CombineParams& c, int q_dtype, cudaStream_t st) {
     if (n_rows > 0x7fffffffLL) return ATTN_B200_ETOOLARGE;
     const unsigned blocks = (unsigned)n_rows;
     const bool xchg = c.n_peers > 0 || c.wait_flags != nullptr;
+    // Programmatic dependent launch: the kernel may start while the kernel before it in the stream
+    // (the partial kernel, which releases its dependents at its start) is still running; it waits
+    // for that grid's completion itself, after its prologue.  Saves the launch gap and one round
+    // trip of a step that is a few microseconds long.
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(blocks);
+    cfg.blockDim = dim3(128);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = st;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
     switch (q_dtype) {
         case ATTN_B200_F16:
-            if (xchg) lse_combine_kernel<__half, true><<<blocks, 128, 0, st>>>(c);
-            else lse_combine_kernel<__half, false><<<blocks, 128, 0, st>>>(c);
-            break;
+            return (int)(xchg ? cudaLaunchKernelEx(&cfg, lse_combine_kernel<__half, true>, c)
+                              : cudaLaunchKernelEx(&cfg, lse_combine_kernel<__half, false>, c));
         case ATTN_B200_BF16:
-            if (xchg) lse_combine_kernel<__nv_bfloat16, true><<<blocks, 128, 0, st>>>(c);
-            else lse_combine_kernel<__nv_bfloat16, false><<<blocks, 128, 0, st>>>(c);
-            break;
+            return (int)(xchg ? cudaLaunchKernelEx(&cfg, lse_combine_kernel<__nv_bfloat16, true>, c)
+                              : cudaLaunchKernelEx(&cfg, lse_combine_kernel<__nv_bfloat16, false>, c));
         case ATTN_B200_F32:
             if (xchg) return ATTN_B200_EDTYPE;
-            lse_combine_kernel<float, false><<<blocks, 128, 0, st>>>(c);
-            break;
+            return (int)cudaLaunchKernelEx(&cfg, lse_combine_kernel<float, false>, c);
         default: return ATTN_B200_EDTYPE;
     }
-    return (int)cudaGetLastError();
 }
 
 static int check_common(const void* q, const void* kc, const void* vc, int B, int H, int Hkv, int D, int64_t n_tokens,
@@ -1142,16 +994,7 @@ using namespace attn;
 
 extern "C" size_t attn_b200_paged_decode_workspace_bytes(int B, int H, int D, int64_t n_tokens, int chunk) {
     if (B <= 0 || H <= 0 || D <= 0 || n_tokens < 0 || chunk <= 0) return 0;
-    return rows_bytes(B, H, D, n_tokens, chunk) + ticket_bytes(B, H);
-}
-
-extern "C" size_t attn_b200_paged_decode_ticket_bytes(int B, int H) {
-    return (B <= 0 || H <= 0) ? 0 : ticket_bytes(B, H);
-}
-
-// The fused single-launch form exists for the multi-head kernel with a per-token slot table.
-static bool fused_ok(const DecodeParams& p, int q_dtype, int kv_dtype) {
-    return fast_ok(p, q_dtype, kv_dtype) && p.G == 1 && p.block_size <= 1 && !p.S;
+    return (size_t)max_units(B, n_tokens, chunk) * H * (D + 2) * sizeof(float);
 }
 
 extern "C" int attn_b200_paged_decode_pick_chunk(int B, int H, int D, int64_t n_tokens, int sm_count) {
@@ -1203,13 +1046,8 @@ extern "C" int attn_b200_paged_decode(const void* q, const void* k_new, const vo
     DecodeParams p{q, k_cache, v_cache, slots, offsets, (float*)workspace, S, sp_stride, B, H, D, n_tokens, n_slots,
                    uniform_ctx, chunk, scale * kLog2e, kv_dtype == ATTN_B200_E4M3 ? k_scale : nullptr,
                    kv_dtype == ATTN_B200_E4M3 ? v_scale : nullptr, err_flag, 1, n_kv_heads, G, block_size,
-                   max_blocks, nullptr, k_new, v_new, out};
-    if (stages < 1 || stages > 4) return ATTN_B200_EINVAL;
-    if (stages == 4) {      // one launch: the partial kernel's last CTA per (sequence, head group) combines
-        if (!fused_ok(p, q_dtype, kv_dtype)) return ATTN_B200_ESHAPE;
-        p.tickets = reinterpret_cast<int32_t*>((char*)workspace + rows_bytes(B, H, D, n_tokens, chunk));
-        return run_stage1(p, q_dtype, kv_dtype, st);
-    }
+                   max_blocks};
+    if (stages < 1 || stages > 3) return ATTN_B200_EINVAL;
     if (stages & 1) {
         rc = run_stage1(p, q_dtype, kv_dtype, st);
         if (rc) return rc;
@@ -1239,7 +1077,7 @@ extern "C" int attn_b200_paged_decode_partial(const void* q, const void* k_cache
     DecodeParams p{q, k_cache, v_cache, slots, offsets, (float*)workspace, nullptr, 0, B, H, D, n_tokens, n_slots,
                    0, chunk, scale * kLog2e, kv_dtype == ATTN_B200_E4M3 ? k_scale : nullptr,
                    kv_dtype == ATTN_B200_E4M3 ? v_scale : nullptr, err_flag, 1, n_kv_heads, G, block_size,
-                   max_blocks, nullptr, nullptr, nullptr, nullptr};
+                   max_blocks};
     rc = run_stage1(p, q_dtype, kv_dtype, st);
     if (rc) return rc;
     CombineParams c{(const float*)workspace, 0, q, nullptr, nullptr, nullptr, part_out, nullptr, nullptr, 0,
@@ -1269,7 +1107,7 @@ extern "C" int attn_b200_paged_decode_partial_push(const void* q, const void* k_
     DecodeParams p{q, k_cache, v_cache, slots, offsets, (float*)workspace, nullptr, 0, B, H, D, n_tokens, n_slots,
                    0, chunk, scale * kLog2e, kv_dtype == ATTN_B200_E4M3 ? k_scale : nullptr,
                    kv_dtype == ATTN_B200_E4M3 ? v_scale : nullptr, err_flag, 1, n_kv_heads, G, block_size,
-                   max_blocks, nullptr, nullptr, nullptr, nullptr};
+                   max_blocks};
     rc = run_stage1(p, q_dtype, kv_dtype, st);
     if (rc) return rc;
     CombineParams c{(const float*)workspace, 0, q, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, 0,

@@ -13,7 +13,7 @@
 namespace attn {
 
 int prefill_tc_launch(const void* q, const void* k, const void* v, const int32_t* offsets, void* out, int B,
-                      int64_t n_tokens, int max_len, int H, int D, float scale, int dtype, int out_f32,
+                      int64_t n_tokens, int max_len, int H, int D, float scale, int dtype, int out_f32, int precise,
                       int32_t* err_flag, cudaStream_t st);
 bool prefill_tc_supported(int D, int dtype);
 
@@ -135,8 +135,9 @@ using namespace attn;
 
 extern "C" int attn_b200_varlen_prefill(const void* q, const void* k, const void* v, const int32_t* offsets,
                                         void* out, void* S, void* P, int B, int64_t n_tokens, int max_len, int H,
-                                        int D, float scale, int dtype, int out_f32, int force_generic,
+                                        int D, float scale, int dtype, int out_flags, int force_generic,
                                         int32_t* err_flag, void* stream) {
+    const int out_f32 = out_flags & ATTN_B200_PREFILL_OUT_F32, precise = out_flags & ATTN_B200_PREFILL_PRECISE_P;
     if (!q || !k || !v || !offsets || !out || B <= 0 || H <= 0 || D <= 0 || n_tokens < 0 || max_len < 0)
         return ATTN_B200_EINVAL;
     if ((S == nullptr) != (P == nullptr)) return ATTN_B200_EINVAL;
@@ -146,8 +147,8 @@ extern "C" int attn_b200_varlen_prefill(const void* q, const void* k, const void
     if (max_len == 0)          // no sequence has a token: the output is all zeros, as the reference's zeros_like
         return (int)cudaMemsetAsync(out, 0, (size_t)n_tokens * H * D * out_el, st);
     if (!force_generic && !S && prefill_tc_supported(D, dtype))
-        return prefill_tc_launch(q, k, v, offsets, out, B, n_tokens, max_len, H, D, scale, dtype, out_f32, err_flag,
-                                 st);
+        return prefill_tc_launch(q, k, v, offsets, out, B, n_tokens, max_len, H, D, scale, dtype, out_f32, precise,
+                                 err_flag, st);
     if (out_f32) return ATTN_B200_EDTYPE;
     DenseParams p{q, k, v, nullptr, offsets, out, S, P, B, H, D, max_len, n_tokens, scale, 10000.f, 1, err_flag};
     return launch_dense(p, dtype, st);

@@ -38,6 +38,7 @@ struct Params {
     int out_f32;
     int32_t* err_flag;
     int* launch_abort;   // this launch's abort word (LaunchState::abort)
+    int split_rows;      // query rows below this index in their sequence carry P as two terms (see `split`)
 };
 
 // =============================================================================================
@@ -66,6 +67,10 @@ struct Params {
 // a sequence's first 256 query rows writes P as TWO terms, hi = round(p) and lo = round(p - hi),
 // and the MMA thread issues P.V for both (columns 0..63 and 64..127 of the S region): 2^-17 per
 // probability there.  That item is 3 of a sequence's ~150 tile steps; the rest is unchanged.
+// What remains for bf16 is the rounding of a single dominant probability: an outlier score in a
+// row of a few hundred keys takes p ~ 0.3, and 0.3 * 2^-9 * |v| reaches 3.4e-3 (p99.9 is 4e-4).
+// Params::split_rows = 256 is that default; a caller who wants 2e-3 everywhere asks for two terms
+// on every row (split_rows = INT_MAX: half as many P.V MMAs again and a second pass over P).
 constexpr int THREADS2 = 384;   // 3 warpgroups: softmax 0, softmax 1, {TMA, MMA, 2 idle warps}
 
 // One softmax thread = one query row (TMEM lane) of a 128-row tile: walks the key tiles, turns S into
@@ -145,22 +150,28 @@ __device__ __forceinline__ void softmax_row(unsigned long long* s_full, unsigned
                 // share the schedulers: measured 895 against 820 TFLOP/s).
                 float rs4[4] = {0.f, 0.f, 0.f, 0.f};
                 const float nm = -m_ref;
+                // the four probabilities of elements c*64 + i .. + 3; the second pass of `split` calls
+                // this again and must get the very same bits (hi is re-derived there from p)
+                auto probs4 = [&](int c, int i, float& p0, float& p1, float& p2, float& p3) {
+                    float x0, x1, x2, x3;
+                    fma2(x0, x1, sv[c * 64 + i], sv[c * 64 + i + 1], p.scale_log2, p.scale_log2, nm, nm);
+                    fma2(x2, x3, sv[c * 64 + i + 2], sv[c * 64 + i + 3], p.scale_log2, p.scale_log2, nm, nm);
+                    p0 = fast_exp2(x0);
+                    p1 = fast_exp2(x1);
+                    if (kPolyOf8 == 4 || (kPolyOf8 == 2 && (i & 4)) || (kPolyOf8 == 1 && (i & 12) == 12)) {
+                        exp2_poly2(p2, p3, x2, x3);
+                    } else {
+                        p2 = fast_exp2(x2);
+                        p3 = fast_exp2(x3);
+                    }
+                };
 #pragma unroll
                 for (int c = 0; c < 2; ++c) {
                     uint32_t pk[32];
 #pragma unroll
                     for (int i = 0; i < 64; i += 4) {
-                        float x0, x1, x2, x3, p0, p1, p2, p3;
-                        fma2(x0, x1, sv[c * 64 + i], sv[c * 64 + i + 1], p.scale_log2, p.scale_log2, nm, nm);
-                        fma2(x2, x3, sv[c * 64 + i + 2], sv[c * 64 + i + 3], p.scale_log2, p.scale_log2, nm, nm);
-                        p0 = fast_exp2(x0);
-                        p1 = fast_exp2(x1);
-                        if (kPolyOf8 == 4 || (kPolyOf8 == 2 && (i & 4)) || (kPolyOf8 == 1 && (i & 12) == 12)) {
-                            exp2_poly2(p2, p3, x2, x3);
-                        } else {
-                            p2 = fast_exp2(x2);
-                            p3 = fast_exp2(x3);
-                        }
+                        float p0, p1, p2, p3;
+                        probs4(c, i, p0, p1, p2, p3);
                         add2(rs4[0], rs4[1], rs4[0], rs4[1], p0, p1);
                         add2(rs4[2], rs4[3], rs4[2], rs4[3], p2, p3);
                         pk[i >> 1] = pack2<T>(p0, p1);
@@ -173,28 +184,29 @@ __device__ __forceinline__ void softmax_row(unsigned long long* s_full, unsigned
                         mbar_arrive(p_half);
                     }
                 }
+                if (split) {
+                    // Second term of P for rows with few visible keys (see the note on `split` above
+                    // the kernels): lo = p - hi with hi = round(p) exactly as stored above, rounded to
+                    // the input type, into columns 64..127 of the S region (free: the whole S row is in
+                    // registers).  Cold path: the first item of a sequence, or every item on request.
+#pragma unroll
+                    for (int c = 0; c < 2; ++c) {
+                        uint32_t pk[32];
+#pragma unroll
+                        for (int i = 0; i < 64; i += 4) {
+                            float p0, p1, p2, p3, h0, h1, h2, h3;
+                            probs4(c, i, p0, p1, p2, p3);
+                            unpack2(pack2<T>(p0, p1), T(), h0, h1);
+                            unpack2(pack2<T>(p2, p3), T(), h2, h3);
+                            pk[i >> 1] = pack2<T>(p0 - h0, p1 - h1);
+                            pk[(i >> 1) + 1] = pack2<T>(p2 - h2, p3 - h3);
+                        }
+                        tmem_st32(s_addr + 64 + c * 32, pk);
+                    }
+                }
                 rs = (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
             }
             l += rs;
-            if (split) {
-                // Second term of P for rows with few visible keys (see the note on `split` above the
-                // kernels): lo = p - round(p), rounded to the input type, into columns 64..127 of the
-                // S region (free: the whole S row is in registers).  Cold path: first item of a sequence.
-                const float nm = -m_ref;
-#pragma unroll
-                for (int c = 0; c < 2; ++c) {
-                    uint32_t pk[32];
-#pragma unroll
-                    for (int i = 0; i < 64; i += 2) {
-                        const float p0 = fast_exp2(fmaf(sv[c * 64 + i], p.scale_log2, nm));
-                        const float p1 = fast_exp2(fmaf(sv[c * 64 + i + 1], p.scale_log2, nm));
-                        float h0, h1;
-                        unpack2(pack2<T>(p0, p1), T(), h0, h1);
-                        pk[i >> 1] = pack2<T>(p0 - h0, p1 - h1);
-                    }
-                    tmem_st32(s_addr + 64 + c * 32, pk);
-                }
-            }
             tmem_st_wait();
             tc_fence_before();
             mbar_arrive(p_full);
@@ -518,7 +530,7 @@ prefill_tc2p_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                             issue_pv(w, s, 0, j == 0, false);
                             if (!(ok = mbar_wait_spin(&sm.p_full[w], (c[w] + j) & 1, wc))) break;
                             tc_fence_after();
-                            issue_pv(w, s, 1, j == 0, it.tp == 0);
+                            issue_pv(w, s, 1, j == 0, it.q0 < p.split_rows);
                         }
                         if (t == 1) umma_commit(&sm.v_empty[s]);
                         if (j + 1 < nw[w]) {
@@ -562,7 +574,7 @@ prefill_tc2p_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             if (nk == 0) continue;
             const int tq = 2 * it.tp + u;
             softmax_row<T, 2>(&sm.s_full[w], &sm.p_half[w], &sm.p_full[w], &sm.o_full[w], s_addr, o_addr, nk, tq * BM + r, r, p,
-                              wc, it.q0 + u * BM + r < it.L, it.seq_beg + it.q0 + u * BM + r, it.h, it.tp == 0, c0,
+                              wc, it.q0 + u * BM + r < it.L, it.seq_beg + it.q0 + u * BM + r, it.h, it.q0 < p.split_rows, c0,
                               &sm.o_free[w]);
             c0 += nk;
         }
@@ -993,7 +1005,7 @@ bool prefill_tc_supported(int D, int dtype) {
 }
 
 int prefill_tc_launch(const void* q, const void* k, const void* v, const int32_t* offsets, void* out, int B,
-                      int64_t n_tokens, int max_len, int H, int D, float scale, int dtype, int out_f32,
+                      int64_t n_tokens, int max_len, int H, int D, float scale, int dtype, int out_f32, int precise,
                       int32_t* err_flag, cudaStream_t st) {
     using namespace tc;
     if (D != HD) return ATTN_B200_ESHAPE;
@@ -1008,7 +1020,7 @@ int prefill_tc_launch(const void* q, const void* k, const void* v, const int32_t
     LaunchState* slot = nullptr;
     if ((rc = device_state(&d)) || (rc = take_launch_slot(d, st, &slot))) return rc;
     Params p{offsets, out, B, H, n_tokens, (max_len + 2 * BM - 1) / (2 * BM), scale * kLog2e, out_f32, err_flag,
-             &slot->abort};
+             &slot->abort, precise ? 0x7fffffff : 2 * BM};
     const int64_t row_bytes = (int64_t)H * HD * (out_f32 ? 4 : 2);
     zero_uncovered_rows_kernel<<<64, 256, 0, st>>>(out, offsets, B, n_tokens, max_len, row_bytes, err_flag);
     const int64_t n_items = (((int64_t)H * B + ITEM_GROUP - 1) / ITEM_GROUP) * ITEM_GROUP * p.n_qtiles;
@@ -1040,7 +1052,7 @@ int paged_prefill_tc_launch_impl(const void* q, const void* k_cache, const void*
     if ((rc = device_state(&d)) || (rc = take_launch_slot(d, st, &slot))) return rc;
     const int smem = (int)sizeof(SmemLayoutPg) + 1024;
     Params p{q_offsets, out, B, H, n_q_tokens, (max_q_len + 2 * BM - 1) / (2 * BM), scale * kLog2e, 0, err_flag,
-             &slot->abort};
+             &slot->abort, 2 * BM};
     PagedTcParams pg{slots, kv_offsets, q_offsets, k_cache, v_cache, Hkv, n_kv_tokens, n_slots};
     zero_uncovered_rows_kernel<<<64, 256, 0, st>>>(out, q_offsets, B, n_q_tokens, max_q_len, (int64_t)H * HD * 2, err_flag);
     if (p.n_qtiles == 0) return (int)cudaGetLastError();

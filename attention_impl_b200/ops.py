@@ -133,31 +133,13 @@ def decode_workspace_bytes(B: int, H: int, D: int, n_tokens: int, chunk: int) ->
     return lib.attn_b200_paged_decode_workspace_bytes(B, H, D, n_tokens, chunk)
 
 
-def decode_ticket_bytes(B: int, H: int) -> int:
-    """Size of the ticket area at the end of a decode workspace (zero before the first fused call)."""
-    return lib.attn_b200_paged_decode_ticket_bytes(B, H)
-
-
-def fused_decode_supported(q_dtype, H: int, Hkv: int, D: int, block_size: int = 1) -> bool:
-    """Whether the single-launch decode (``fused=True``) exists for this case."""
-    return (q_dtype in (torch.float16, torch.bfloat16) and H == Hkv and block_size == 1 and D in (64, 128, 256))
-
-
-def new_decode_workspace(B: int, H: int, D: int, n_tokens: int, chunk: int, device) -> torch.Tensor:
-    """A workspace ready for fused and two-launch calls alike (ticket area zeroed)."""
-    need = decode_workspace_bytes(B, H, D, n_tokens, chunk)
-    ws = torch.empty(need, dtype=torch.uint8, device=device)
-    ws[need - decode_ticket_bytes(B, H):].zero_()
-    return ws
-
-
 def paged_kv_attention_forward(Q, K, V, K_cache, V_cache, cache_indices, offsets, num_heads: int, *,
                                scale: Optional[float] = None, return_sp: bool = True,
                                chunk: Optional[int] = None, k_scale=None, v_scale=None,
                                max_context_len: Optional[int] = None, workspace: Optional[torch.Tensor] = None,
                                out: Optional[torch.Tensor] = None,
                                err_flag: Optional[torch.Tensor] = None, stages: int = 3,
-                               block_size: int = 1, fused: bool = False) -> List[torch.Tensor]:
+                               block_size: int = 1) -> List[torch.Tensor]:
     """KV-paged single-query attention, block_size = 1 (paged_attention_kernel.cu:237-294).
 
     Q, K, V ``[B, H*D]`` (the current token); K_cache, V_cache ``[slots, H*D]``; cache_indices
@@ -174,10 +156,6 @@ def paged_kv_attention_forward(Q, K, V, K_cache, V_cache, cache_indices, offsets
     D`` must divide ``num_heads``); query head h reads KV head ``h // (num_heads // Hkv)``.
     ``block_size > 1``: ``cache_indices`` is a block table int32 ``[B, max_blocks]`` and token t of
     sequence b lives in pool row ``cache_indices[b, t // block_size] * block_size + t % block_size``.
-    ``fused=True`` runs the step as ONE launch (the partial kernel's last CTA per sequence and head
-    group does the combine; see :func:`fused_decode_supported` for the cases it exists for).  A caller
-    ``workspace`` must then have its last :func:`decode_ticket_bytes` bytes zeroed once before the
-    first fused call (the kernel leaves them zero); S and P are not produced.
     """
     for t, n in ((Q, "Q"), (K, "K"), (V, "V"), (K_cache, "K_cache"), (V_cache, "V_cache")):
         _check_input(t, n)
@@ -220,17 +198,8 @@ def paged_kv_attention_forward(Q, K, V, K_cache, V_cache, cache_indices, offsets
         if chunk is None:
             chunk = pick_chunk(B, Hkv, D, T, dev, group=H // Hkv, kv_dtype=kvd)
         need = decode_workspace_bytes(B, H, D, T, chunk)
-        if fused:
-            if return_sp:
-                raise RuntimeError("fused=True does not produce S and P: pass return_sp=False")
-            if not fused_decode_supported(Q.dtype, H, Hkv, D, block_size):
-                raise RuntimeError("fused=True needs multi-head attention (Hkv == num_heads), block_size 1, "
-                                   "float16/bfloat16 queries and head_dim 64, 128 or 256")
-            stages = 4
         if workspace is None:
             workspace = torch.empty(need, dtype=torch.uint8, device=dev)
-            if fused:
-                workspace[need - decode_ticket_bytes(B, H):].zero_()
         elif workspace.numel() * workspace.element_size() < need:
             raise RuntimeError(f"workspace too small: {need} bytes needed")
         O = torch.empty_like(Q) if out is None else out
@@ -284,7 +253,7 @@ class _StepArena:
             self.dev[:end].copy_(self.host[:end], non_blocking=True)
 
 
-def _capture(device, call):
+def capture_graph(device, call):
     """Run ``call`` once on a side stream (module load, attribute set-up), then record it."""
     with torch.cuda.device(device):
         side = torch.cuda.Stream()
@@ -300,7 +269,7 @@ def _capture(device, call):
 
 class PagedDecodeGraph:
     """A paged decode step captured in a CUDA graph: one graph launch per step instead of kernel
-    launches plus the Python wrapper, which is what bounds small batches (a B=8 step is ~15 us of
+    launches plus the Python wrapper, which is what bounds small batches (a B=8 step is ~20 us of
     GPU work).  Not in the reference; it is how a serving loop would call this path.
 
     The kernels take sequence lengths from the device-side ``offsets`` and derive their grid from
@@ -312,12 +281,11 @@ class PagedDecodeGraph:
 
     ``head_dim`` must be given for grouped-query pools (``K_cache.size(1) == Hkv * head_dim`` with
     ``Hkv < num_heads``); it defaults to ``K_cache.size(1) // num_heads`` (multi-head attention).
-    Multi-head 16-bit steps are captured in the fused single-launch form unless ``fused=False``.
     """
 
     def __init__(self, K_cache, V_cache, batch: int, num_heads: int, max_tokens: int, *, dtype=None,
                  head_dim: Optional[int] = None, scale: Optional[float] = None, chunk: Optional[int] = None,
-                 k_scale=None, v_scale=None, fused: Optional[bool] = None):
+                 k_scale=None, v_scale=None):
         dev = K_cache.device
         dtype = dtype or (K_cache.dtype if K_cache.dtype in _DT else torch.float16)
         H = num_heads
@@ -340,12 +308,12 @@ class PagedDecodeGraph:
         self.out = torch.zeros(batch, H * D, dtype=dtype, device=dev)
         kvd = _kv_code(K_cache, self.q)
         self.chunk = chunk or pick_chunk(batch, Hkv, D, max_tokens, dev, group=H // Hkv, kv_dtype=kvd)
-        self.fused = fused_decode_supported(dtype, H, Hkv, D) if fused is None else fused
-        self.workspace = new_decode_workspace(batch, H, D, max_tokens, self.chunk, dev)
+        self.workspace = torch.empty(decode_workspace_bytes(batch, H, D, max_tokens, self.chunk), dtype=torch.uint8,
+                                     device=dev)
         kw = dict(scale=scale, return_sp=False, chunk=self.chunk, k_scale=k_scale, v_scale=v_scale,
-                  workspace=self.workspace, out=self.out, fused=self.fused)
+                  workspace=self.workspace, out=self.out)
         self._pools = (K_cache, V_cache)
-        self.graph = _capture(dev, lambda: paged_kv_attention_forward(
+        self.graph = capture_graph(dev, lambda: paged_kv_attention_forward(
             self.q, self.k, self.v, K_cache, V_cache, self.cache_indices, self.offsets, H, **kw))
 
     def upload(self, n_tokens: Optional[int] = None) -> None:
@@ -383,8 +351,7 @@ class DecodeStepGraph:
     """
 
     def __init__(self, K_cache, V_cache, cos, sin, batch: int, num_heads: int, head_dim: int, max_tokens: int, *,
-                 dtype=None, scale: Optional[float] = None, chunk: Optional[int] = None, k_scale=None, v_scale=None,
-                 fused: Optional[bool] = None):
+                 dtype=None, scale: Optional[float] = None, chunk: Optional[int] = None, k_scale=None, v_scale=None):
         dev = K_cache.device
         dtype = dtype or (K_cache.dtype if K_cache.dtype in _DT else torch.float16)
         H, D = num_heads, head_dim
@@ -404,8 +371,8 @@ class DecodeStepGraph:
         self.err_flag = torch.zeros(1, dtype=torch.int32, device=dev)
         kvd = _kv_code(K_cache, self.q)
         self.chunk = chunk or pick_chunk(batch, Hkv, D, max_tokens, dev, group=H // Hkv, kv_dtype=kvd)
-        self.fused = fused_decode_supported(dtype, H, Hkv, D) if fused is None else fused
-        self.workspace = new_decode_workspace(batch, H, D, max_tokens, self.chunk, dev)
+        self.workspace = torch.empty(decode_workspace_bytes(batch, H, D, max_tokens, self.chunk), dtype=torch.uint8,
+                                     device=dev)
         self._keep = (K_cache, V_cache, cos, sin, k_scale, v_scale)
         d = self.dev_in
 
@@ -415,13 +382,13 @@ class DecodeStepGraph:
             paged_kv_attention_forward(d["q"], d["k"], d["v"], K_cache, V_cache, d["cache_indices"], d["offsets"], H,
                                        scale=scale, return_sp=False, chunk=self.chunk, k_scale=k_scale,
                                        v_scale=v_scale, workspace=self.workspace, out=self.out,
-                                       err_flag=self.err_flag, fused=self.fused)
+                                       err_flag=self.err_flag)
 
-        # the warm-up run inside _capture executes a real step on whatever the arena holds (zeros:
+        # the warm-up run inside capture_graph executes a real step on whatever the arena holds (zeros:
         # position 0, slot 0, no cached tokens): the caller's first upload overwrites all of it, but
         # pool row 0 receives one bogus append, so put it back afterwards
         row0 = (K_cache[0].clone(), V_cache[0].clone())
-        self.graph = _capture(dev, step)
+        self.graph = capture_graph(dev, step)
         K_cache[0].copy_(row0[0])
         V_cache[0].copy_(row0[1])
         self.err_flag.zero_()
@@ -649,7 +616,7 @@ def kv_attention_forward(Q, K, V, K_cache, V_cache, num_heads: int, *, scale: fl
 def paged_attention_forward(Q, K, V, offsets, num_heads: int, *, scale: Optional[float] = None,
                             return_sp: bool = True, max_seqlen: Optional[int] = None,
                             out_dtype: Optional[torch.dtype] = None, force_generic: bool = False,
-                            err_flag: Optional[torch.Tensor] = None) -> List[torch.Tensor]:
+                            err_flag: Optional[torch.Tensor] = None, precise: bool = False) -> List[torch.Tensor]:
     """Causal attention over a packed ``[sum L, H*D]`` token buffer (paged_attention_kernel.cu:189-235).
 
     ``offsets`` int32 ``[B]`` are inclusive cumulative lengths.  Returns ``[S, P, O]``; S, P are
@@ -657,6 +624,9 @@ def paged_attention_forward(Q, K, V, offsets, num_heads: int, *, scale: Optional
     (empty placeholders; required for the tensor-core path and for any large input).
     ``out_dtype=torch.float32`` makes the tensor-core path store fp32 output.  ``err_flag`` (int32
     device scalar) receives ATTN_B200_FLAG_* bits (bad offsets, an in-kernel wait that ran out).
+    ``precise=True`` (tensor-core path) carries P into P·V as two terms on every row, not only on a
+    sequence's first 256 rows: bfloat16 inputs then stay within 2e-3 of exact arithmetic everywhere
+    (3.4e-3 otherwise), for about a quarter more time.
     """
     for t, n in ((Q, "Q"), (K, "K"), (V, "V")):
         _check_input(t, n)
@@ -692,7 +662,8 @@ def paged_attention_forward(Q, K, V, offsets, num_heads: int, *, scale: Optional
         check(lib.attn_b200_varlen_prefill(
             Q.data_ptr(), K.data_ptr(), V.data_ptr(), offsets.data_ptr(), O.data_ptr(),
             S.data_ptr() if return_sp else None, P.data_ptr() if return_sp else None, B, n_tokens, max_seqlen, H, D,
-            float(scale), dt, int(out_f32), int(force_generic), _ptr(err_flag), _stream()), "paged_attention_forward")
+            float(scale), dt, int(out_f32) | (2 if precise else 0), int(force_generic), _ptr(err_flag), _stream()),
+            "paged_attention_forward")
     return [S, P, O]
 
 

@@ -114,18 +114,12 @@ ATTN_B200_API int attn_b200_rope_write_kv(void* q, void* k, const void* v, const
  * global grid; each (chunk, head) is reduced by one warp into an (m, l, o) partial in
  * `workspace`, then attn_b200_lse_combine-style reduction folds the partials and the new token.
  * `chunk` must be a multiple of 32 in [32, 2048]; use attn_b200_paged_decode_pick_chunk.
- * `workspace` needs attn_b200_paged_decode_workspace_bytes(...) bytes, 16-byte aligned.  Its last
- * attn_b200_paged_decode_ticket_bytes(B, H) bytes are the ticket counters of the fused form
- * (`stages` = 4), the only part that carries a requirement: zero before the first fused call; every
- * fused call leaves them zero again.  The rest needs no initialisation and holds nothing between calls.
+ * `workspace` needs attn_b200_paged_decode_workspace_bytes(...) bytes, 16-byte aligned; it needs
+ * no initialisation and holds nothing between calls.
  * `stages`: 3 runs both kernels (the normal call); 1 runs only the partial kernel, 2 only the
- * combine kernel (same arguments) so that a profiler or benchmark can put events between them;
- * 4 is the fused single launch: each CTA of the partial kernel publishes its rows and takes a
- * ticket, and the CTA that draws a (sequence, head group)'s last ticket folds that group's rows
- * and the new token and writes `out` (nobody waits for anybody).  It exists for multi-head
- * attention (n_kv_heads == H) with a per-token table (block_size == 1), 16-bit q, head_dim 64 /
- * 128 / 256 and S == NULL; anything else returns ATTN_B200_ESHAPE.  It pays when the step is a
- * few microseconds long (small batches), where the second launch is a third of the step.
+ * combine kernel (same arguments) so that a profiler or benchmark can put events between them.
+ * The combine kernel is launched as a programmatic dependent of the partial kernel (its launch and
+ * prologue overlap that kernel's tail; it waits for the partial rows itself).
  * Extensions beyond the reference (which is multi-head, block_size = 1):
  *   n_kv_heads  KV heads (H % n_kv_heads == 0); k_new, v_new, k_cache, v_cache then have n_kv_heads*D
  *               columns and query head h reads KV head h / (H / n_kv_heads).  Pass H for MHA.
@@ -142,8 +136,6 @@ ATTN_B200_API int attn_b200_paged_decode(const void* q, const void* k_new, const
                            int32_t* err_flag, void* stream);
 
 ATTN_B200_API size_t attn_b200_paged_decode_workspace_bytes(int B, int H, int D, int64_t n_tokens, int chunk);
-/* Size of the ticket area at the END of the workspace (see `stages` = 4). */
-ATTN_B200_API size_t attn_b200_paged_decode_ticket_bytes(int B, int H);
 /* Heuristic chunk length: enough (chunk, head-group) work items to fill `sm_count` SMs. */
 ATTN_B200_API int attn_b200_paged_decode_pick_chunk(int B, int H, int D, int64_t n_tokens, int sm_count);
 /* The same for grouped-query heads: `group` query heads per KV head, `kv_dtype` of the pools.  Groups
@@ -249,12 +241,19 @@ ATTN_B200_API int attn_b200_paged_decode_static_scratch(
  *   max_len >= longest sequence (sizes the grid; rows beyond a sequence's end are skipped).
  *   S, P optional [B, H, max_len, max_len] (dtype) — both or neither; only the generic path
  *   writes them.  Key j is visible to query i of the same sequence iff j <= i.
- * dtype F16/BF16 with D == 128 and S == NULL runs the tcgen05 tensor-core kernel (`out_f32`
- * != 0 stores fp32 output instead of dtype); everything else runs the generic kernel.
+ * dtype F16/BF16 with D == 128 and S == NULL runs the tcgen05 tensor-core kernel; everything else
+ * runs the generic kernel.  `out_flags` (tensor-core kernel only): ATTN_B200_PREFILL_OUT_F32 stores
+ * fp32 output instead of dtype; ATTN_B200_PREFILL_PRECISE_P carries the probabilities into P*V as two
+ * terms of the input type on EVERY row instead of only on a sequence's first 256 rows: bf16 inputs
+ * then stay within 2e-3 max-abs of exact arithmetic everywhere (3.4e-3 without it, from the 2^-9
+ * rounding of one dominant probability), for about a quarter more time.
+ * A sequence longer than max_len raises ATTN_B200_FLAG_BAD_OFFSETS; rows that no tile covers (past
+ * offsets[B-1], or beyond max_len rounded up to 256) are written as zeros by the tensor-core path.
  */
+enum { ATTN_B200_PREFILL_OUT_F32 = 1, ATTN_B200_PREFILL_PRECISE_P = 2 };
 ATTN_B200_API int attn_b200_varlen_prefill(const void* q, const void* k, const void* v, const int32_t* offsets, void* out,
                              void* S, void* P, int B, int64_t n_tokens, int max_len, int H, int D,
-                             float scale, int dtype, int out_f32, int force_generic, int32_t* err_flag,
+                             float scale, int dtype, int out_flags, int force_generic, int32_t* err_flag,
                              void* stream);
 
 /* Chunked / prefix-cached prefill through the slot table (no counterpart in the reference: it is

@@ -1,5 +1,5 @@
-"""GPU: the single-launch (fused combine) decode, the software-pipelined multi-head kernel behind
-short units, the captured decode steps, and the host-staged decoder with a prefetched slot table.
+"""GPU: captured decode steps (grouped-query pools; RoPE -> cache append -> attention -> combine in
+one graph), the host-staged decoder with a prefetched slot table, and the e4m3 path at long context.
 
 Every case goes through the drop-in modules / the C ABI and is compared with the CPU oracle
 (fp16: <= 2e-3 max-abs against the fp32-evaluated oracle; bf16: its output rounding added; e4m3
@@ -16,111 +16,6 @@ pytestmark = pytest.mark.gpu
 TOL16 = 2e-3
 
 
-def _fused(inp, H, chunk, **kw):
-    import attention_impl_b200 as A
-    Q, K, V, Kc, Vc, ci, off = [t.cuda() for t in inp]
-    _, _, O = A.paged_kv_attention_forward(Q, K, V, Kc, Vc, ci, off, H, return_sp=False, chunk=chunk, fused=True, **kw)
-    torch.cuda.synchronize()
-    return O.cpu()
-
-
-@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
-@pytest.mark.parametrize("H,D", [(32, 128), (3, 128), (24, 128), (8, 64), (5, 64), (4, 256), (1, 256)])
-@pytest.mark.parametrize("chunk", [32, 64, 256])
-def test_fused_decode_ragged(dtype, H, D, chunk):
-    """Ragged lengths incl. empty sequences (first, middle, last, adjacent), chunk-boundary lengths,
-    head counts that leave warps of the last head group without heads; chunks on both sides of the
-    pipelined / plain kernel split."""
-    lens = [0, 1, 31, 32, 33, 64, 0, 0, 100, 257, 5, 96, 0]
-    inp = decode_inputs(len(lens), H, D, lens, 1024, dtype, seed=H * 100 + D + chunk)
-    O = _fused(inp, H, chunk)
-    _, _, O32 = orc.paged_decode(*inp, H, compute_dtype=torch.float32)
-    tol = TOL16 if dtype == torch.float16 else 1.6e-2
-    assert torch.isfinite(O).all()
-    assert (O.float() - O32.float()).abs().max() <= tol
-
-
-def test_fused_decode_small_batch_workload_matches_two_launch_form():
-    """B=8, H=32, D=128, ctx ~ U[128,1024]: fused against the oracle and against the two-kernel form."""
-    import attention_impl_b200 as A
-    B, H, D = 8, 32, 128
-    lens = uniform_lens(B, 128, 1024, seed=1)
-    inp = decode_inputs(B, H, D, lens, 16384, torch.float16, seed=1001)
-    O = _fused(inp, H, None)
-    _, _, O32 = orc.paged_decode(*inp, H, compute_dtype=torch.float32)
-    assert (O.float() - O32.float()).abs().max() <= TOL16
-    _, _, O2 = A.paged_kv_attention_forward(*[t.cuda() for t in inp], H, return_sp=False)
-    assert (O.float() - O2.cpu().float()).abs().max() <= 5e-4     # same partial rows, other summation order
-
-
-def test_fused_decode_leaves_its_tickets_clean():
-    """One workspace, three fused calls with different batches: the ticket area must be zero after
-    every call (each call's last CTAs reset what they counted)."""
-    import attention_impl_b200 as A
-    B, H, D, cap = 6, 16, 128, 4096
-    chunk = 32
-    ws = A.ops.new_decode_workspace(B, H, D, cap, chunk, "cuda")
-    tail = A.ops.decode_ticket_bytes(B, H)
-    for seed in (3, 4, 5):
-        lens = uniform_lens(B, 0, 600, seed=seed)
-        Q, K, V, Kc, Vc, ci, off = decode_inputs(B, H, D, lens, 8192, torch.float16, seed=seed)
-        ci_cap = torch.zeros(cap, dtype=torch.int32)
-        ci_cap[: ci.numel()] = ci
-        _, _, O = A.paged_kv_attention_forward(Q.cuda(), K.cuda(), V.cuda(), Kc.cuda(), Vc.cuda(), ci_cap.cuda(),
-                                               off.cuda(), H, return_sp=False, chunk=chunk, workspace=ws, fused=True)
-        torch.cuda.synchronize()
-        assert int(ws[-tail:].view(torch.int32).abs().sum().item()) == 0
-        _, _, O32 = orc.paged_decode(Q, K, V, Kc, Vc, ci, off, H, compute_dtype=torch.float32)
-        assert (O.cpu().float() - O32.float()).abs().max() <= TOL16
-
-
-def test_fused_decode_fp8_kv():
-    B, H, D = 6, 8, 128
-    lens = uniform_lens(B, 0, 2000, seed=11)
-    Q, K, V, Kc, Vc, ci, off = decode_inputs(B, H, D, lens, 16384, torch.float16, seed=12)
-    K8, ks = orc.quantize_e4m3_per_head(Kc, H)
-    V8, vs = orc.quantize_e4m3_per_head(Vc, H)
-    Kd, Vd = orc.dequantize_e4m3_per_head(K8, ks, H), orc.dequantize_e4m3_per_head(V8, vs, H)
-    _, _, Oref = orc.paged_decode(Q.float(), K.float(), V.float(), Kd, Vd, ci, off, H)
-    for chunk in (32, 512):
-        O = _fused((Q, K, V, K8, V8, ci, off), H, chunk, k_scale=ks.cuda(), v_scale=vs.cuda())
-        assert (O.float() - Oref).norm() / Oref.norm() <= 2e-2
-        assert (O.float() - Oref).abs().max() <= 2e-2 * Oref.abs().max()
-
-
-def test_fused_decode_rejects_what_it_does_not_cover():
-    import attention_impl_b200 as A
-    lens = [5, 9]
-    Q, K, V, Kc, Vc, ci, off = [t.cuda() for t in decode_inputs(2, 8, 128, lens, 64, torch.float16, seed=1)]
-    with pytest.raises(RuntimeError, match="fused=True"):
-        A.paged_kv_attention_forward(Q, K, V, Kc, Vc, ci, off, 8, fused=True)                    # S and P requested
-    with pytest.raises(RuntimeError, match="fused=True"):
-        A.paged_kv_attention_forward(Q.float(), K.float(), V.float(), Kc.float(), Vc.float(), ci, off, 8,
-                                     return_sp=False, fused=True)                               # fp32
-    # straight through the C ABI: grouped-query pools with stages = 4
-    from attention_impl_b200 import _lib
-    ws = A.ops.new_decode_workspace(2, 8, 128, 14, 32, "cuda")
-    rc = _lib.lib.attn_b200_paged_decode(Q.data_ptr(), K.data_ptr(), V.data_ptr(), Kc.data_ptr(), Vc.data_ptr(),
-                                         ci.data_ptr(), off.data_ptr(), Q.data_ptr(), ws.data_ptr(), ws.numel(), None,
-                                         None, 0, 2, 8, 4, 128, 14, 64, 0, 1, 0, 32, 1.0, None, None, _lib.F16, _lib.F16,
-                                         4, None, None)
-    assert rc == -3
-
-
-@pytest.mark.parametrize("chunk", [32, 64, 128])
-def test_pipelined_kernel_with_scores_and_probabilities(chunk):
-    """The two-launch form with S and P requested also runs the pipelined kernel on short units."""
-    import lm_ops
-    lens = [0, 3, 4, 5, 36, 131, 260]
-    B, H, D = len(lens), 8, 128
-    inp = decode_inputs(B, H, D, lens, 1024, torch.float16, seed=chunk)
-    S, P, O = lm_ops.paged_kv_attention_forward(*[t.cuda() for t in inp], H, chunk=chunk)
-    S32, P32, O32 = orc.paged_decode(*inp, H, compute_dtype=torch.float32)
-    assert (O.cpu().float() - O32.float()).abs().max() <= TOL16
-    assert (S.cpu() - S32).abs().max() < 3e-3
-    assert (P.cpu() - P32).abs().max() < 2e-4
-
-
 def test_decode_graph_grouped_query_pools():
     """A captured step over pools with fewer KV heads than query heads (head_dim given explicitly)."""
     import attention_impl_b200 as A
@@ -128,7 +23,7 @@ def test_decode_graph_grouped_query_pools():
     g = torch.Generator().manual_seed(5)
     Kc, Vc = (torch.randn(8192, Hkv * D, generator=g).half().cuda() for _ in range(2))
     graph = A.PagedDecodeGraph(Kc, Vc, B, H, cap, head_dim=D)
-    assert graph.q.shape == (B, H * D) and graph.k.shape == (B, Hkv * D) and not graph.fused
+    assert graph.q.shape == (B, H * D) and graph.k.shape == (B, Hkv * D)
     for seed in (1, 2):
         lens = uniform_lens(B, 1, 900, seed=seed)
         gg = torch.Generator().manual_seed(seed)

@@ -1,10 +1,12 @@
 """GPU: tensor-core (tcgen05) packed causal prefill vs the CPU oracle.
 
-Tolerances.  With fp32 output the kernel is within 2e-3 max-abs of the fp32-evaluated oracle for
-fp16 AND bf16 inputs.  P is rounded to the input type before P·V (2^-12 per probability for fp16,
-2^-9 for bf16); over many keys that averages out, and the first 256 rows of every sequence, which
-see few keys, carry P as two terms (hi + lo).  A bf16 OUTPUT adds its own rounding (half an ulp is
-3.9e-3 at |O| >= 1), so bf16-out is held to 2 bf16 ulp (1.6e-2 at |O| < 2).
+Tolerances (max-abs against the fp32-evaluated oracle, fp32 output).  P is rounded to the input type
+before P·V: 2^-12 per probability for fp16, 2^-9 for bf16.  Over many keys that averages out, and
+the first 256 rows of every sequence, which see few keys, carry P as two terms (hi + lo).  Both
+input types: <= 2e-3 (measured: 1.6e-3 for bf16 at the workload's lengths, where what is left is the
+rounding of a dominant probability, p ~ 0.2 times 2^-9 times |v|; 1e-4 for fp16); with
+``precise=True`` (two terms on every row) both are below 1e-4.  A bf16 OUTPUT adds its own rounding (half an ulp is 3.9e-3 at |O| >= 1), so bf16-out is held
+to 2 bf16 ulp (1.6e-2 at |O| < 2).
 """
 import pytest
 import torch
@@ -13,6 +15,8 @@ from oracle import attention_oracle as orc
 from helpers import prefill_inputs
 
 pytestmark = pytest.mark.gpu
+
+TOL = {torch.float16: 2e-3, torch.bfloat16: 2e-3}     # fp32 output, default (two-term P on the first 256 rows only)
 
 
 def _run(Q, K, V, off, H, **kw):
@@ -32,10 +36,12 @@ def test_prefill_tc_fp32_out_vs_fp32_oracle(dtype, lens):
     O = _run(Q, K, V, off, H, out_dtype=torch.float32)
     assert O.dtype == torch.float32
     O32 = orc.packed_prefill(Q, K, V, off, H, compute_dtype=torch.float32, out_dtype=torch.float32)
-    tol = 2e-3
+    tol = TOL[dtype]
     assert (O - O32).abs().max() <= tol
     # typical error is far below the bound
-    assert (O - O32).abs().mean() <= tol / 10
+    assert (O - O32).abs().mean() <= tol / 20
+    Op = _run(Q, K, V, off, H, out_dtype=torch.float32, precise=True)
+    assert (Op - O32).abs().max() <= 2e-4
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
@@ -60,7 +66,9 @@ def test_prefill_tc_many_heads_and_sequences():
     Q, K, V, off = prefill_inputs(lens, H, 128, torch.bfloat16, seed=11)
     O = _run(Q, K, V, off, H, out_dtype=torch.float32)
     O32 = orc.packed_prefill(Q, K, V, off, H, compute_dtype=torch.float32, out_dtype=torch.float32)
-    assert (O - O32).abs().max() <= 2e-3
+    assert (O - O32).abs().max() <= TOL[torch.bfloat16]
+    Op = _run(Q, K, V, off, H, out_dtype=torch.float32, precise=True)
+    assert (Op - O32).abs().max() <= 2e-4
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
@@ -73,8 +81,10 @@ def test_prefill_tc_workload_sized_sequences_vs_oracle(dtype):
     O = _run(Q, K, V, off, H, out_dtype=torch.float32)
     O32 = orc.packed_prefill(Q, K, V, off, H, compute_dtype=torch.float32, out_dtype=torch.float32)
     err = (O - O32).abs()
-    assert err.max() <= 2e-3
-    assert torch.quantile(err.flatten()[:: 7], 0.999) <= 5e-4 and err.mean() <= 1e-4
+    assert err.max() <= TOL[dtype]
+    assert torch.quantile(err.flatten()[:: 7], 0.999) <= 6e-4 and err.mean() <= 1e-4
+    Op = _run(Q, K, V, off, H, out_dtype=torch.float32, precise=True)
+    assert (Op - O32).abs().max() <= 2e-4
 
 
 def test_prefill_tc_understated_max_seqlen_is_flagged_and_rows_are_zero():
