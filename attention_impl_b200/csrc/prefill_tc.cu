@@ -73,17 +73,38 @@ struct Params {
 // on every row (split_rows = INT_MAX: half as many P.V MMAs again and a second pass over P).
 constexpr int THREADS2 = 384;   // 3 warpgroups: softmax 0, softmax 1, {TMA, MMA, 2 idle warps}
 
+// Staged read-out of an output tile (16-bit output, all 128 rows of the tile inside the sequence):
+// the warpgroup packs its rows into a private 16 KB shared-memory buffer in the 128-byte-swizzled
+// layout of a [128 rows x 64 columns] TMA box and one thread stores the box with
+// cp.async.bulk.tensor (two boxes per tile).  Written straight from registers, every 16-byte store
+// instruction of a warp touches 32 different rows, 8 KB apart: 32 sectors per instruction, about two
+// thousand LSU clocks per tile, as long as a whole key-tile step; staged, it is a few hundred.
+struct OutStage {
+    unsigned char* buf;          // 16 KB, 1024-byte aligned, private to the warpgroup
+    const CUtensorMap* map;      // output tensor [n_tokens, H*128], box 64 x 128, 128-byte swizzle
+    int row0;                    // first row of the tile in the packed buffer
+    int bar_id;                  // named barrier of the warpgroup (128 threads)
+};
+
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* src, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
+                 ::"l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(src)) : "memory");
+}
+__device__ __forceinline__ void named_bar_sync(int id, int n_threads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(n_threads) : "memory");
+}
+
 // One softmax thread = one query row (TMEM lane) of a 128-row tile: walks the key tiles, turns S into
 // P in place, keeps the running maximum lazily, and writes the normalised output row at the end.
 // `qpos` is the row's position in key coordinates (keys 0..qpos are visible): its index within the
 // sequence for the packed prefill, kv_len - q_len + index for a chunk over a cached prefix.
-template <typename T, int kPolyOf8>
+template <typename T, int kPolyOf8, bool kStaged>
 __device__ __forceinline__ void softmax_row(unsigned long long* s_full, unsigned long long* p_half,
                                             unsigned long long* p_full,
                                             unsigned long long* o_full, uint32_t s_addr, uint32_t o_addr, int nk,
                                             int qpos, int r, const Params& p, AbortBox* wc,
                                             bool row_valid, int64_t out_row, int h, bool split, int c0 = 0,
-                                            unsigned long long* o_free = nullptr) {
+                                            unsigned long long* o_free = nullptr, const OutStage* stage = nullptr) {
     // c0: tiles this warpgroup has processed before this call (persistent kernels keep their
     // barriers across work items, so the phase of tile j is (c0 + j) & 1); o_free, if given, is
     // signalled once the accumulator has been read out and may be overwritten by the next item.
@@ -217,6 +238,38 @@ __device__ __forceinline__ void softmax_row(unsigned long long* s_full, unsigned
             const bool valid = row_valid;
             const float inv = 1.f / l;
             const int64_t row = out_row;
+            if (kStaged && stage->buf) {
+                // whole tile inside the sequence, 16-bit output: through shared memory and TMA
+                float ov[HD];
+#pragma unroll
+                for (int c = 0; c < 4; ++c) tmem_ld32_nowait(o_addr + c * 32, ov + c * 32);
+                tmem_ld_wait();
+                if (o_free) {                  // the accumulator is in registers: the next item may overwrite it
+                    tc_fence_before();
+                    mbar_arrive(o_free);
+                }
+                const uint32_t sbase = smem_u32(stage->buf) + (uint32_t)r * 128u;
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) {              // 16-byte chunk c of this row's 64 columns
+                        const float* o8 = ov + half * 64 + c * 8;
+                        const uint32_t dst = sbase + (uint32_t)((c ^ (r & 7)) << 4);
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst),
+                                     "r"(pack2<T>(o8[0] * inv, o8[1] * inv)), "r"(pack2<T>(o8[2] * inv, o8[3] * inv)),
+                                     "r"(pack2<T>(o8[4] * inv, o8[5] * inv)), "r"(pack2<T>(o8[6] * inv, o8[7] * inv))
+                                     : "memory");
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    named_bar_sync(stage->bar_id, 128);
+                    if (r == 0) {
+                        tma_store_2d(stage->map, stage->buf, h * HD + half * 64, stage->row0);
+                        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");     // the buffer has been read
+                    }
+                    named_bar_sync(stage->bar_id, 128);
+                }
+            } else {
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 float ov[32];
@@ -240,6 +293,7 @@ __device__ __forceinline__ void softmax_row(unsigned long long* s_full, unsigned
                                             pack2<T>(ov[8 * i + 4] * inv, ov[8 * i + 5] * inv),
                                             pack2<T>(ov[8 * i + 6] * inv, ov[8 * i + 7] * inv));
                 }
+            }
             }
         }
         }
@@ -282,6 +336,7 @@ struct SmemLayout2p {
     alignas(1024) unsigned char q[2][TILE_BYTES];
     alignas(1024) unsigned char k[STAGES][TILE_BYTES];
     alignas(1024) unsigned char v[STAGES][TILE_BYTES];
+    alignas(1024) unsigned char o_stage[2][SUB_BYTES];     // output staging, one [128 x 64] box per warpgroup
     alignas(8) unsigned long long q_full[2], q_empty[2];
     // item_id[n & 3] = n-th item of this CTA (-1: no more work), published by the producer.  The
     // producer draws item n only after it has issued every K/V tile of item n-1, which needs both
@@ -335,8 +390,8 @@ __device__ __forceinline__ int upper_of(int w, int n) { return (w ^ n) & 1; }
 template <typename T>
 __global__ void __launch_bounds__(THREADS2, 1)
 prefill_tc2p_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                    const __grid_constant__ CUtensorMap map_v, const Params p, const int64_t n_items,
-                    unsigned long long* work_counter) {
+                    const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o,
+                    const Params p, const int64_t n_items, unsigned long long* work_counter) {
     extern __shared__ unsigned char smem_raw[];
     SmemLayout2p& sm = *reinterpret_cast<SmemLayout2p*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
@@ -573,9 +628,12 @@ prefill_tc2p_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             const int nk = u ? it.n1 : it.n0;
             if (nk == 0) continue;
             const int tq = 2 * it.tp + u;
-            softmax_row<T, 2>(&sm.s_full[w], &sm.p_half[w], &sm.p_full[w], &sm.o_full[w], s_addr, o_addr, nk, tq * BM + r, r, p,
+            // staged read-out when the tile lies wholly inside the sequence and the output is 16-bit
+            const bool whole = it.q0 + u * BM + BM <= it.L && !p.out_f32;
+            const OutStage stage{whole ? sm.o_stage[w] : nullptr, &map_o, (int)(it.seq_beg + it.q0 + u * BM), 1 + w};
+            softmax_row<T, 2, true>(&sm.s_full[w], &sm.p_half[w], &sm.p_full[w], &sm.o_full[w], s_addr, o_addr, nk, tq * BM + r, r, p,
                               wc, it.q0 + u * BM + r < it.L, it.seq_beg + it.q0 + u * BM + r, it.h, it.q0 < p.split_rows, c0,
-                              &sm.o_free[w]);
+                              &sm.o_free[w], &stage);
             c0 += nk;
         }
     }
@@ -860,7 +918,7 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const Params 
         const int nk = w ? n1 : n0;
         const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
         const int qi = q0 + w * BM + r;                    // row within the chunk
-        softmax_row<T, 0>(&sm.s_full[w], &sm.p_half[w], &sm.p_full[w], &sm.o_full[w], lane_base + w * 128, lane_base + 256 + w * 128,
+        softmax_row<T, 0, false>(&sm.s_full[w], &sm.p_half[w], &sm.p_full[w], &sm.o_full[w], lane_base + w * 128, lane_base + 256 + w * 128,
                        nk, shift + qi, r, p, wc, qi < q_len, q_beg + qi, h, split);
     }
     // ---------------------------------------------------------------------- teardown
@@ -1011,11 +1069,14 @@ int prefill_tc_launch(const void* q, const void* k, const void* v, const int32_t
     if (D != HD) return ATTN_B200_ESHAPE;
     if (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)out) % 16) return ATTN_B200_EINVAL;
     if (n_tokens > 0x7fffffffLL || B > 65535 || H > 65535) return ATTN_B200_ETOOLARGE;
-    CUtensorMap mq, mk, mv;
+    CUtensorMap mq, mk, mv, mo;
     int rc;
     if ((rc = make_map(&mq, q, n_tokens, H, dtype)) || (rc = make_map(&mk, k, n_tokens, H, dtype)) ||
         (rc = make_map(&mv, v, n_tokens, H, dtype)))
         return rc;
+    // the staged read-out stores 16-bit tiles through this map (fp32 output takes the direct path:
+    // the map then describes the buffer as if it were 16-bit and is never used)
+    if ((rc = make_map(&mo, out, n_tokens, H, dtype))) return rc;
     DeviceState d;
     LaunchState* slot = nullptr;
     if ((rc = device_state(&d)) || (rc = take_launch_slot(d, st, &slot))) return rc;
@@ -1028,9 +1089,9 @@ int prefill_tc_launch(const void* q, const void* k, const void* v, const int32_t
     const int smem_p = (int)sizeof(SmemLayout2p) + 1024;
     const unsigned ctas = (unsigned)(n_items < d.n_sm ? n_items : d.n_sm);
     if (dtype == ATTN_B200_BF16)
-        prefill_tc2p_kernel<__nv_bfloat16><<<ctas, THREADS2, smem_p, st>>>(mq, mk, mv, p, n_items, &slot->work);
+        prefill_tc2p_kernel<__nv_bfloat16><<<ctas, THREADS2, smem_p, st>>>(mq, mk, mv, mo, p, n_items, &slot->work);
     else
-        prefill_tc2p_kernel<__half><<<ctas, THREADS2, smem_p, st>>>(mq, mk, mv, p, n_items, &slot->work);
+        prefill_tc2p_kernel<__half><<<ctas, THREADS2, smem_p, st>>>(mq, mk, mv, mo, p, n_items, &slot->work);
     return (int)cudaGetLastError();
 }
 

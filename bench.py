@@ -280,6 +280,27 @@ class LargeDecode(Workload):
 
     E2E_NOTE = "slot table of step s+1 uploaded during step s (double-buffered); q/k/v in, O out on the critical path"
 
+    def extra_multi_gpu(self, fence, max_over_ranks):
+        """Head sharding needs no collective for the attention itself; a caller that wants every rank
+        to hold all heads of O adds one all-gather of [B, (H/N)*D] per rank.  Timed apart from the step."""
+        import torch.distributed as dist
+        if self.world == 1:
+            return None
+        full = torch.empty(self.world * self.O.size(0), self.O.size(1), dtype=self.O.dtype, device=self.dev)
+        for _ in range(3):
+            dist.all_gather_into_tensor(full, self.O)
+        fence()
+        n = 20
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            dist.all_gather_into_tensor(full, self.O)
+        e1.record()
+        fence()
+        return {"o_all_gather_ms": max_over_ranks(e0.elapsed_time(e1)) / n,
+                "bytes_per_rank": self.O.numel() * self.O.element_size(),
+                "note": "optional NCCL all-gather of O (rank-major head slices), not part of the timed step"}
+
     def units_per_step_rank(self):
         return 2.0 * self.T * self.Hl * self.D * self.kv_bytes_el
 
@@ -1274,6 +1295,10 @@ def run_b200(args, W):
         "dtype": W.dtype, "data": "synthetic", "tokens_per_s": m["tokens_per_s"], "config": w.config(),
         "roofline": m["roofline"], "e2e": m["e2e"], "gpu_launches": m["gpu_launches"], "clocks": m["clocks"],
     }
+    if world > 1 and hasattr(w, "extra_multi_gpu"):
+        x = w.extra_multi_gpu(fence, max_over_ranks)
+        if x:
+            line["o_all_gather"] = x
     # CPU leg: rank 0 at N = 1; workloads whose sample is spread over the ranks run it collectively
     if not args.no_cpu and (world == 1 or getattr(w, "collective_cpu_leg", False)):
         cb, par = w.cpu_baseline()
