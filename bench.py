@@ -1045,6 +1045,33 @@ class Fp8Split(Workload):
 
     collective_cpu_leg = True      # cpu_baseline() is called on every rank (it gathers one sequence to rank 0)
 
+    def extra_multi_gpu(self, fence, max_over_ranks):
+        """Every step of the KV split ends with an exchange, so the ranks run in lock step and a step
+        lasts as long as the slowest rank's local work.  This times the local part alone (partial
+        kernel + local combine, no exchange) on every rank and reports the spread."""
+        import torch.distributed as dist
+        if self.world == 1:
+            return None
+        call = lambda: self.A.paged_decode_partial(self.Q, self.Kc, self.Vc, self.ci, self.off, self.H,
+                                                   k_scale=self.ks, v_scale=self.vs, chunk=self.chunk)
+        for _ in range(3):
+            call()
+        fence()
+        n = 10
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            call()
+        e1.record()
+        fence()
+        mine = torch.tensor([e0.elapsed_time(e1) / n], device=self.dev)
+        allms = [torch.zeros_like(mine) for _ in range(self.world)]
+        dist.all_gather(allms, mine)
+        ms = [round(float(x), 4) for x in allms]
+        return {"local_ms_per_rank": ms, "local_ms_min": min(ms), "local_ms_max": max(ms),
+                "note": "partial kernel + local combine only, no exchange; the lock-stepped step cannot be "
+                        "shorter than local_ms_max"}
+
     def cpu_baseline(self):
         """The shortest sequence of the batch, whole (>= 32768 tokens): its e4m3 rows are collected
         from every rank's pool in token order on rank 0, dequantised on the host with the per-head
@@ -1298,7 +1325,7 @@ def run_b200(args, W):
     if world > 1 and hasattr(w, "extra_multi_gpu"):
         x = w.extra_multi_gpu(fence, max_over_ranks)
         if x:
-            line["o_all_gather"] = x
+            line["o_all_gather" if "o_all_gather_ms" in x else "rank_skew"] = x
     # CPU leg: rank 0 at N = 1; workloads whose sample is spread over the ranks run it collectively
     if not args.no_cpu and (world == 1 or getattr(w, "collective_cpu_leg", False)):
         cb, par = w.cpu_baseline()
