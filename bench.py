@@ -53,9 +53,9 @@ NOMINAL_BF16_TFLOPS = 2250.0      # dense bf16
 
 # dram__bytes_read.sum + dram__bytes_write.sum per algorithmic byte of the decode partial kernel, from
 # the ncu capture of a 5.3 GB case of the large_decode workload
-# (profiles/paged_decode_fast_kernel_small_case_ncu.md); every row is read once, so traffic grows in
-# proportion to the tokens processed.
-DECODE_TRAFFIC_RATIO = 1.0017
+# (profiles/paged_decode_mha_kernel_small_case_ncu.md); every row is read once, so the reads grow in
+# proportion to the tokens processed (the partial-row writes grow with tokens / chunk: an upper bound).
+DECODE_TRAFFIC_RATIO = 1.0023
 
 
 def measured_peaks():
@@ -311,7 +311,7 @@ class LargeDecode(Workload):
         return 2
 
     def kernel_name(self):
-        return "paged_decode_mha_kernel<half,half,128,heads-per-warp>"
+        return "paged_decode_mha_kernel<half,half,128>"
 
     def traffic(self):
         return DECODE_TRAFFIC_RATIO * self.units_per_step_rank()
@@ -1026,7 +1026,7 @@ class Fp8Split(Workload):
         return 3 + (1 if self.world > 1 else 0)     # partial, local combine, (all-gather), final combine
 
     def kernel_name(self):
-        return "paged_decode_mha_kernel<half,e4m3,128,heads-per-warp>"
+        return "paged_decode_mha_kernel<half,e4m3,128>"
 
     def static_config(self):
         return {"workload": "long_context_fp8_kv_paged_decode", "batch": self.args.batch or self.B, "heads": self.H,
