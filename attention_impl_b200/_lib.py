@@ -30,6 +30,7 @@ PROTOTYPES = {
                                       _i32, _i32, _i32, _i32, _i64, _i64, _i32, _i32, _i32, _i32, _f32, _vp, _vp,
                                       _i32, _i32, _i32, _vp, _vp]),
     "attn_b200_paged_decode_workspace_bytes": (_sz, [_i32, _i32, _i32, _i64, _i32]),
+    "attn_b200_paged_decode_single_launch_ok": (_i32, [_i32, _i32, _i32, _i32, _i64, _i32, _i32, _i32, _i32]),
     "attn_b200_paged_decode_pick_chunk": (_i32, [_i32, _i32, _i32, _i64, _i32]),
     "attn_b200_paged_decode_pick_chunk_gqa": (_i32, [_i32, _i32, _i32, _i32, _i32, _i64, _i32]),
     "attn_b200_paged_decode_partial": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _i32, _i32, _i32, _i32, _i64,

@@ -528,6 +528,183 @@ paged_decode_fast_kernel(const DecodeParams p) {
 }
 
 // ---------------------------------------------------------------------------------------------
+// whole-sequence kernel: one CTA per (sequence, head), combine in shared memory, ONE launch
+// ---------------------------------------------------------------------------------------------
+// For batches whose (sequence, head) pairs alone fill the machine and whose sequences are short
+// (batch 8 x 32 heads x <= 1024 tokens: 256 CTAs).  The split-KV form spends a third of such a step
+// on its second launch and on the partial rows' round trip through L2; here the 8 warps of a CTA
+// split the sequence's tokens tile by tile (warp w takes tiles w, w + 8, ...), every warp keeps its
+// (m, l, o) in registers, and the eight partial results meet in shared memory, where the current
+// token is folded in and the output row is written.  No workspace, no second kernel.  The price is
+// imbalance: a CTA lives as long as its sequence is long, so it is the wrong kernel for long or very
+// unequal sequences (the host-side heuristic decides; attn_b200_paged_decode_single_launch_ok).
+// Lane mapping: a row of D 16-bit elements is LPR = D/8 lanes of 16 bytes; a warp-wide load covers
+// TPI = 32/LPR different TOKENS of the CTA's one head; U = 8 such loads for K and 8 for V are in
+// flight per tile of TPI*8 tokens.
+struct SeqDecodeParams {
+    const void* q;
+    const void* k_new;
+    const void* v_new;
+    const void* k_cache;
+    const void* v_cache;
+    const int32_t* slots;
+    const int32_t* offsets;
+    void* out;
+    int B, H, D;
+    int64_t n_tokens, n_slots;
+    int uniform_ctx;
+    float scale_log2;
+    int32_t* err_flag;
+};
+
+template <typename QT, int D>
+__global__ void __launch_bounds__(256, 2)
+paged_decode_seq_kernel(const SeqDecodeParams p) {
+    constexpr int EPL = 8;                       // elements per lane (one 16-byte slice of a 16-bit row)
+    constexpr int LPR = D / EPL;                 // lanes per row
+    constexpr int TPI = 32 / LPR;                // tokens per warp-wide load
+    constexpr int U = 8;                         // loads in flight per lane and tensor
+    constexpr int TILE = TPI * U;                // tokens per warp and tile
+    constexpr int WARPS = 8;
+    static_assert(LPR >= 1 && LPR <= 32 && TILE <= 32, "unsupported head_dim");
+    __shared__ float s_o[WARPS][D];
+    __shared__ float s_ml[WARPS][2];
+    __shared__ float s_new_sh;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int b = blockIdx.x / p.H, h = blockIdx.x % p.H;
+    const int sub = lane % LPR, tsel = lane / LPR;
+    SeqBounds sb{p.offsets, p.uniform_ctx, p.n_tokens};
+    const int64_t seq_beg = sb.beg(b), seq_end_raw = sb.beg(b + 1);
+    const int64_t seq_end = seq_end_raw > seq_beg ? seq_end_raw : seq_beg;
+    const int64_t row_bytes = (int64_t)p.H * D * sizeof(QT);
+    const char* kbase = (const char*)p.k_cache + ((int64_t)h * D + sub * EPL) * sizeof(QT);
+    const char* vbase = (const char*)p.v_cache + ((int64_t)h * D + sub * EPL) * sizeof(QT);
+    const QT* qp = (const QT*)p.q + ((int64_t)b * p.H + h) * D + sub * EPL;
+
+    float qf[EPL];
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) qf[i] = to_f32<QT>(qp[i]) * p.scale_log2;
+    if (warp == 0) {                             // score of the current token (every row group computes the same)
+        const QT* kp = (const QT*)p.k_new + ((int64_t)b * p.H + h) * D + sub * EPL;
+        float acc = 0.f;
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) acc = fmaf(qf[i], to_f32<QT>(kp[i]), acc);
+        acc = group_sum<LPR>(acc);
+        if (lane == 0) s_new_sh = acc;
+    }
+    float m = -INFINITY, l = 0.f, o[EPL];
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) o[i] = 0.f;
+
+    auto load_slot = [&](int64_t t0) -> int {    // slots of the TILE tokens from t0, one per lane
+        const int64_t t = t0 + lane;
+        int s = -1;
+        if (lane < TILE && t < seq_end) {
+            const int64_t v = p.slots ? (int64_t)p.slots[t] : t;
+            if (v >= 0 && v < p.n_slots) s = (int)v;
+            else if (p.err_flag) atomicOr(p.err_flag, ATTN_B200_FLAG_BAD_SLOT);
+        }
+        return s;
+    };
+    const int64_t stride = (int64_t)WARPS * TILE;
+    int next_slot = seq_beg + (int64_t)warp * TILE < seq_end ? load_slot(seq_beg + (int64_t)warp * TILE) : -1;
+    for (int64_t t0 = seq_beg + (int64_t)warp * TILE; t0 < seq_end; t0 += stride) {
+        const int my_slot = next_slot;
+        uint4 kr[U], vr[U];
+        int sl[U];
+#pragma unroll
+        for (int j = 0; j < U; ++j) {
+            sl[j] = __shfl_sync(0xffffffffu, my_slot, j * TPI + tsel);
+            kr[j] = sl[j] >= 0 ? ldg_stream128(kbase + (int64_t)sl[j] * row_bytes) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int j = 0; j < U; ++j)
+            vr[j] = sl[j] >= 0 ? ldg_stream128(vbase + (int64_t)sl[j] * row_bytes) : make_uint4(0, 0, 0, 0);
+        if (t0 + stride < seq_end) next_slot = load_slot(t0 + stride);
+
+        float s[U];
+        float tmax = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < U; ++j) {
+            float kf[EPL];
+            RowChunk<QT, EPL>::unpack(kr[j], kf);
+            float acc = 0.f;
+#pragma unroll
+            for (int i = 0; i < EPL; ++i) acc = fmaf(qf[i], kf[i], acc);
+            acc = group_sum<LPR>(acc);
+            s[j] = sl[j] >= 0 ? acc : -INFINITY;
+            tmax = fmaxf(tmax, s[j]);
+        }
+        const float m_new = fmaxf(m, tmax);
+        if (m_new > -INFINITY) {
+            const float alpha = fast_exp2(m - m_new);
+            l *= alpha;
+#pragma unroll
+            for (int i = 0; i < EPL; ++i) o[i] *= alpha;
+#pragma unroll
+            for (int j = 0; j < U; ++j) {
+                const float pj = fast_exp2(s[j] - m_new);
+                l += pj;
+                float vf[EPL];
+                RowChunk<QT, EPL>::unpack(vr[j], vf);
+#pragma unroll
+                for (int i = 0; i < EPL; ++i) o[i] = fmaf(pj, vf[i], o[i]);
+            }
+            m = m_new;
+        }
+    }
+    // fold the warp's TPI row groups (same head, different tokens), then the CTA's warps
+#pragma unroll
+    for (int x = LPR; x < 32; x <<= 1) {
+        const float mo = __shfl_xor_sync(0xffffffffu, m, x);
+        const float mn = fmaxf(m, mo);
+        const float a = mn > -INFINITY ? fast_exp2(m - mn) : 0.f;      // this side's factor (0 if it saw nothing)
+        const float bq = mn > -INFINITY ? fast_exp2(mo - mn) : 0.f;
+        l = l * a + __shfl_xor_sync(0xffffffffu, l, x) * bq;
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) o[i] = o[i] * a + __shfl_xor_sync(0xffffffffu, o[i], x) * bq;
+        m = mn;
+    }
+    if (tsel == 0) {
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) s_o[warp][sub * EPL + i] = o[i];
+        if (sub == 0) { s_ml[warp][0] = m; s_ml[warp][1] = l; }
+    }
+    __syncthreads();
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        const float s_new = s_new_sh;
+        float M = s_new;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) M = fmaxf(M, s_ml[w][0]);
+        const float w_new = exp2f(s_new - M);
+        float L = w_new;
+        float acc = w_new * to_f32<QT>(((const QT*)p.v_new)[((int64_t)b * p.H + h) * D + d]);
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) {
+            const float mw = s_ml[w][0];
+            const float f = mw > -INFINITY ? exp2f(mw - M) : 0.f;
+            L = fmaf(s_ml[w][1], f, L);
+            acc = fmaf(s_o[w][d], f, acc);
+        }
+        ((QT*)p.out)[((int64_t)b * p.H + h) * D + d] = from_f32<QT>(acc / L);
+    }
+}
+
+template <typename QT>
+static int launch_seq(const SeqDecodeParams& p, cudaStream_t st) {
+    const int64_t blocks = (int64_t)p.B * p.H;
+    if (blocks > 0x7fffffffLL) return ATTN_B200_ETOOLARGE;
+    switch (p.D) {
+        case 64: paged_decode_seq_kernel<QT, 64><<<(unsigned)blocks, 256, 0, st>>>(p); break;
+        case 128: paged_decode_seq_kernel<QT, 128><<<(unsigned)blocks, 256, 0, st>>>(p); break;
+        case 256: paged_decode_seq_kernel<QT, 256><<<(unsigned)blocks, 256, 0, st>>>(p); break;
+        default: return ATTN_B200_ESHAPE;
+    }
+    return (int)cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------------------------
 // generic kernel: any dtype / head_dim, one CTA per (unit, head)
 // ---------------------------------------------------------------------------------------------
 template <typename QT, typename KVT>
@@ -1010,6 +1187,19 @@ extern "C" int attn_b200_paged_decode_pick_chunk(int B, int H, int D, int64_t n_
     return chunk;
 }
 
+// One CTA per (sequence, head) pays when those CTAs alone fill the machine (at least one per SM,
+// at most the two per SM that are resident at once, so that it is a single wave) and the sequences
+// are short: a CTA works through its sequence 128 tokens per round.  Lengths are not known on the
+// host; the capacity per sequence stands in for them.
+extern "C" int attn_b200_paged_decode_single_launch_ok(int B, int H, int n_kv_heads, int D, int64_t n_tokens,
+                                                       int block_size, int q_dtype, int kv_dtype, int sm_count) {
+    if (sm_count <= 0) sm_count = 148;
+    if (B <= 0 || H <= 0 || n_kv_heads != H || block_size > 1 || kv_dtype != q_dtype) return 0;
+    if (!(q_dtype == ATTN_B200_F16 || q_dtype == ATTN_B200_BF16) || !(D == 64 || D == 128 || D == 256)) return 0;
+    const int64_t ctas = (int64_t)B * H;
+    return ctas >= sm_count && ctas <= 2LL * sm_count && n_tokens / B <= 2048;
+}
+
 extern "C" int attn_b200_paged_decode_pick_chunk_gqa(int B, int n_kv_heads, int group, int D, int kv_dtype,
                                                      int64_t n_tokens, int sm_count) {
     const bool mma = (group == 2 || group == 4 || group == 8) && D == 128 &&
@@ -1035,9 +1225,20 @@ extern "C" int attn_b200_paged_decode(const void* q, const void* k_new, const vo
     int rc = check_common(q, k_cache, v_cache, B, H, n_kv_heads, D, n_tokens, n_slots, block_size, max_blocks, chunk,
                           kv_dtype, k_scale, v_scale);
     if (rc) return rc;
-    if (!out || !workspace || !k_new || !v_new) return ATTN_B200_EINVAL;
+    if (!out || !k_new || !v_new) return ATTN_B200_EINVAL;
     if ((S == nullptr) != (P == nullptr)) return ATTN_B200_EINVAL;
     if (!offsets && (uniform_ctx < 0 || (int64_t)uniform_ctx * B != n_tokens)) return ATTN_B200_EINVAL;
+    if (stages == 4) {      // single launch: one CTA per (sequence, head), no workspace
+        if (S || n_kv_heads != H || block_size > 1 || kv_dtype != q_dtype ||
+            !(q_dtype == ATTN_B200_F16 || q_dtype == ATTN_B200_BF16) || !(D == 64 || D == 128 || D == 256) ||
+            ((uintptr_t)k_cache | (uintptr_t)v_cache) % 16)
+            return ATTN_B200_ESHAPE;
+        SeqDecodeParams sp{q, k_new, v_new, k_cache, v_cache, slots, offsets, out, B, H, D, n_tokens, n_slots,
+                           uniform_ctx, scale * kLog2e, err_flag};
+        return q_dtype == ATTN_B200_F16 ? launch_seq<__half>(sp, (cudaStream_t)stream)
+                                        : launch_seq<__nv_bfloat16>(sp, (cudaStream_t)stream);
+    }
+    if (!workspace) return ATTN_B200_EINVAL;
     if (workspace_bytes < attn_b200_paged_decode_workspace_bytes(B, H, D, n_tokens, chunk) ||
         (uintptr_t)workspace % 16)
         return ATTN_B200_EWORKSPACE;

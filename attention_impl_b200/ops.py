@@ -139,7 +139,7 @@ def paged_kv_attention_forward(Q, K, V, K_cache, V_cache, cache_indices, offsets
                                max_context_len: Optional[int] = None, workspace: Optional[torch.Tensor] = None,
                                out: Optional[torch.Tensor] = None,
                                err_flag: Optional[torch.Tensor] = None, stages: int = 3,
-                               block_size: int = 1) -> List[torch.Tensor]:
+                               block_size: int = 1, single_launch: Optional[bool] = None) -> List[torch.Tensor]:
     """KV-paged single-query attention, block_size = 1 (paged_attention_kernel.cu:237-294).
 
     Q, K, V ``[B, H*D]`` (the current token); K_cache, V_cache ``[slots, H*D]``; cache_indices
@@ -156,6 +156,11 @@ def paged_kv_attention_forward(Q, K, V, K_cache, V_cache, cache_indices, offsets
     D`` must divide ``num_heads``); query head h reads KV head ``h // (num_heads // Hkv)``.
     ``block_size > 1``: ``cache_indices`` is a block table int32 ``[B, max_blocks]`` and token t of
     sequence b lives in pool row ``cache_indices[b, t // block_size] * block_size + t % block_size``.
+    ``single_launch``: run the step as ONE kernel, a CTA per (sequence, head) that combines in shared
+    memory (multi-head attention over 16-bit pools, per-token table, head_dim 64/128/256, no S/P).
+    ``None`` (default) takes it when S and P are not requested and the library's heuristic expects it
+    to win: the (sequence, head) pairs alone fill the machine in one wave and sequences are short (a
+    batch of 8 with 32 heads); ``True`` forces it (RuntimeError if the case is not covered).
     """
     for t, n in ((Q, "Q"), (K, "K"), (V, "V"), (K_cache, "K_cache"), (V_cache, "V_cache")):
         _check_input(t, n)
@@ -197,8 +202,17 @@ def paged_kv_attention_forward(Q, K, V, K_cache, V_cache, cache_indices, offsets
     with torch.cuda.device(dev):
         if chunk is None:
             chunk = pick_chunk(B, Hkv, D, T, dev, group=H // Hkv, kv_dtype=kvd)
-        need = decode_workspace_bytes(B, H, D, T, chunk)
-        if workspace is None:
+        if single_launch is None:
+            single_launch = (not return_sp and stages == 3 and bool(lib.attn_b200_paged_decode_single_launch_ok(
+                B, H, Hkv, D, T, block_size, qd, kvd, sm_count(dev))))
+        elif single_launch and return_sp:
+            raise RuntimeError("single_launch=True does not produce S and P: pass return_sp=False")
+        if single_launch:
+            stages = 4
+        need = 0 if single_launch else decode_workspace_bytes(B, H, D, T, chunk)
+        if single_launch:
+            workspace = None
+        elif workspace is None:
             workspace = torch.empty(need, dtype=torch.uint8, device=dev)
         elif workspace.numel() * workspace.element_size() < need:
             raise RuntimeError(f"workspace too small: {need} bytes needed")
@@ -216,8 +230,8 @@ def paged_kv_attention_forward(Q, K, V, K_cache, V_cache, cache_indices, offsets
             stride = 0
         check(lib.attn_b200_paged_decode(
             Q.data_ptr(), K.data_ptr(), V.data_ptr(), K_cache.data_ptr(), V_cache.data_ptr(),
-            cache_indices.data_ptr(), offsets.data_ptr(), O.data_ptr(), workspace.data_ptr(),
-            workspace.numel() * workspace.element_size(),
+            cache_indices.data_ptr(), offsets.data_ptr(), O.data_ptr(), _ptr(workspace),
+            0 if workspace is None else workspace.numel() * workspace.element_size(),
             S.data_ptr() if return_sp else None, P.data_ptr() if return_sp else None, stride,
             B, H, Hkv, D, T, K_cache.size(0), 0, block_size, max_blocks, chunk, float(scale), _ptr(k_scale),
             _ptr(v_scale), qd, kvd, stages, _ptr(err_flag), _stream()), "paged_kv_attention_forward")

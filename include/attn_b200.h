@@ -117,7 +117,13 @@ ATTN_B200_API int attn_b200_rope_write_kv(void* q, void* k, const void* v, const
  * `workspace` needs attn_b200_paged_decode_workspace_bytes(...) bytes, 16-byte aligned; it needs
  * no initialisation and holds nothing between calls.
  * `stages`: 3 runs both kernels (the normal call); 1 runs only the partial kernel, 2 only the
- * combine kernel (same arguments) so that a profiler or benchmark can put events between them.
+ * combine kernel (same arguments) so that a profiler or benchmark can put events between them;
+ * 4 is the single-launch form: one CTA per (sequence, head) whose warps split the sequence's tokens
+ * and combine in shared memory (`workspace` may be NULL, `chunk` is only range-checked).  It exists
+ * for multi-head attention (n_kv_heads == H) with a per-token table, 16-bit q and pools of q's type,
+ * head_dim 64 / 128 / 256 and S == NULL (anything else: ATTN_B200_ESHAPE), and it pays only when B*H
+ * CTAs fill the machine in one wave and the sequences are short:
+ * attn_b200_paged_decode_single_launch_ok() says when.
  * The combine kernel is launched as a programmatic dependent of the partial kernel (its launch and
  * prologue overlap that kernel's tail; it waits for the partial rows itself).
  * Extensions beyond the reference (which is multi-head, block_size = 1):
@@ -136,6 +142,10 @@ ATTN_B200_API int attn_b200_paged_decode(const void* q, const void* k_new, const
                            int32_t* err_flag, void* stream);
 
 ATTN_B200_API size_t attn_b200_paged_decode_workspace_bytes(int B, int H, int D, int64_t n_tokens, int chunk);
+/* Non-zero when the single-launch form (`stages` = 4) exists for this case and is expected to beat
+ * the two-launch form: sm_count <= B*H <= 2*sm_count and at most 2048 tokens of capacity per sequence. */
+ATTN_B200_API int attn_b200_paged_decode_single_launch_ok(int B, int H, int n_kv_heads, int D, int64_t n_tokens,
+                                                          int block_size, int q_dtype, int kv_dtype, int sm_count);
 /* Heuristic chunk length: enough (chunk, head-group) work items to fill `sm_count` SMs. */
 ATTN_B200_API int attn_b200_paged_decode_pick_chunk(int B, int H, int D, int64_t n_tokens, int sm_count);
 /* The same for grouped-query heads: `group` query heads per KV head, `kv_dtype` of the pools.  Groups

@@ -16,6 +16,53 @@ pytestmark = pytest.mark.gpu
 TOL16 = 2e-3
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("H,D", [(32, 128), (3, 128), (8, 64), (4, 256)])
+def test_single_launch_decode_ragged(dtype, H, D):
+    """One CTA per (sequence, head), combine in shared memory: ragged lengths incl. empty sequences,
+    sequences shorter than one warp tile, longer than one round of the CTA's eight warps."""
+    import attention_impl_b200 as A
+    lens = [0, 1, 15, 16, 17, 127, 128, 129, 0, 700, 1030, 5]
+    inp = decode_inputs(len(lens), H, D, lens, 4096, dtype, seed=H * 10 + D)
+    args = [t.cuda() for t in inp]
+    _, _, O = A.paged_kv_attention_forward(*args, H, return_sp=False, single_launch=True)
+    _, _, O32 = orc.paged_decode(*inp, H, compute_dtype=torch.float32)
+    tol = TOL16 if dtype == torch.float16 else 1.6e-2
+    assert torch.isfinite(O).all()
+    assert (O.cpu().float() - O32.float()).abs().max() <= tol
+    _, _, O2 = A.paged_kv_attention_forward(*args, H, return_sp=False, single_launch=False)
+    assert (O.float() - O2.float()).abs().max() <= (1e-3 if dtype == torch.float16 else 1.6e-2)
+
+
+def test_single_launch_decode_small_batch_workload_and_its_choice():
+    """B=8, H=32, D=128, ctx ~ U[128,1024]: the heuristic picks the single-launch form by itself; bad
+    slots are flagged and skipped; cases it does not cover are refused when forced."""
+    import attention_impl_b200 as A
+    from attention_impl_b200 import _lib
+    B, H, D = 8, 32, 128
+    lens = uniform_lens(B, 128, 1024, seed=1)
+    inp = decode_inputs(B, H, D, lens, 16384, torch.float16, seed=1001)
+    T = sum(lens)
+    assert _lib.lib.attn_b200_paged_decode_single_launch_ok(B, H, H, D, T, 1, _lib.F16, _lib.F16, 148) == 1
+    assert _lib.lib.attn_b200_paged_decode_single_launch_ok(256, H, H, D, 4_600_000, 1, _lib.F16, _lib.F16, 148) == 0
+    assert _lib.lib.attn_b200_paged_decode_single_launch_ok(B, H, 8, D, T, 1, _lib.F16, _lib.F16, 148) == 0
+    args = [t.cuda() for t in inp]
+    _, _, O = A.paged_kv_attention_forward(*args, H, return_sp=False)                 # auto: single launch
+    _, _, O32 = orc.paged_decode(*inp, H, compute_dtype=torch.float32)
+    assert (O.cpu().float() - O32.float()).abs().max() <= TOL16
+    ci = inp[5].clone()
+    ci[3] = 10 ** 6
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    _, _, Ob = A.paged_kv_attention_forward(*args[:5], ci.cuda(), args[6], H, return_sp=False, single_launch=True,
+                                            err_flag=flag)
+    assert int(flag.item()) & 1 and torch.isfinite(Ob).all()
+    with pytest.raises(RuntimeError):
+        A.paged_kv_attention_forward(*[a.float() if a.is_floating_point() else a for a in args], H, return_sp=False,
+                                     single_launch=True)
+    with pytest.raises(RuntimeError, match="single_launch=True"):
+        A.paged_kv_attention_forward(*args, H, single_launch=True)
+
+
 def test_decode_graph_grouped_query_pools():
     """A captured step over pools with fewer KV heads than query heads (head_dim given explicitly)."""
     import attention_impl_b200 as A
