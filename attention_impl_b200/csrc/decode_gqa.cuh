@@ -4,11 +4,15 @@
 //
 // Why: the CUDA-core kernel does the arithmetic of MHA per token and query head while the bytes
 // shrink by G; from G = 4 up it is bound by instruction issue (3.2 TB/s at G = 4, 1.2 at G = 8).
-// Here a warp owns one KV head and its G query heads and walks the unit's tokens 16 at a time:
-//   S[16 x 16] = Q[16 x 128] K^T   16 x mma.sync.m16n8k16 (rows >= G of Q are zero)
-//   online softmax on the rows it owns (row = lane / 4; the 4 lanes of a row hold 4 tokens each)
-//   O[16 x 128] += P[16 x 16] V    16 x mma.sync.m16n8k16, P taken straight from the S fragments
-// (mma.sync, not tcgen05: M is 2 to 8 rows; a 128-row tcgen05 tile would be 94 % padding or more.
+// Here a warp owns one KV head and its G query heads and walks the unit's tokens 16 at a time, with
+// the KEYS as the M dimension of the MMAs (with the heads as M half of every A fragment was padding
+// for G <= 8 and a tile cost 32 MMAs instead of 16):
+//   S^T[16 keys x 8 heads] = K[16 x 128] Q^T      8 x mma.sync.m16n8k16 (heads >= G of Q are zero)
+//   online softmax per head: lane (n, c) holds keys n, 8 + n of heads 2c, 2c + 1; the maximum over
+//   the keys is three shuffles over n
+//   O^T[128 dims x 8 heads] += V^T[128 x 16] P^T  8 x mma.sync.m16n8k16; P^T is the transposed score
+//   fragment (two movmatrix), V^T the transposed 8-key x 8-dim blocks the lanes hold (four per MMA)
+// (mma.sync, not tcgen05: N is 2 to 8 heads; a 128-row tcgen05 tile would be mostly padding.
 // G = 2 is memory bound either way; the gain there, 5.3 -> 5.95 TB/s, comes from the copy pipeline.)
 //
 // Data movement.  Lane (n = lane / 4, c = lane % 4) copies, for tokens n and 8 + n of the tile,
@@ -18,12 +22,13 @@
 // synchronisation there is) and 16 KB per warp are in flight regardless of registers.
 //
 // Fragments.  A dot product does not care in which order the dims are visited, so the 8 k-slices of
-// the MMA use the dims in the order the lanes hold them: slice 2j + e takes, from lane (n, c), the
-// dims (4j + c) * 8 + 4e + {0, 1} as k = 2c, 2c + 1 and + {2, 3} as k = 2c + 8, 2c + 9; Q's A
-// fragments are loaded once with the same mapping.  For P V the B operand wants pairs of TOKENS per
-// register: movmatrix.trans turns the 8-token x 8-dim block that the lanes hold row-wise (one
-// register per lane) into that form.  The output columns come out so that lane (row, c) owns the
-// same 32 dims of its row that it loaded.
+// the first product use the dims in the order the lanes hold them: slice 2j + e takes, from lane
+// (n, c), for keys n and 8 + n (the A rows), the dims (4j + c) * 8 + 4e + {0, 1} as k = 2c, 2c + 1 and
+// + {2, 3} as k = 2c + 8, 2c + 9; Q^T's B fragments (head n of lane (n, c)) are loaded once with the
+// same mapping.  For the second product the A operand wants pairs of KEYS per register:
+// movmatrix.trans turns the 8-key x 8-dim block that the lanes hold row-wise (one register per lane)
+// into that form; the 16 rows of output block (j, e) are the dims (4j + r/2) * 8 + 4e + r%2 (r = 0..7,
+// first word of the pair) and + 2 (second word).
 #pragma once
 
 namespace gqa {
@@ -85,8 +90,8 @@ paged_decode_gqa_mma_kernel(const DecodeParams p) {
     Unit un;
     if (!resolve_unit(u, p.B, p.chunk, sb, un) || hk >= p.Hkv) return;
 
-    // Q as A fragments (rows >= G stay zero): slice s = 2j + e, registers {k = 2c.., k = 2c+8..}
-    uint32_t aq[8][2];
+    // Q^T as B fragments of head n (heads >= G stay zero): slice s = 2j + e, registers {k = 2c.., k = 2c+8..}
+    uint32_t bq[8][2];
     {
         const bool row_ok = n < G;
         const T* qrow = (const T*)p.q + ((int64_t)un.b * p.H + hk * G + (row_ok ? n : 0)) * D;
@@ -95,8 +100,8 @@ paged_decode_gqa_mma_kernel(const DecodeParams p) {
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 const uint32_t* src = reinterpret_cast<const uint32_t*>(qrow + (4 * j + c) * 8 + 4 * e);
-                aq[2 * j + e][0] = row_ok ? src[0] : 0u;
-                aq[2 * j + e][1] = row_ok ? src[1] : 0u;
+                bq[2 * j + e][0] = row_ok ? src[0] : 0u;
+                bq[2 * j + e][1] = row_ok ? src[1] : 0u;
             }
     }
     const int64_t row_bytes = (int64_t)p.Hkv * D * sizeof(T);
@@ -126,13 +131,17 @@ paged_decode_gqa_mma_kernel(const DecodeParams p) {
         }
         return __ballot_sync(0xffffffffu, my_slot >= 0) & 0xffffu;
     };
+    auto lds128 = [](uint32_t addr, uint32_t (&w)[4]) {
+        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]) : "r"(addr));
+    };
 
-    float oacc[16][4];
+    // O^T accumulators: block (j, e) = oacc[2j + e]: {dim row n, head 2c | head 2c+1 | dim row 8+n, head 2c | head 2c+1}
+    float oacc[8][4];
 #pragma unroll
-    for (int i = 0; i < 16; ++i)
+    for (int i = 0; i < 8; ++i)
 #pragma unroll
         for (int k = 0; k < 4; ++k) oacc[i][k] = 0.f;
-    float m = -INFINITY, l = 0.f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};      // heads 2c and 2c + 1 (l: this lane's keys only)
 
     // pipeline: tiles t+1 and t+2 are in flight while tile t is multiplied
     unsigned v0 = 0, v1 = 0, v2 = 0;        // validity bits of the tiles computed next, after that, and just issued
@@ -161,86 +170,107 @@ paged_decode_gqa_mma_kernel(const DecodeParams p) {
         v0 = v1;
         v1 = v2;
 
-        // S = Q K^T for the tile's two groups of 8 tokens
-        float sacc[2][4];
-#pragma unroll
-        for (int grp = 0; grp < 2; ++grp) {
-#pragma unroll
-            for (int k = 0; k < 4; ++k) sacc[grp][k] = 0.f;
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                uint4 kc;
-                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(kc.x), "=r"(kc.y), "=r"(kc.z), "=r"(kc.w)
-                             : "r"(base + ((grp * 2 + 0) * 4 + j) * 512));
-                const uint32_t a0[4] = {aq[2 * j][0], 0u, aq[2 * j][1], 0u};
-                const uint32_t a1[4] = {aq[2 * j + 1][0], 0u, aq[2 * j + 1][1], 0u};
-                Mma<T>::run(sacc[grp], a0, kc.x, kc.y);
-                Mma<T>::run(sacc[grp], a1, kc.z, kc.w);
-            }
-        }
-        // this lane's four scores of row n: tokens grp*8 + 2c + {0, 1}
-        float sc[4];
-#pragma unroll
-        for (int grp = 0; grp < 2; ++grp)
-#pragma unroll
-            for (int i = 0; i < 2; ++i) {
-                const bool ok = (vb >> (grp * 8 + 2 * c + i)) & 1u;
-                sc[grp * 2 + i] = ok ? sacc[grp][i] * p.scale_log2 : -INFINITY;
-            }
-        float tmax = fmaxf(fmaxf(sc[0], sc[1]), fmaxf(sc[2], sc[3]));
-        tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
-        tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
-        const float m_new = fmaxf(m, tmax);
-        const float msub = m_new > -INFINITY ? m_new : 0.f;     // no valid token yet: exp2(-inf - 0) = 0
-        const float alpha = fast_exp2(m - msub);
-        float pr[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) pr[i] = fast_exp2(sc[i] - msub);
-        l = l * alpha + ((pr[0] + pr[1]) + (pr[2] + pr[3]));
-        m = m_new;
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-            oacc[i][0] *= alpha;
-            oacc[i][1] *= alpha;
-        }
-        // O += P V: P's A fragments are the score fragments (tokens 2c, 2c+1 of group 0 are k = 2c, 2c+1;
-        // of group 1, k = 2c + 8, 2c + 9)
-        const uint32_t pa[4] = {Mma<T>::pack(pr[0], pr[1]), 0u, Mma<T>::pack(pr[2], pr[3]), 0u};
+        // S^T = K Q^T: rows = keys n, 8 + n; columns = heads 2c, 2c + 1
+        float sacc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-            uint4 va, vb4;
-            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(va.x), "=r"(va.y), "=r"(va.z), "=r"(va.w)
-                         : "r"(base + ((0 * 2 + 1) * 4 + j) * 512));
-            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(vb4.x), "=r"(vb4.y), "=r"(vb4.z), "=r"(vb4.w)
-                         : "r"(base + ((1 * 2 + 1) * 4 + j) * 512));
-            const uint32_t w0[4] = {va.x, va.y, va.z, va.w}, w1[4] = {vb4.x, vb4.y, vb4.z, vb4.w};
+            uint32_t w0[4], w1[4];          // key n, key 8 + n: chunk 4j + c
+            lds128(base + ((0 * 2 + 0) * 4 + j) * 512, w0);
+            lds128(base + ((1 * 2 + 0) * 4 + j) * 512, w1);
 #pragma unroll
-            for (int r = 0; r < 4; ++r)
-                Mma<T>::run(oacc[j * 4 + r], pa, movmatrix_trans(w0[r]), movmatrix_trans(w1[r]));
+            for (int e = 0; e < 2; ++e) {
+                const uint32_t a[4] = {w0[2 * e], w1[2 * e], w0[2 * e + 1], w1[2 * e + 1]};
+                Mma<T>::run(sacc, a, bq[2 * j + e][0], bq[2 * j + e][1]);
+            }
+        }
+        const bool ok0 = (vb >> n) & 1u, ok1 = (vb >> (8 + n)) & 1u;
+        float pr[4];                         // (key n, head 2c), (key n, 2c+1), (key 8+n, 2c), (key 8+n, 2c+1)
+        float alpha[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const float s0 = ok0 ? sacc[i] * p.scale_log2 : -INFINITY, s1 = ok1 ? sacc[2 + i] * p.scale_log2 : -INFINITY;
+            float tmax = fmaxf(s0, s1);
+            tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 4));
+            tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 8));
+            tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 16));
+            const float m_new = fmaxf(m[i], tmax);
+            const float msub = m_new > -INFINITY ? m_new : 0.f;     // no valid token yet: exp2(-inf - 0) = 0
+            alpha[i] = fast_exp2(m[i] - msub);
+            pr[i] = fast_exp2(s0 - msub);
+            pr[2 + i] = fast_exp2(s1 - msub);
+            l[i] = l[i] * alpha[i] + (pr[i] + pr[2 + i]);
+            m[i] = m_new;
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            oacc[i][0] *= alpha[0];
+            oacc[i][1] *= alpha[1];
+            oacc[i][2] *= alpha[0];
+            oacc[i][3] *= alpha[1];
+        }
+        // P^T as the B operand: transpose the 8-key x 8-head blocks of the score fragment
+        const uint32_t pb0 = movmatrix_trans(Mma<T>::pack(pr[0], pr[1]));      // head n; keys 2c, 2c + 1
+        const uint32_t pb1 = movmatrix_trans(Mma<T>::pack(pr[2], pr[3]));      // head n; keys 8 + 2c, 9 + 2c
+        // O^T += V^T P^T: A = transposed 8-key x 8-dim blocks (word 2e -> rows 0..7, word 2e + 1 -> rows 8..15)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            uint32_t w0[4], w1[4];
+            lds128(base + ((0 * 2 + 1) * 4 + j) * 512, w0);
+            lds128(base + ((1 * 2 + 1) * 4 + j) * 512, w1);
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const uint32_t a[4] = {movmatrix_trans(w0[2 * e]), movmatrix_trans(w0[2 * e + 1]),
+                                       movmatrix_trans(w1[2 * e]), movmatrix_trans(w1[2 * e + 1])};
+                Mma<T>::run(oacc[2 * j + e], a, pb0, pb1);
+            }
         }
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
-    // the four lanes of a row hold disjoint tokens: fold their denominators
-    l += __shfl_xor_sync(0xffffffffu, l, 1);
-    l += __shfl_xor_sync(0xffffffffu, l, 2);
-    if (n < G) {
-        const float vs = p.v_scale ? p.v_scale[hk] : 1.f;
-        float* row = p.part + ((int64_t)u * p.H + hk * G + n) * (D + 2);
+    // the eight lanes with this lane's c hold disjoint keys: fold their denominators
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        l[i] += __shfl_xor_sync(0xffffffffu, l[i], 4);
+        l[i] += __shfl_xor_sync(0xffffffffu, l[i], 8);
+        l[i] += __shfl_xor_sync(0xffffffffu, l[i], 16);
+    }
+    const float vs = p.v_scale ? p.v_scale[hk] : 1.f;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int hq = 2 * c + i;
+        if (hq >= G) continue;
+        float* row = p.part + ((int64_t)u * p.H + hk * G + hq) * (D + 2);
+        // block (j, e): row n of the first word's block is dim (4j + n/2) * 8 + 4e + n%2, of the second word's + 2
 #pragma unroll
         for (int j = 0; j < 4; ++j)
 #pragma unroll
-            for (int r = 0; r < 4; ++r)
-                *reinterpret_cast<float2*>(row + (4 * j + c) * 8 + 2 * r) =
-                    make_float2(oacc[j * 4 + r][0] * vs, oacc[j * 4 + r][1] * vs);
-        if (c == 0) *reinterpret_cast<float2*>(row + D) = make_float2(m, l);
+            for (int e = 0; e < 2; ++e) {
+                const int d = (4 * j + (n >> 1)) * 8 + 4 * e + (n & 1);
+                row[d] = oacc[2 * j + e][i] * vs;
+                row[d + 2] = oacc[2 * j + e][2 + i] * vs;
+            }
+        if (n == 0) *reinterpret_cast<float2*>(row + D) = make_float2(m[i], l[i]);
     }
 }
 
-// The same kernel for e4m3 pools: a token's row of a head is 128 bytes = 8 chunks of 16 dims, lane
-// (n, c) copies chunks 4j + c (j = 0, 1); a 32-bit word of a chunk (4 e4m3) becomes two fp16 pairs
-// (cvt.rn.f16x2.e4m3x2), which are the two B registers of one k-slice for Q K^T and two 8-dim output
-// blocks for P V.  The MMAs are fp16 for either query type (q is converted once, as the CUDA-core
-// e4m3 kernels do); the per-head scales enter the score and the output.
+// The kernel for e4m3 pools, with the KEYS as the M dimension of the MMAs.
+//
+// A token's row of a head is 128 bytes = 8 chunks of 16 dims; lane (n, c) copies chunks 4j + c
+// (j = 0, 1) of tokens n and 8 + n of the tile and reads back what it copied, as above.  With the
+// query heads as M (the 16-bit kernel's form) half of every A fragment is padding for G <= 8 and a
+// 16-key tile costs 32 MMAs, about half of the instruction issue time of this conversion-heavy
+// kernel.  Here a tile is
+//   S^T[16 keys x 8 heads] = K[16 x 128] Q^T      8 x mma.sync.m16n8k16 (fp16; heads >= G are zero)
+//   O^T[128 dims x 8 heads] += V^T[128 x 16] P^T  8 x mma.sync.m16n8k16
+// 16 MMAs.  K is the A operand straight from the converted words: for k-slice s = 4j + e lane (n, c)
+// supplies, for keys n and 8 + n, the dims (4j + c) * 16 + 4e + {0, 1} (k = 2c, 2c + 1) and + {2, 3}
+// (k = 2c + 8, 2c + 9); Q^T is the B operand with the same dim order (b0, b1 of lane (h, c) = those
+// dims of head h).  The score fragment of lane (n, c) is (key n | key 8 + n) x (heads 2c, 2c + 1):
+// a lane tracks the running maximum and denominator of its two heads, the maximum over the keys is
+// three shuffles over n.  P^T as the B operand of the second product is the transposed score
+// fragment: two movmatrix.  V^T as its A operand is the transposed 8-key x 8-"dim" blocks the lanes
+// hold (four movmatrix per MMA, as many as before); the 16 rows of output block (j, e) are the dims
+// (4j + r/2) * 16 + 4e + r%2 (rows r = 0..7, from the words' low halves) and + 2 (rows 8..15, high
+// halves).  The MMAs are fp16 for either query type; the per-head scales enter the score and the output.
 namespace gqa {
 constexpr int kStageBytes8 = kTile * 256;
 constexpr int kSmemBytes8 = kWarps * kStages * kStageBytes8;
@@ -263,8 +293,8 @@ paged_decode_gqa_mma_e4m3_kernel(const DecodeParams p) {
     Unit un;
     if (!resolve_unit(u, p.B, p.chunk, sb, un) || hk >= p.Hkv) return;
 
-    // Q as fp16 A fragments: slice s = 4j + e takes dims (4j + c) * 16 + 4e + {0, 1} and + {2, 3}
-    uint32_t aq[8][2];
+    // Q^T as fp16 B fragments of head n: slice s = 4j + e holds dims (4j + c) * 16 + 4e + {0, 1} and + {2, 3}
+    uint32_t bq[8][2];
     {
         const bool row_ok = n < G;
         const QT* qrow = (const QT*)p.q + ((int64_t)un.b * p.H + hk * G + (row_ok ? n : 0)) * D;
@@ -273,8 +303,8 @@ paged_decode_gqa_mma_e4m3_kernel(const DecodeParams p) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const QT* src = qrow + (4 * j + c) * 16 + 4 * e;
-                aq[4 * j + e][0] = row_ok ? M16::pack(to_f32<QT>(src[0]), to_f32<QT>(src[1])) : 0u;
-                aq[4 * j + e][1] = row_ok ? M16::pack(to_f32<QT>(src[2]), to_f32<QT>(src[3])) : 0u;
+                bq[4 * j + e][0] = row_ok ? M16::pack(to_f32<QT>(src[0]), to_f32<QT>(src[1])) : 0u;
+                bq[4 * j + e][1] = row_ok ? M16::pack(to_f32<QT>(src[2]), to_f32<QT>(src[3])) : 0u;
             }
     }
     const float qs = p.scale_log2 * (p.k_scale ? p.k_scale[hk] : 1.f);
@@ -303,13 +333,18 @@ paged_decode_gqa_mma_e4m3_kernel(const DecodeParams p) {
         }
         return __ballot_sync(0xffffffffu, my_slot >= 0) & 0xffffu;
     };
+    auto lds128 = [](uint32_t addr, uint32_t (&w)[4]) {
+        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]) : "r"(addr));
+    };
+    auto u32 = [](const __half2& h) { return *reinterpret_cast<const uint32_t*>(&h); };
 
-    float oacc[16][4];
+    // O^T accumulators: block (j, e) = oacc[4j + e]: {dim row n, head 2c | head 2c+1 | dim row 8+n, head 2c | head 2c+1}
+    float oacc[8][4];
 #pragma unroll
-    for (int i = 0; i < 16; ++i)
+    for (int i = 0; i < 8; ++i)
 #pragma unroll
         for (int k = 0; k < 4; ++k) oacc[i][k] = 0.f;
-    float m = -INFINITY, l = 0.f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};      // heads 2c and 2c + 1 (l: this lane's keys only)
 
     unsigned v0 = 0, v1 = 0, v2 = 0;
     int next_slot = tile_slot(0);
@@ -337,84 +372,90 @@ paged_decode_gqa_mma_e4m3_kernel(const DecodeParams p) {
         v0 = v1;
         v1 = v2;
 
-        float sacc[2][4];
-#pragma unroll
-        for (int grp = 0; grp < 2; ++grp) {
-#pragma unroll
-            for (int k = 0; k < 4; ++k) sacc[grp][k] = 0.f;
-#pragma unroll
-            for (int j = 0; j < 2; ++j) {
-                uint32_t w[4];
-                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3])
-                             : "r"(base + ((grp * 2 + 0) * 2 + j) * 512));
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    __half2 lo, hi;
-                    e4m3x4_to_half2x2(w[e], lo, hi);
-                    const uint32_t a[4] = {aq[4 * j + e][0], 0u, aq[4 * j + e][1], 0u};
-                    M16::run(sacc[grp], a, *reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
-                }
-            }
-        }
-        float sc[4];
-#pragma unroll
-        for (int grp = 0; grp < 2; ++grp)
-#pragma unroll
-            for (int i = 0; i < 2; ++i) {
-                const bool ok = (vb >> (grp * 8 + 2 * c + i)) & 1u;
-                sc[grp * 2 + i] = ok ? sacc[grp][i] * qs : -INFINITY;
-            }
-        float tmax = fmaxf(fmaxf(sc[0], sc[1]), fmaxf(sc[2], sc[3]));
-        tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
-        tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
-        const float m_new = fmaxf(m, tmax);
-        const float msub = m_new > -INFINITY ? m_new : 0.f;
-        const float alpha = fast_exp2(m - msub);
-        float pr[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) pr[i] = fast_exp2(sc[i] - msub);
-        l = l * alpha + ((pr[0] + pr[1]) + (pr[2] + pr[3]));
-        m = m_new;
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-            oacc[i][0] *= alpha;
-            oacc[i][1] *= alpha;
-        }
-        const uint32_t pa[4] = {M16::pack(pr[0], pr[1]), 0u, M16::pack(pr[2], pr[3]), 0u};
+        // S^T = K Q^T: rows = keys n, 8 + n; columns = heads 2c, 2c + 1
+        float sacc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
-            uint32_t w0[4], w1[4];
-            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w0[0]), "=r"(w0[1]), "=r"(w0[2]), "=r"(w0[3])
-                         : "r"(base + ((0 * 2 + 1) * 2 + j) * 512));
-            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w1[0]), "=r"(w1[1]), "=r"(w1[2]), "=r"(w1[3])
-                         : "r"(base + ((1 * 2 + 1) * 2 + j) * 512));
+            uint32_t w0[4], w1[4];          // key n, key 8 + n: chunk 4j + c
+            lds128(base + ((0 * 2 + 0) * 2 + j) * 512, w0);
+            lds128(base + ((1 * 2 + 0) * 2 + j) * 512, w1);
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 __half2 lo0, hi0, lo1, hi1;
                 e4m3x4_to_half2x2(w0[e], lo0, hi0);
                 e4m3x4_to_half2x2(w1[e], lo1, hi1);
-                M16::run(oacc[(j * 4 + e) * 2 + 0], pa, movmatrix_trans(*reinterpret_cast<const uint32_t*>(&lo0)),
-                         movmatrix_trans(*reinterpret_cast<const uint32_t*>(&lo1)));
-                M16::run(oacc[(j * 4 + e) * 2 + 1], pa, movmatrix_trans(*reinterpret_cast<const uint32_t*>(&hi0)),
-                         movmatrix_trans(*reinterpret_cast<const uint32_t*>(&hi1)));
+                const uint32_t a[4] = {u32(lo0), u32(lo1), u32(hi0), u32(hi1)};
+                M16::run(sacc, a, bq[4 * j + e][0], bq[4 * j + e][1]);
+            }
+        }
+        const bool ok0 = (vb >> n) & 1u, ok1 = (vb >> (8 + n)) & 1u;
+        float pr[4];                         // (key n, head 2c), (key n, 2c+1), (key 8+n, 2c), (key 8+n, 2c+1)
+        float alpha[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const float s0 = ok0 ? sacc[i] * qs : -INFINITY, s1 = ok1 ? sacc[2 + i] * qs : -INFINITY;
+            float tmax = fmaxf(s0, s1);
+            tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 4));
+            tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 8));
+            tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 16));
+            const float m_new = fmaxf(m[i], tmax);
+            const float msub = m_new > -INFINITY ? m_new : 0.f;     // no valid token yet: exp2(-inf - 0) = 0
+            alpha[i] = fast_exp2(m[i] - msub);
+            pr[i] = fast_exp2(s0 - msub);
+            pr[2 + i] = fast_exp2(s1 - msub);
+            l[i] = l[i] * alpha[i] + (pr[i] + pr[2 + i]);
+            m[i] = m_new;
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            oacc[i][0] *= alpha[0];
+            oacc[i][1] *= alpha[1];
+            oacc[i][2] *= alpha[0];
+            oacc[i][3] *= alpha[1];
+        }
+        // P^T as the B operand: transpose the 8-key x 8-head blocks of the score fragment
+        const uint32_t pb0 = movmatrix_trans(M16::pack(pr[0], pr[1]));      // head n; keys 2c, 2c + 1
+        const uint32_t pb1 = movmatrix_trans(M16::pack(pr[2], pr[3]));      // head n; keys 8 + 2c, 9 + 2c
+        // O^T += V^T P^T: A = transposed 8-key x 8-dim blocks (low halves -> rows 0..7, high -> rows 8..15)
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            uint32_t w0[4], w1[4];
+            lds128(base + ((0 * 2 + 1) * 2 + j) * 512, w0);
+            lds128(base + ((1 * 2 + 1) * 2 + j) * 512, w1);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                __half2 lo0, hi0, lo1, hi1;
+                e4m3x4_to_half2x2(w0[e], lo0, hi0);
+                e4m3x4_to_half2x2(w1[e], lo1, hi1);
+                const uint32_t a[4] = {movmatrix_trans(u32(lo0)), movmatrix_trans(u32(hi0)), movmatrix_trans(u32(lo1)),
+                                       movmatrix_trans(u32(hi1))};
+                M16::run(oacc[4 * j + e], a, pb0, pb1);
             }
         }
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
-    l += __shfl_xor_sync(0xffffffffu, l, 1);
-    l += __shfl_xor_sync(0xffffffffu, l, 2);
-    if (n < G) {
-        const float vs = p.v_scale ? p.v_scale[hk] : 1.f;
-        float* row = p.part + ((int64_t)u * p.H + hk * G + n) * (D + 2);
-        // output block (j, e, h) of this lane: dims (4j + c) * 16 + 4e + 2h + {0, 1}
+    // the eight lanes with this lane's c hold disjoint keys: fold their denominators
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        l[i] += __shfl_xor_sync(0xffffffffu, l[i], 4);
+        l[i] += __shfl_xor_sync(0xffffffffu, l[i], 8);
+        l[i] += __shfl_xor_sync(0xffffffffu, l[i], 16);
+    }
+    const float vs = p.v_scale ? p.v_scale[hk] : 1.f;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int hq = 2 * c + i;
+        if (hq >= G) continue;
+        float* row = p.part + ((int64_t)u * p.H + hk * G + hq) * (D + 2);
+        // block (j, e): row n of the low-half block is dim (4j + n/2) * 16 + 4e + n%2, of the high-half block + 2
 #pragma unroll
         for (int j = 0; j < 2; ++j)
 #pragma unroll
-            for (int e = 0; e < 4; ++e)
-#pragma unroll
-                for (int hh = 0; hh < 2; ++hh)
-                    *reinterpret_cast<float2*>(row + (4 * j + c) * 16 + 4 * e + 2 * hh) =
-                        make_float2(oacc[(j * 4 + e) * 2 + hh][0] * vs, oacc[(j * 4 + e) * 2 + hh][1] * vs);
-        if (c == 0) *reinterpret_cast<float2*>(row + D) = make_float2(m, l);
+            for (int e = 0; e < 4; ++e) {
+                const int d = (4 * j + (n >> 1)) * 16 + 4 * e + (n & 1);
+                row[d] = oacc[4 * j + e][i] * vs;
+                row[d + 2] = oacc[4 * j + e][2 + i] * vs;
+            }
+        if (n == 0) *reinterpret_cast<float2*>(row + D) = make_float2(m[i], l[i]);
     }
 }
