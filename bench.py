@@ -138,6 +138,21 @@ def seeded_lengths(n, lo, hi, seed):
     return torch.randint(lo, hi + 1, (n,), generator=g)
 
 
+def quantize_e4m3_per_head(x: torch.Tensor, heads: int, rows_per_chunk: int = 1 << 17):
+    """[rows, heads*D] -> (e4m3 codes, float32 scales [heads]) with scale_h = absmax_h / 448, on x's device."""
+    rows, dim = x.shape
+    D = dim // heads
+    amax = torch.zeros(heads, device=x.device)
+    for r in range(0, rows, rows_per_chunk):
+        amax = torch.maximum(amax, x[r:r + rows_per_chunk].view(-1, heads, D).abs().amax(dim=(0, 2)).float())
+    scale = (amax / 448.0).clamp_min(1e-12)
+    out = torch.empty(rows, dim, dtype=torch.float8_e4m3fn, device=x.device)
+    for r in range(0, rows, rows_per_chunk):
+        c = x[r:r + rows_per_chunk].float().view(-1, heads, D)
+        out[r:r + rows_per_chunk] = (c / scale.view(1, heads, 1)).to(torch.float8_e4m3fn).view(-1, dim)
+    return out, scale
+
+
 def fill_normal(t: torch.Tensor, rows_per_chunk: int = 1 << 18):
     for r in range(0, t.size(0), rows_per_chunk):
         t[r:r + rows_per_chunk].normal_()
@@ -812,7 +827,8 @@ class PagedPrefill(Prefill):
 
 
 class GqaDecode(Workload):
-    """Grouped-query paged decode (not in the reference): 32 query heads over 8 KV heads, fp16 pools."""
+    """Grouped-query paged decode (not in the reference): 32 query heads over 32 / group KV heads
+    (`--gqa-group`, default 4), fp16 or e4m3 pools (`--gqa-kv`)."""
     name, metric, unit, dtype = "gqa_decode", "paged_decode_kv_read_bandwidth", "TB/s", "f16"
     B, H, HKV, D, LO, HI, SEED = 64, 32, 8, 128, 1024, 32768, 4
 
@@ -820,6 +836,9 @@ class GqaDecode(Workload):
         import attention_impl_b200 as A
         self.A = A
         dev = self.dev
+        self.HKV = self.H // self.args.gqa_group
+        self.fp8 = self.args.gqa_kv == "e4m3"
+        self.kv_el = 1 if self.fp8 else 2
         self.lens_ = seeded_lengths(self.args.batch or self.B, self.LO, self.HI, self.SEED)
         self.Bn, self.T = len(self.lens_), int(self.lens_.sum())
         torch.manual_seed(4100 + self.rank)
@@ -828,19 +847,25 @@ class GqaDecode(Workload):
         self.Vc = torch.empty(self.T, kvdim, dtype=torch.float16, device=dev)
         fill_normal(self.Kc)
         fill_normal(self.Vc)
+        self.kw = {}
+        if self.fp8:       # per-head absmax scales, as in the long-context workload
+            self.Kc, ks = quantize_e4m3_per_head(self.Kc, self.HKV)
+            self.Vc, vs = quantize_e4m3_per_head(self.Vc, self.HKV)
+            self.kw = dict(k_scale=ks, v_scale=vs)
         self.ci = torch.randperm(self.T, device=dev).to(torch.int32)
         self.off = self.lens_.cumsum(0).to(torch.int32).to(dev)
         self.Q = torch.randn(self.Bn, self.H * self.D, device=dev, dtype=torch.float16)
         self.K, self.V = (torch.randn(self.Bn, kvdim, device=dev, dtype=torch.float16) for _ in range(2))
         self.O = torch.empty_like(self.Q)
-        self.chunk = A.ops.pick_chunk(self.Bn, self.HKV, self.D, self.T, dev, group=self.H // self.HKV, kv_dtype=0)
+        self.chunk = A.ops.pick_chunk(self.Bn, self.HKV, self.D, self.T, dev, group=self.H // self.HKV,
+                                      kv_dtype=3 if self.fp8 else 0)
         self.ws = torch.empty(A.ops.decode_workspace_bytes(self.Bn, self.H, self.D, self.T, self.chunk),
                               dtype=torch.uint8, device=dev)
 
     def _call(self, stages):
         self.A.paged_kv_attention_forward(self.Q, self.K, self.V, self.Kc, self.Vc, self.ci, self.off, self.H,
                                           return_sp=False, chunk=self.chunk, workspace=self.ws, out=self.O,
-                                          stages=stages)
+                                          stages=stages, **self.kw)
 
     def step(self):
         self._call(3)
@@ -856,12 +881,12 @@ class GqaDecode(Workload):
     def e2e_step(self):
         dQ, dK, dV, dci, doff = (x.to(self.dev, non_blocking=True) for x in self.h_in)
         o = self.A.paged_kv_attention_forward(dQ, dK, dV, self.Kc, self.Vc, dci, doff, self.H, return_sp=False,
-                                              max_context_len=int(self.lens_.max()))[2]
+                                              max_context_len=int(self.lens_.max()), **self.kw)[2]
         self.h_out.copy_(o, non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
     def units_per_step_rank(self):
-        return 2.0 * self.T * self.HKV * self.D * 2
+        return 2.0 * self.T * self.HKV * self.D * self.kv_el
 
     def sequences_per_step(self):
         return self.Bn
@@ -870,11 +895,13 @@ class GqaDecode(Workload):
         return 2
 
     def kernel_name(self):
-        return "paged_decode_gqa_mma_kernel<half,4>"
+        g = self.H // self.HKV
+        return f"paged_decode_gqa_mma_e4m3_kernel<half,{g}>" if self.fp8 else f"paged_decode_gqa_mma_kernel<half,{g}>"
 
     def static_config(self):
         return {"workload": "grouped_query_paged_decode", "batch": self.args.batch or self.B, "heads": self.H,
-                "kv_heads": self.HKV, "head_dim": self.D, "ctx_range": [self.LO, self.HI]}
+                "kv_heads": self.H // self.args.gqa_group, "kv_dtype": self.args.gqa_kv, "head_dim": self.D,
+                "ctx_range": [self.LO, self.HI]}
 
     def config(self):
         per = self.units_per_step_rank()
@@ -882,13 +909,19 @@ class GqaDecode(Workload):
                     chunk=self.chunk, l2=f"inputs larger than L2 ({per / 1e9:.1f} GB of KV per step)")
 
     def _sample(self, n_seq):
+        from oracle import attention_oracle as orc
         T = int(self.lens_[:n_seq].sum())
         rows = self.ci[:T].long()
         order = torch.argsort(rows)
         rank_of = torch.empty_like(order)
         rank_of[order] = torch.arange(T, device=self.dev)
-        return (self.Q[:n_seq].cpu(), self.K[:n_seq].cpu(), self.V[:n_seq].cpu(), self.Kc[rows[order]].cpu(),
-                self.Vc[rows[order]].cpu(), rank_of.int().cpu(), self.off[:n_seq].cpu()), T
+        Kc, Vc = self.Kc[rows[order]].cpu(), self.Vc[rows[order]].cpu()
+        Q, K, V = self.Q[:n_seq].cpu(), self.K[:n_seq].cpu(), self.V[:n_seq].cpu()
+        if self.fp8:       # the oracle runs on the dequantised pools
+            Kc = orc.dequantize_e4m3_per_head(Kc, self.kw["k_scale"].cpu(), self.HKV)
+            Vc = orc.dequantize_e4m3_per_head(Vc, self.kw["v_scale"].cpu(), self.HKV)
+            Q, K, V = Q.float(), K.float(), V.float()
+        return (Q, K, V, Kc, Vc, rank_of.int().cpu(), self.off[:n_seq].cpu()), T
 
     def cpu_baseline(self):
         from oracle import attention_oracle as orc
@@ -898,12 +931,13 @@ class GqaDecode(Workload):
         O32 = orc.paged_decode(*inputs, self.H, compute_dtype=torch.float32)[2]
         self.step()
         torch.cuda.synchronize()
-        err = (self.O[:n_seq].cpu().float() - O32.float()).abs().max().item()
-        kv_bytes = 2 * T * self.HKV * self.D * 2
+        diff = self.O[:n_seq].cpu().float() - O32.float()
+        kv_bytes = 2 * T * self.HKV * self.D * self.kv_el
+        par = ({"rel_err": (diff.norm() / O32.float().norm()).item(), "tolerance": 2e-2} if self.fp8
+               else {"max_abs_err_vs_fp32_oracle": diff.abs().max().item(), "tolerance": 2e-3})
         return ({"value": kv_bytes / sec / 1e12, "unit": "TB/s", "cores": torch.get_num_threads(), "kind": "port",
                  "sample": f"first {n_seq} of {self.Bn} sequences ({T} tokens)", "seconds": sec,
-                 "torch": torch.__version__},
-                {"max_abs_err_vs_fp32_oracle": err, "tolerance": 2e-3, "sequences_checked": n_seq})
+                 "torch": torch.__version__}, dict(par, sequences_checked=n_seq))
 
     def reference_run(self, steps, warmup):
         from oracle import attention_oracle as orc
@@ -1358,6 +1392,8 @@ def main():
     ap.add_argument("--batch", type=int, default=None, help="override the batch size (profiling a small case)")
     ap.add_argument("--exchange", default="nccl", choices=["nccl", "peer", "peer_graph", "peer_unfused"],
                     help="fp8_split: how the partial rows travel between ranks")
+    ap.add_argument("--gqa-group", type=int, default=4, choices=[2, 4, 8], help="gqa_decode: query heads per KV head")
+    ap.add_argument("--gqa-kv", default="f16", choices=["f16", "e4m3"], help="gqa_decode: type of the KV pools")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (profiling runs)")
     ap.add_argument("--no-secondary", action="store_true",
                     help="default workload at 1 GPU: skip the short legs of the other configurations")
