@@ -1197,7 +1197,7 @@ extern "C" int attn_b200_paged_decode_single_launch_ok(int B, int H, int n_kv_he
     if (B <= 0 || H <= 0 || n_kv_heads != H || block_size > 1 || kv_dtype != q_dtype) return 0;
     if (!(q_dtype == ATTN_B200_F16 || q_dtype == ATTN_B200_BF16) || !(D == 64 || D == 128 || D == 256)) return 0;
     const int64_t ctas = (int64_t)B * H;
-    return ctas >= sm_count && ctas <= 2LL * sm_count && n_tokens / B <= 2048;
+    return ctas >= sm_count && ctas <= 2LL * sm_count && n_tokens / B <= 1024;
 }
 
 extern "C" int attn_b200_paged_decode_pick_chunk_gqa(int B, int n_kv_heads, int group, int D, int kv_dtype,

@@ -143,7 +143,9 @@ ATTN_B200_API int attn_b200_paged_decode(const void* q, const void* k_new, const
 
 ATTN_B200_API size_t attn_b200_paged_decode_workspace_bytes(int B, int H, int D, int64_t n_tokens, int chunk);
 /* Non-zero when the single-launch form (`stages` = 4) exists for this case and is expected to beat
- * the two-launch form: sm_count <= B*H <= 2*sm_count and at most 2048 tokens of capacity per sequence. */
+ * the two-launch form: sm_count <= B*H <= 2*sm_count and at most 1024 tokens of capacity per sequence on
+ * average (a CTA lives as long as its sequence is long: one long sequence among short ones would
+ * hold the step). */
 ATTN_B200_API int attn_b200_paged_decode_single_launch_ok(int B, int H, int n_kv_heads, int D, int64_t n_tokens,
                                                           int block_size, int q_dtype, int kv_dtype, int sm_count);
 /* Heuristic chunk length: enough (chunk, head-group) work items to fill `sm_count` SMs. */
