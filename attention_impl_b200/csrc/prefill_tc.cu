@@ -80,18 +80,14 @@ constexpr int THREADS2 = 384;   // 3 warpgroups: softmax 0, softmax 1, {TMA, MMA
 // instruction of a warp touches 32 different rows, 8 KB apart: 32 sectors per instruction, about two
 // thousand LSU clocks per tile, as long as a whole key-tile step; staged, it is a few hundred.
 struct OutStage {
-    unsigned char* buf;          // 16 KB, 1024-byte aligned, private to the warpgroup
-    const CUtensorMap* map;      // output tensor [n_tokens, H*128], box 64 x 128, 128-byte swizzle
+    unsigned char* buf;          // 16 KB, 1024-byte aligned, private to the warpgroup: 4 KB per warp
+    const CUtensorMap* map;      // output tensor [n_tokens, H*128], box 32 columns x 32 rows, 64-byte swizzle
     int row0;                    // first row of the tile in the packed buffer
-    int bar_id;                  // named barrier of the warpgroup (128 threads)
 };
 
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* src, int x, int y) {
     asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
                  ::"l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(src)) : "memory");
-}
-__device__ __forceinline__ void named_bar_sync(int id, int n_threads) {
-    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(n_threads) : "memory");
 }
 
 // One softmax thread = one query row (TMEM lane) of a 128-row tile: walks the key tiles, turns S into
@@ -239,7 +235,13 @@ __device__ __forceinline__ void softmax_row(unsigned long long* s_full, unsigned
             const float inv = 1.f / l;
             const int64_t row = out_row;
             if (kStaged && stage->buf) {
-                // whole tile inside the sequence, 16-bit output: through shared memory and TMA
+                // Whole tile inside the sequence, 16-bit output: through shared memory and TMA, every
+                // warp by itself.  A warp's 4 KB of staging are two buffers of [32 rows x 32
+                // columns]; the row's four quarters go through them in turn, each followed by the
+                // warp's own TMA store, and a buffer is rewritten once the store that read it two
+                // quarters earlier has finished reading (cp.async.bulk.wait_group.read 1).  Nothing
+                // waits for the last two stores here: the next read-out (or the end of the kernel)
+                // does.  No barrier across warps is involved.
                 float ov[HD];
 #pragma unroll
                 for (int c = 0; c < 4; ++c) tmem_ld32_nowait(o_addr + c * 32, ov + c * 32);
@@ -248,26 +250,33 @@ __device__ __forceinline__ void softmax_row(unsigned long long* s_full, unsigned
                     tc_fence_before();
                     mbar_arrive(o_free);
                 }
-                const uint32_t sbase = smem_u32(stage->buf) + (uint32_t)r * 128u;
+                const int lr = r & 31, wq = (r >> 5) & 3;
+                unsigned char* const wbuf = stage->buf + wq * 4096;
+                if (lr == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // the previous read-out's stores
+                __syncwarp();
 #pragma unroll
-                for (int half = 0; half < 2; ++half) {
+                for (int qt = 0; qt < 4; ++qt) {
+                    unsigned char* const sub = wbuf + (qt & 1) * 2048;
+                    if (qt >= 2) {
+                        if (lr == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                        __syncwarp();
+                    }
+                    const uint32_t sbase = smem_u32(sub) + (uint32_t)lr * 64u;
 #pragma unroll
-                    for (int c = 0; c < 8; ++c) {              // 16-byte chunk c of this row's 64 columns
-                        const float* o8 = ov + half * 64 + c * 8;
-                        const uint32_t dst = sbase + (uint32_t)((c ^ (r & 7)) << 4);
+                    for (int c = 0; c < 4; ++c) {              // 16-byte chunk c of this row's 32 columns
+                        const float* o8 = ov + qt * 32 + c * 8;
+                        const uint32_t dst = sbase + (uint32_t)((c ^ ((lr >> 1) & 3)) << 4);
                         asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst),
                                      "r"(pack2<T>(o8[0] * inv, o8[1] * inv)), "r"(pack2<T>(o8[2] * inv, o8[3] * inv)),
                                      "r"(pack2<T>(o8[4] * inv, o8[5] * inv)), "r"(pack2<T>(o8[6] * inv, o8[7] * inv))
                                      : "memory");
                     }
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                    named_bar_sync(stage->bar_id, 128);
-                    if (r == 0) {
-                        tma_store_2d(stage->map, stage->buf, h * HD + half * 64, stage->row0);
+                    __syncwarp();
+                    if (lr == 0) {
+                        tma_store_2d(stage->map, sub, h * HD + qt * 32, stage->row0 + wq * 32);
                         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-                        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");     // the buffer has been read
                     }
-                    named_bar_sync(stage->bar_id, 128);
                 }
             } else {
 #pragma unroll
@@ -332,18 +341,25 @@ struct LaunchState {
 constexpr int kLaunchSlots = 64;
 static __device__ LaunchState g_launch[kLaunchSlots];
 
+struct Item2p {
+    int tp, h, b, L, q0, n0, n1, nmax;
+    int64_t seq_beg;
+    bool valid;
+};
+
 struct SmemLayout2p {
     alignas(1024) unsigned char q[2][TILE_BYTES];
     alignas(1024) unsigned char k[STAGES][TILE_BYTES];
     alignas(1024) unsigned char v[STAGES][TILE_BYTES];
     alignas(1024) unsigned char o_stage[2][SUB_BYTES];     // output staging, one [128 x 64] box per warpgroup
     alignas(8) unsigned long long q_full[2], q_empty[2];
-    // item_id[n & 3] = n-th item of this CTA (-1: no more work), published by the producer.  The
-    // producer draws item n only after it has issued every K/V tile of item n-1, which needs both
-    // streams and therefore both softmax warpgroups to be inside item n-1 or later; slot n & 3 was
-    // last read at the start of item n-4, so it is free.
+    // item[n & 3] = n-th item of this CTA, decoded (tp < 0: no more work), published by the producer:
+    // the other roles start an item from shared memory and never wait for the offsets to come from
+    // global memory.  The producer draws item n only after it has issued every K/V tile of item
+    // n-1, which needs both streams and therefore both softmax warpgroups to be inside item n-1 or
+    // later; slot n & 3 was last read at the start of item n-4, so it is free.
     unsigned long long item_full[4];
-    long long item_id[4];
+    Item2p item[4];
     unsigned long long s_full[2], p_half[2], p_full[2], o_full[2], o_free[2];
     unsigned long long k_full[STAGES], k_empty[STAGES], v_full[STAGES], v_empty[STAGES];
     unsigned int tmem_base;
@@ -356,11 +372,6 @@ struct SmemLayout2p {
 // head) combinations, which stay in L2 (with the pair index slowest over ALL combinations every CTA
 // would stream its own K/V from DRAM: measured 814 against 960 TFLOP/s).
 constexpr int ITEM_GROUP = 16;
-struct Item2p {
-    int tp, h, b, L, q0, n0, n1, nmax;
-    int64_t seq_beg;
-    bool valid;
-};
 __device__ __forceinline__ Item2p decode_item(const Params& p, int64_t id) {
     Item2p it;
     const int per_group = p.n_qtiles * ITEM_GROUP;
@@ -442,7 +453,7 @@ prefill_tc2p_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             bool ok = true;
             while (ok) {
                 // draw the next non-empty item (empty ones: pairs past the end of a short sequence)
-                Item2p it;
+                Item2p it = {};
                 long long id;
                 do {
                     id = (long long)atomicAdd(work_counter, 1ull);
@@ -450,7 +461,8 @@ prefill_tc2p_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                     it = decode_item(p, id);
                     if (!it.valid && p.err_flag) atomicOr(p.err_flag, ATTN_B200_FLAG_BAD_OFFSETS);
                 } while (!it.valid || it.q0 >= it.L);
-                sm.item_id[n_it & 3] = id;
+                if (id < 0) it.tp = -1;
+                sm.item[n_it & 3] = it;
                 mbar_arrive(&sm.item_full[n_it & 3]);
                 if (id < 0) break;
                 const int col0 = it.h * HD;
@@ -531,9 +543,8 @@ prefill_tc2p_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             bool ok = true;
             while (ok) {
                 if (!(ok = mbar_wait_spin(&sm.item_full[n & 3], (n >> 2) & 1, wc))) break;
-                const long long id = sm.item_id[n & 3];
-                if (id < 0) break;
-                const Item2p it = decode_item(p, id);
+                const Item2p it = sm.item[n & 3];
+                if (it.tp < 0) break;
                 // Within an item the warpgroup with the upper query tile is served first in every
                 // round: it has one key tile more and (after an early start) is one tile ahead.
                 const int wu = (n & 1) ? 0 : 1, wl = wu ^ 1;
@@ -564,8 +575,7 @@ prefill_tc2p_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                         // but the alternation of the two warpgroups is lost and long ones lose more.)
                         const int G1 = g + it.nmax;
                         if (mbar_test(&sm.item_full[(n + 1) & 3], ((n + 1) >> 2) & 1)) {
-                            const long long id1 = sm.item_id[(n + 1) & 3];
-                            if (id1 >= 0 && decode_item(p, id1).n1 > 0 && mbar_test(&sm.q_full[wl], (uses[wl] + 1) & 1) &&
+                            if (sm.item[(n + 1) & 3].tp >= 0 && sm.item[(n + 1) & 3].n1 > 0 && mbar_test(&sm.q_full[wl], (uses[wl] + 1) & 1) &&
                                 mbar_test(&sm.k_full[G1 & 1], (G1 >> 1) & 1)) {
                                 tc_fence_after();
                                 issue_qk(wl, G1 & 1);
@@ -620,9 +630,8 @@ prefill_tc2p_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         int c0 = 0;
         for (int n_it = 0;; ++n_it) {
             if (!mbar_wait(&sm.item_full[n_it & 3], (n_it >> 2) & 1, wc)) break;
-            const long long id = sm.item_id[n_it & 3];
-            if (id < 0) break;
-            const Item2p it = decode_item(p, id);
+            const Item2p it = sm.item[n_it & 3];
+            if (it.tp < 0) break;
             if (wc->abort) break;
             const int u = upper_of(w, n_it);
             const int nk = u ? it.n1 : it.n0;
@@ -630,12 +639,14 @@ prefill_tc2p_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             const int tq = 2 * it.tp + u;
             // staged read-out when the tile lies wholly inside the sequence and the output is 16-bit
             const bool whole = it.q0 + u * BM + BM <= it.L && !p.out_f32;
-            const OutStage stage{whole ? sm.o_stage[w] : nullptr, &map_o, (int)(it.seq_beg + it.q0 + u * BM), 1 + w};
+            const OutStage stage{whole ? sm.o_stage[w] : nullptr, &map_o, (int)(it.seq_beg + it.q0 + u * BM)};
             softmax_row<T, 2, true>(&sm.s_full[w], &sm.p_half[w], &sm.p_full[w], &sm.o_full[w], s_addr, o_addr, nk, tq * BM + r, r, p,
                               wc, it.q0 + u * BM + r < it.L, it.seq_beg + it.q0 + u * BM + r, it.h, it.q0 < p.split_rows, c0,
                               &sm.o_free[w], &stage);
             c0 += nk;
         }
+        // the staged read-out leaves its last stores in flight: shared memory stays until they have read it
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
     }
     // ---------------------------------------------------------------------- teardown
     if (warp == 8 && lane == 0 && sm.box.abort) {
@@ -980,16 +991,17 @@ static EncodeTiledFn encode_fn() {
     return fn;
 }
 
-// [n_tokens, H*128] 16-bit row-major; box = 64 elements (128 B) x 128 rows, 128-byte swizzle.
-// A tensor map is a pure function of (base, n_tokens, H, dtype), so the last few are kept per host
-// thread: a serving loop that calls with the same buffers pays for the encoding once.
-static int make_map(CUtensorMap* map, const void* base, int64_t n_tokens, int H, int dtype) {
-    struct Entry { const void* base; int64_t n_tokens; int H, dtype; bool used; CUtensorMap map; };
+// [n_tokens, H*128] 16-bit row-major.  Loads: box = 64 elements (128 B) x 128 rows, 128-byte swizzle;
+// the output's stores (`store_box`): 32 elements (64 B) x 32 rows, 64-byte swizzle.
+// A tensor map is a pure function of (base, n_tokens, H, dtype, box), so the last few are kept per
+// host thread: a serving loop that calls with the same buffers pays for the encoding once.
+static int make_map(CUtensorMap* map, const void* base, int64_t n_tokens, int H, int dtype, bool store_box = false) {
+    struct Entry { const void* base; int64_t n_tokens; int H, dtype; bool store_box, used; CUtensorMap map; };
     constexpr int kEntries = 8;
     static thread_local Entry cache[kEntries] = {};
     static thread_local unsigned next = 0;
     for (const Entry& e : cache)
-        if (e.used && e.base == base && e.n_tokens == n_tokens && e.H == H && e.dtype == dtype) {
+        if (e.used && e.base == base && e.n_tokens == n_tokens && e.H == H && e.dtype == dtype && e.store_box == store_box) {
             *map = e.map;
             return 0;
         }
@@ -997,14 +1009,14 @@ static int make_map(CUtensorMap* map, const void* base, int64_t n_tokens, int H,
     if (!fn) return (int)cudaErrorNotSupported;
     const cuuint64_t dims[2] = {(cuuint64_t)H * HD, (cuuint64_t)n_tokens};
     const cuuint64_t strides[1] = {(cuuint64_t)H * HD * 2};
-    const cuuint32_t box[2] = {64, 128};
+    const cuuint32_t box[2] = {store_box ? 32u : 64u, store_box ? 32u : 128u};
     const cuuint32_t estr[2] = {1, 1};
     const CUresult r = fn(map, dtype == ATTN_B200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
                           2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                          store_box ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return (int)cudaErrorInvalidValue;
-    cache[next++ % kEntries] = Entry{base, n_tokens, H, dtype, true, *map};
+    cache[next++ % kEntries] = Entry{base, n_tokens, H, dtype, store_box, true, *map};
     return 0;
 }
 
@@ -1076,7 +1088,7 @@ int prefill_tc_launch(const void* q, const void* k, const void* v, const int32_t
         return rc;
     // the staged read-out stores 16-bit tiles through this map (fp32 output takes the direct path:
     // the map then describes the buffer as if it were 16-bit and is never used)
-    if ((rc = make_map(&mo, out, n_tokens, H, dtype))) return rc;
+    if ((rc = make_map(&mo, out, n_tokens, H, dtype, true))) return rc;
     DeviceState d;
     LaunchState* slot = nullptr;
     if ((rc = device_state(&d)) || (rc = take_launch_slot(d, st, &slot))) return rc;
