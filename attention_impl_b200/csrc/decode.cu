@@ -163,7 +163,11 @@ paged_decode_mha_kernel(const DecodeParams p) {
     __shared__ int32_t s_off[kMaxStagedB];
     // The combine kernel that follows is launched as a programmatic dependent: its CTAs may be
     // scheduled (and run their prologue up to griddepcontrol.wait) while this grid still runs.
+    // This grid is itself launched as a programmatic dependent of whatever kernel precedes it on
+    // the stream; if that kernel releases its dependents early (the combine of the previous decode
+    // step does), the launch latency is spent while it still runs.  Nothing is read before the wait.
     asm volatile("griddepcontrol.launch_dependents;");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     SeqBounds sb{stage_offsets(p, s_off), p.uniform_ctx, p.n_tokens};
 
     const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -805,10 +809,11 @@ struct CombineParams {
 };
 
 // One CTA of four warps per (b, h).  Every warp finds the global maximum and denominator (lanes over
-// units, the m and l of a unit loaded together: one round trip), then the numerator's units are
-// dealt to the warps round-robin, each warp keeping its row loads independent (8 in flight), and
-// the four partial sums meet in shared memory.  With one warp doing all units in turn the combine
-// took as long as the partial kernel on small batches (16.6 us against 15.0 at batch 8).
+// units, the m and l of a unit loaded together), the numerator's units are dealt to the warps
+// round-robin in batches of eight per warp whose loads are all independent and are requested
+// together with the (m, l) pairs, and the four partial sums meet in shared memory.  With one warp
+// doing all units in turn the combine took as long as the partial kernel on small batches (16.6 us
+// against 15.0 at batch 8).
 //
 // XCHG = true adds the two ends of the cross-GPU KV-split exchange, so that a step is three launches
 // (partial kernel, this kernel pushing, this kernel waiting) instead of five:
@@ -829,6 +834,9 @@ __global__ void __launch_bounds__(128)
 lse_combine_kernel(const CombineParams p) {
     __shared__ float s_acc[4][256];
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    // A kernel launched behind this one as a programmatic dependent (the partial kernel of the next
+    // decode step) may be scheduled from here on; it reads nothing before its own wait.
+    asm volatile("griddepcontrol.launch_dependents;");
     if constexpr (XCHG) {
         if (p.wait_flags) {
             if (threadIdx.x < p.n_parts) {
@@ -899,6 +907,28 @@ lse_combine_kernel(const CombineParams p) {
         mr[k] = in ? p.parts[(first + i * stride) * RS + D] : -INFINITY;
         lr[k] = in ? p.parts[(first + i * stride) * RS + D + 1] : 0.f;
     }
+    // The numerator's rows are requested in batches of KB units per warp, every load of a batch
+    // independent of the others, and the first batch together with the (m, l) pairs above: a
+    // (sequence, head) of up to 32 units costs ONE round trip to L2 after the grid dependency.
+    // (A loop with one unit per iteration paid a round trip per unit, up to seven in a row at
+    // batch 8: 5 us of a 22 us step.)
+    constexpr int KB = 8;
+    float rv[KB][8], mi[KB];
+    auto load_batch = [&](int i0, int dbase) {
+#pragma unroll
+        for (int u = 0; u < KB; ++u) {
+            const int i = i0 + 4 * u;
+            const bool in = i < count;
+            const float* row = p.parts + (first + (in ? i : 0) * stride) * RS;
+            mi[u] = in ? row[D] : -INFINITY;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const int d = dbase + k * 32 + lane;
+                rv[u][k] = (in && d < D) ? row[d] : 0.f;
+            }
+        }
+    };
+    load_batch(wid, 0);
     float M = fmaxf(fmaxf(mr[0], mr[1]), fmaxf(mr[2], mr[3]));
     for (int i = lane + 32 * KR; i < count; i += 32) M = fmaxf(M, p.parts[(first + i * stride) * RS + D]);
     if (p.k_new) M = fmaxf(M, s_new);
@@ -922,15 +952,13 @@ lse_combine_kernel(const CombineParams p) {
         float acc[8];
 #pragma unroll
         for (int k = 0; k < 8; ++k) acc[k] = 0.f;
-#pragma unroll 8
-        for (int i = wid; i < count; i += 4) {
-            const float* row = p.parts + (first + i * stride) * RS;
-            const float mi = row[D];
-            const float wi = mi > -INFINITY ? exp2f(mi - M) : 0.f;
+        for (int i0 = wid; i0 < count; i0 += 4 * KB) {
+            if (dbase > 0 || i0 > wid) load_batch(i0, dbase);
 #pragma unroll
-            for (int k = 0; k < 8; ++k) {
-                const int d = dbase + k * 32 + lane;
-                if (d < D) acc[k] = fmaf(row[d], wi, acc[k]);
+            for (int u = 0; u < KB; ++u) {
+                const float wi = mi[u] > -INFINITY ? exp2f(mi[u] - M) : 0.f;
+#pragma unroll
+                for (int k = 0; k < 8; ++k) acc[k] = fmaf(rv[u][k], wi, acc[k]);
             }
         }
         if (dbase > 0) __syncthreads();          // the previous sweep's sums have been read
@@ -986,13 +1014,21 @@ template <typename QT, typename KVT>
 static int launch_mha(const DecodeParams& p, int warps, int64_t n_units, cudaStream_t st) {
     const int64_t blocks = n_units * p.head_groups;
     if (blocks > 0x7fffffffLL) return ATTN_B200_ETOOLARGE;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)blocks);
+    cfg.blockDim = dim3((unsigned)(warps * 32));
+    cfg.stream = st;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
     switch (p.D) {
-        case 64: paged_decode_mha_kernel<QT, KVT, 64><<<(unsigned)blocks, warps * 32, 0, st>>>(p); break;
-        case 128: paged_decode_mha_kernel<QT, KVT, 128><<<(unsigned)blocks, warps * 32, 0, st>>>(p); break;
-        case 256: paged_decode_mha_kernel<QT, KVT, 256><<<(unsigned)blocks, warps * 32, 0, st>>>(p); break;
+        case 64: return (int)cudaLaunchKernelEx(&cfg, paged_decode_mha_kernel<QT, KVT, 64>, p);
+        case 128: return (int)cudaLaunchKernelEx(&cfg, paged_decode_mha_kernel<QT, KVT, 128>, p);
+        case 256: return (int)cudaLaunchKernelEx(&cfg, paged_decode_mha_kernel<QT, KVT, 256>, p);
         default: return ATTN_B200_ESHAPE;
     }
-    return (int)cudaGetLastError();
 }
 
 #include "decode_gqa.cuh"

@@ -158,9 +158,13 @@ def paged_kv_attention_forward(Q, K, V, K_cache, V_cache, cache_indices, offsets
     sequence b lives in pool row ``cache_indices[b, t // block_size] * block_size + t % block_size``.
     ``single_launch``: run the step as ONE kernel, a CTA per (sequence, head) that combines in shared
     memory (multi-head attention over 16-bit pools, per-token table, head_dim 64/128/256, no S/P).
-    ``None`` (default) takes it when S and P are not requested and the library's heuristic expects it
-    to win: the (sequence, head) pairs alone fill the machine in one wave and sequences are short (a
-    batch of 8 with 32 heads); ``True`` forces it (RuntimeError if the case is not covered).
+    ``None`` (default) takes it for an EAGER call when S and P are not requested and the library's
+    heuristic covers the case: the (sequence, head) pairs alone fill the machine in one wave and
+    sequences are short (a batch of 8 with 32 heads).  There the host bounds the call (32 us against
+    42 us per call for the two launches and their scratch allocation).  While the stream is being
+    captured into a CUDA graph the default is the two-kernel form, whose step is shorter on the GPU
+    (18 against 21 us at that shape).  ``True`` forces the single launch (RuntimeError if the case is
+    not covered), ``False`` the two kernels.
     """
     for t, n in ((Q, "Q"), (K, "K"), (V, "V"), (K_cache, "K_cache"), (V_cache, "V_cache")):
         _check_input(t, n)
@@ -203,8 +207,9 @@ def paged_kv_attention_forward(Q, K, V, K_cache, V_cache, cache_indices, offsets
         if chunk is None:
             chunk = pick_chunk(B, Hkv, D, T, dev, group=H // Hkv, kv_dtype=kvd)
         if single_launch is None:
-            single_launch = (not return_sp and stages == 3 and bool(lib.attn_b200_paged_decode_single_launch_ok(
-                B, H, Hkv, D, T, block_size, qd, kvd, sm_count(dev))))
+            single_launch = (not return_sp and stages == 3 and not torch.cuda.is_current_stream_capturing()
+                             and bool(lib.attn_b200_paged_decode_single_launch_ok(
+                                 B, H, Hkv, D, T, block_size, qd, kvd, sm_count(dev))))
         elif single_launch and return_sp:
             raise RuntimeError("single_launch=True does not produce S and P: pass return_sp=False")
         if single_launch:

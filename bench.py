@@ -438,11 +438,11 @@ class SmallDecode(LargeDecode):
         return None
 
     def kernel_name(self):
-        return (f"paged_decode_seq_kernel<half,128> (one launch per decode step: a CTA per (sequence, head), combine "
-                f"in shared memory); {self.INNER} decode steps per CUDA-graph launch, timed as a whole")
+        return (f"paged_decode_mha_kernel<half,half,128> + lse_combine_kernel<half> (programmatic dependent launch); "
+                f"{self.INNER} decode steps per CUDA-graph launch, timed as a whole")
 
     def launches_per_step(self):
-        return 1
+        return 2
 
     LABEL = "small_batch_paged_decode"
     E2E_NOTE = None
