@@ -50,6 +50,7 @@ struct DecodeParams {
     int G;            // query heads per KV head
     int block_size;   // tokens per KV block; 1 = `slots` is a per-token table
     int max_blocks;   // block_size > 1: `slots` is a [B, max_blocks] block table
+    int tables_ready; // `slots` and `offsets` were complete before the kernel preceding this launch started
 };
 
 // Pool row of token `t` (absolute index in the token stream) of the unit's sequence, or -1.
@@ -149,7 +150,17 @@ template <> struct RowChunk<__nv_fp8_e4m3, 16> {
 // group keeps its own softmax state and nothing is merged across groups.  A tile is 8 tokens; its
 // 8 K-row and 8 V-row loads are issued, then consumed.  With many CTAs per SM in different phases
 // the memory pipe stays full: this is the form for long units (large batches, long contexts).
-template <typename QT, typename KVT, int D>
+//
+// The grid is launched as a programmatic dependent of whatever kernel precedes it on the stream: if
+// that kernel releases its dependents early (the combine of the previous decode step and the RoPE /
+// cache-append kernel do), this grid's launch latency is spent while it still runs.  Nothing the
+// preceding kernel may have written is read before griddepcontrol.wait.  EARLY = true (the caller
+// vouches that the slot table and the offsets were complete before the preceding kernel STARTED:
+// they came from an upload, not from that kernel) also finds the CTA's unit and fetches its first
+// slots before the wait, so that two of the prologue's three dependent round trips overlap the
+// preceding kernel's tail.  This grid releases its own dependent (the combine kernel, which reads the
+// step's inputs before its own wait) only after its wait: those inputs are complete by then.
+template <typename QT, typename KVT, int D, bool EARLY>
 __global__ void __launch_bounds__(256)
 paged_decode_mha_kernel(const DecodeParams p) {
     constexpr int EPL = 16 / (int)sizeof(KVT);   // elements per lane (one 16-byte slice)
@@ -161,13 +172,10 @@ paged_decode_mha_kernel(const DecodeParams p) {
     static_assert(LPR >= 1 && LPR <= 32 && TILE <= 32, "unsupported head_dim");
 
     __shared__ int32_t s_off[kMaxStagedB];
-    // The combine kernel that follows is launched as a programmatic dependent: its CTAs may be
-    // scheduled (and run their prologue up to griddepcontrol.wait) while this grid still runs.
-    // This grid is itself launched as a programmatic dependent of whatever kernel precedes it on
-    // the stream; if that kernel releases its dependents early (the combine of the previous decode
-    // step does), the launch latency is spent while it still runs.  Nothing is read before the wait.
-    asm volatile("griddepcontrol.launch_dependents;");
-    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if constexpr (!EARLY) {
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        asm volatile("griddepcontrol.launch_dependents;");
+    }
     SeqBounds sb{stage_offsets(p, s_off), p.uniform_ctx, p.n_tokens};
 
     const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -176,6 +184,17 @@ paged_decode_mha_kernel(const DecodeParams p) {
     const int h_raw = ((blockIdx.x % p.head_groups) * warps + warp) * HPW + grp;
     Unit un;
     if (!resolve_unit(u, p.B, p.chunk, sb, un) || h_raw - grp >= p.H) return;
+    int early_slot = -1;
+    if constexpr (EARLY) {
+        const int64_t t = un.tbeg + lane;
+        if (lane < TILE && t < un.tend) {
+            const int64_t v = p.slots ? (int64_t)p.slots[t] : t;
+            if (v >= 0 && v < p.n_slots) early_slot = (int)v;
+            else if (p.err_flag) atomicOr(p.err_flag, ATTN_B200_FLAG_BAD_SLOT);
+        }
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        asm volatile("griddepcontrol.launch_dependents;");
+    }
     const bool h_ok = h_raw < p.H;               // trailing groups of the last warp may have no head
     const int h = h_ok ? h_raw : p.H - 1;
     const int64_t row_bytes = (int64_t)p.H * D * sizeof(KVT);
@@ -216,7 +235,9 @@ paged_decode_mha_kernel(const DecodeParams p) {
         return s;
     };
 
-    int next_slot = load_slot(un.tbeg);
+    int next_slot;
+    if constexpr (EARLY) next_slot = early_slot;
+    else next_slot = load_slot(un.tbeg);
     for (int64_t t0 = un.tbeg; t0 < un.tend; t0 += TILE) {
         const int my_slot = next_slot;
         uint4 kr[U], vr[U];
@@ -893,6 +914,14 @@ lse_combine_kernel(const CombineParams p) {
         for (int d = lane; d < D; d += 32) acc = fmaf(to_f32<QT>(qp[d]), to_f32<QT>(kp[d]), acc);
         s_new = group_sum<32>(acc) * p.scale_log2;
     }
+    float v_pre[2] = {0.f, 0.f};                 // the new token's value at this thread's two dims of the first sweep
+    if (p.k_new) {
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            const int d = threadIdx.x + 128 * k;
+            if (d < D) v_pre[k] = to_f32<QT>(((const QT*)p.v_new)[((int64_t)b * (p.H / p.G) + h / p.G) * D + d]);
+        }
+    }
     // Launched as a programmatic dependent of the partial kernel (see run_combine): the CTA may have
     // started while that grid was still running; from here on its rows are needed.  Without such a
     // launch relation the instruction returns at once.
@@ -965,10 +994,14 @@ lse_combine_kernel(const CombineParams p) {
 #pragma unroll
         for (int k = 0; k < 8; ++k) s_acc[wid][k * 32 + lane] = acc[k];
         __syncthreads();
-        for (int dd = threadIdx.x; dd < 256 && dbase + dd < D; dd += 128) {
-            const int d = dbase + dd;
+#pragma unroll
+        for (int k2 = 0; k2 < 2; ++k2) {
+            const int dd = threadIdx.x + 128 * k2, d = dbase + dd;
+            if (d >= D) continue;
             float a = (s_acc[0][dd] + s_acc[1][dd]) + (s_acc[2][dd] + s_acc[3][dd]);
-            if (p.k_new) a = fmaf(w_new, to_f32<QT>(((const QT*)p.v_new)[((int64_t)b * (p.H / p.G) + h / p.G) * D + d]), a);
+            if (p.k_new)
+                a = fmaf(w_new, dbase == 0 ? v_pre[k2]
+                                           : to_f32<QT>(((const QT*)p.v_new)[((int64_t)b * (p.H / p.G) + h / p.G) * D + d]), a);
             if (p.out) ((QT*)p.out)[((int64_t)b * p.H + h) * D + d] = from_f32<QT>(a * inv);
             else if (XCHG && p.n_peers > 0) {
                 for (int g = 0; g < p.n_peers; ++g) p.peer_dst[g][((int64_t)b * p.H + h) * RS + d] = a;
@@ -1023,10 +1056,14 @@ static int launch_mha(const DecodeParams& p, int warps, int64_t n_units, cudaStr
     cfg.stream = st;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
+    const bool early = p.tables_ready != 0;
     switch (p.D) {
-        case 64: return (int)cudaLaunchKernelEx(&cfg, paged_decode_mha_kernel<QT, KVT, 64>, p);
-        case 128: return (int)cudaLaunchKernelEx(&cfg, paged_decode_mha_kernel<QT, KVT, 128>, p);
-        case 256: return (int)cudaLaunchKernelEx(&cfg, paged_decode_mha_kernel<QT, KVT, 256>, p);
+        case 64: return (int)(early ? cudaLaunchKernelEx(&cfg, paged_decode_mha_kernel<QT, KVT, 64, true>, p)
+                                    : cudaLaunchKernelEx(&cfg, paged_decode_mha_kernel<QT, KVT, 64, false>, p));
+        case 128: return (int)(early ? cudaLaunchKernelEx(&cfg, paged_decode_mha_kernel<QT, KVT, 128, true>, p)
+                                     : cudaLaunchKernelEx(&cfg, paged_decode_mha_kernel<QT, KVT, 128, false>, p));
+        case 256: return (int)(early ? cudaLaunchKernelEx(&cfg, paged_decode_mha_kernel<QT, KVT, 256, true>, p)
+                                     : cudaLaunchKernelEx(&cfg, paged_decode_mha_kernel<QT, KVT, 256, false>, p));
         default: return ATTN_B200_ESHAPE;
     }
 }
@@ -1264,6 +1301,8 @@ extern "C" int attn_b200_paged_decode(const void* q, const void* k_new, const vo
     if (!out || !k_new || !v_new) return ATTN_B200_EINVAL;
     if ((S == nullptr) != (P == nullptr)) return ATTN_B200_EINVAL;
     if (!offsets && (uniform_ctx < 0 || (int64_t)uniform_ctx * B != n_tokens)) return ATTN_B200_EINVAL;
+    const int tables_ready = (stages & ATTN_B200_DECODE_TABLES_READY) ? 1 : 0;
+    stages &= ~ATTN_B200_DECODE_TABLES_READY;
     if (stages == 4) {      // single launch: one CTA per (sequence, head), no workspace
         if (S || n_kv_heads != H || block_size > 1 || kv_dtype != q_dtype ||
             !(q_dtype == ATTN_B200_F16 || q_dtype == ATTN_B200_BF16) || !(D == 64 || D == 128 || D == 256) ||
@@ -1283,7 +1322,7 @@ extern "C" int attn_b200_paged_decode(const void* q, const void* k_new, const vo
     DecodeParams p{q, k_cache, v_cache, slots, offsets, (float*)workspace, S, sp_stride, B, H, D, n_tokens, n_slots,
                    uniform_ctx, chunk, scale * kLog2e, kv_dtype == ATTN_B200_E4M3 ? k_scale : nullptr,
                    kv_dtype == ATTN_B200_E4M3 ? v_scale : nullptr, err_flag, 1, n_kv_heads, G, block_size,
-                   max_blocks};
+                   max_blocks, tables_ready};
     if (stages < 1 || stages > 3) return ATTN_B200_EINVAL;
     if (stages & 1) {
         rc = run_stage1(p, q_dtype, kv_dtype, st);

@@ -72,6 +72,9 @@ template <typename T2>
 __global__ void __launch_bounds__(256)
 rope_write_kv_kernel(const RopeKvParams p) {
     using A = Rn2<T2>;
+    // A kernel launched behind this one as a programmatic dependent (the decode's partial kernel)
+    // may be scheduled from here on; it reads nothing this kernel writes before its own wait.
+    asm volatile("griddepcontrol.launch_dependents;");
     const int64_t token = blockIdx.x;
     const int tid = threadIdx.x, nthr = blockDim.x;
     const int cph = p.cph, hv = p.head_vec;

@@ -139,7 +139,8 @@ def paged_kv_attention_forward(Q, K, V, K_cache, V_cache, cache_indices, offsets
                                max_context_len: Optional[int] = None, workspace: Optional[torch.Tensor] = None,
                                out: Optional[torch.Tensor] = None,
                                err_flag: Optional[torch.Tensor] = None, stages: int = 3,
-                               block_size: int = 1, single_launch: Optional[bool] = None) -> List[torch.Tensor]:
+                               block_size: int = 1, single_launch: Optional[bool] = None,
+                               tables_ready: bool = False) -> List[torch.Tensor]:
     """KV-paged single-query attention, block_size = 1 (paged_attention_kernel.cu:237-294).
 
     Q, K, V ``[B, H*D]`` (the current token); K_cache, V_cache ``[slots, H*D]``; cache_indices
@@ -165,6 +166,9 @@ def paged_kv_attention_forward(Q, K, V, K_cache, V_cache, cache_indices, offsets
     captured into a CUDA graph the default is the two-kernel form, whose step is shorter on the GPU
     (18 against 21 us at that shape).  ``True`` forces the single launch (RuntimeError if the case is
     not covered), ``False`` the two kernels.
+    ``tables_ready=True`` is the caller's statement that ``cache_indices`` and ``offsets`` were complete
+    before the kernel that precedes this call on the stream started (they were uploaded, not written
+    by that kernel): the multi-head partial kernel then reads them while that kernel still runs.
     """
     for t, n in ((Q, "Q"), (K, "K"), (V, "V"), (K_cache, "K_cache"), (V_cache, "V_cache")):
         _check_input(t, n)
@@ -239,7 +243,8 @@ def paged_kv_attention_forward(Q, K, V, K_cache, V_cache, cache_indices, offsets
             0 if workspace is None else workspace.numel() * workspace.element_size(),
             S.data_ptr() if return_sp else None, P.data_ptr() if return_sp else None, stride,
             B, H, Hkv, D, T, K_cache.size(0), 0, block_size, max_blocks, chunk, float(scale), _ptr(k_scale),
-            _ptr(v_scale), qd, kvd, stages, _ptr(err_flag), _stream()), "paged_kv_attention_forward")
+            _ptr(v_scale), qd, kvd, stages | (_lib.DECODE_TABLES_READY if tables_ready else 0), _ptr(err_flag),
+            _stream()), "paged_kv_attention_forward")
     return [S, P, O]
 
 
@@ -329,8 +334,9 @@ class PagedDecodeGraph:
         self.chunk = chunk or pick_chunk(batch, Hkv, D, max_tokens, dev, group=H // Hkv, kv_dtype=kvd)
         self.workspace = torch.empty(decode_workspace_bytes(batch, H, D, max_tokens, self.chunk), dtype=torch.uint8,
                                      device=dev)
+        # tables_ready: the slot table and the offsets are written into the arena before the graph is launched
         kw = dict(scale=scale, return_sp=False, chunk=self.chunk, k_scale=k_scale, v_scale=v_scale,
-                  workspace=self.workspace, out=self.out)
+                  workspace=self.workspace, out=self.out, tables_ready=True)
         self._pools = (K_cache, V_cache)
         self.graph = capture_graph(dev, lambda: paged_kv_attention_forward(
             self.q, self.k, self.v, K_cache, V_cache, self.cache_indices, self.offsets, H, **kw))
@@ -401,7 +407,7 @@ class DecodeStepGraph:
             paged_kv_attention_forward(d["q"], d["k"], d["v"], K_cache, V_cache, d["cache_indices"], d["offsets"], H,
                                        scale=scale, return_sp=False, chunk=self.chunk, k_scale=k_scale,
                                        v_scale=v_scale, workspace=self.workspace, out=self.out,
-                                       err_flag=self.err_flag)
+                                       err_flag=self.err_flag, tables_ready=True)   # tables: uploaded, not made by the RoPE kernel
 
         # the warm-up run inside capture_graph executes a real step on whatever the arena holds (zeros:
         # position 0, slot 0, no cached tokens): the caller's first upload overwrites all of it, but

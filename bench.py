@@ -424,7 +424,8 @@ class SmallDecode(LargeDecode):
             for i in range(self.INNER):
                 Kc, Vc = self.pools[i % self.POOLS]
                 A.paged_kv_attention_forward(self.Q, self.K, self.V, Kc, Vc, self.ci, self.off, self.H,
-                                             return_sp=False, chunk=self.chunk, workspace=self.ws, out=self.O)
+                                             return_sp=False, chunk=self.chunk, workspace=self.ws, out=self.O,
+                                             tables_ready=True)     # the slot table and offsets are static
         self.many_graph = A.ops.capture_graph(dev, many)
         torch.cuda.synchronize()
 

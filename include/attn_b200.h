@@ -125,7 +125,15 @@ ATTN_B200_API int attn_b200_rope_write_kv(void* q, void* k, const void* v, const
  * CTAs fill the machine in one wave and the sequences are short:
  * attn_b200_paged_decode_single_launch_ok() says when.
  * The combine kernel is launched as a programmatic dependent of the partial kernel (its launch and
- * prologue overlap that kernel's tail; it waits for the partial rows itself).
+ * prologue overlap that kernel's tail; it waits for the partial rows itself).  The multi-head partial
+ * kernel is in turn launched as a programmatic dependent of whatever kernel precedes the call on
+ * `stream`, and reads nothing before that kernel has completed, so this is invisible to the caller.
+ * ATTN_B200_DECODE_TABLES_READY or-ed into `stages` (3 | ATTN_B200_DECODE_TABLES_READY) is the
+ * caller's statement that `slots` and `offsets` were complete BEFORE the kernel preceding this call
+ * on `stream` started (they came from an upload or an earlier kernel, not from that one): the partial
+ * kernel then reads them while that kernel may still be running, which hides two of its three
+ * dependent round trips.  Everything else (q, the pools, k_new, v_new) may still be written by the
+ * preceding kernel.  Without the flag nothing is assumed.
  * Extensions beyond the reference (which is multi-head, block_size = 1):
  *   n_kv_heads  KV heads (H % n_kv_heads == 0); k_new, v_new, k_cache, v_cache then have n_kv_heads*D
  *               columns and query head h reads KV head h / (H / n_kv_heads).  Pass H for MHA.
@@ -133,6 +141,7 @@ ATTN_B200_API int attn_b200_rope_write_kv(void* q, void* k, const void* v, const
  *               block table int32 [B, max_blocks]; token t of sequence b lives in pool row
  *               slots[b*max_blocks + t/block_size]*block_size + t%block_size.
  */
+enum { ATTN_B200_DECODE_TABLES_READY = 0x100 };
 ATTN_B200_API int attn_b200_paged_decode(const void* q, const void* k_new, const void* v_new, const void* k_cache,
                            const void* v_cache, const int32_t* slots, const int32_t* offsets, void* out,
                            void* workspace, size_t workspace_bytes, double* S, double* P, int64_t sp_stride,

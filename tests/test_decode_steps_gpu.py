@@ -34,6 +34,53 @@ def test_single_launch_decode_ragged(dtype, H, D):
     assert (O.float() - O2.float()).abs().max() <= (1e-3 if dtype == torch.float16 else 1.6e-2)
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_tables_ready_steps_chained_in_one_graph(dtype):
+    """Four decode steps back to back in one CUDA graph, each over its own pool, with `tables_ready`:
+    every partial kernel is a programmatic dependent of the previous step's combine and reads the slot
+    table and the offsets before that kernel has finished.  Each step's output equals the plain call's
+    bit for bit and the oracle within tolerance; a bad slot is still flagged."""
+    import attention_impl_b200 as A
+    B, H, D = 8, 32, 128
+    lens = [0, 1, 31, 32, 33, 700, 1024, 129]
+    steps = []
+    for s_ in range(4):
+        inp = decode_inputs(B, H, D, lens, 4096, dtype, seed=50 + s_)
+        steps.append((inp, [t.cuda() for t in inp], torch.empty(B, H * D, dtype=dtype, device="cuda")))
+    T = sum(lens)
+    chunk = 32
+    ws = torch.empty(A.ops.decode_workspace_bytes(B, H, D, T, chunk), dtype=torch.uint8, device="cuda")
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+
+    def many():
+        for _, a, out in steps:
+            A.paged_kv_attention_forward(*a, H, return_sp=False, chunk=chunk, workspace=ws, out=out,
+                                         tables_ready=True, err_flag=flag)
+    g = A.ops.capture_graph(torch.device("cuda"), many)
+    for _ in range(3):
+        g.replay()
+    torch.cuda.synchronize()
+    assert int(flag.item()) == 0
+    tol = TOL16 if dtype == torch.float16 else 1.6e-2
+    for inp, a, out in steps:
+        _, _, O32 = orc.paged_decode(*inp, H, compute_dtype=torch.float32)
+        assert (out.cpu().float() - O32.float()).abs().max() <= tol
+        _, _, plain = A.paged_kv_attention_forward(*a, H, return_sp=False, chunk=chunk, single_launch=False)
+        assert torch.equal(out, plain)
+    # eager, right behind a kernel that writes q (the case the flag allows): same bits again
+    inp, a, out = steps[0]
+    q2 = a[0].clone()
+    q2.mul_(1.0)
+    _, _, O = A.paged_kv_attention_forward(q2, *a[1:], H, return_sp=False, chunk=chunk, single_launch=False,
+                                           tables_ready=True)
+    assert torch.equal(O, out)
+    ci = a[5].clone()
+    ci[40] = -7
+    A.paged_kv_attention_forward(*a[:5], ci, a[6], H, return_sp=False, chunk=chunk, single_launch=False,
+                                 tables_ready=True, err_flag=flag)
+    assert int(flag.item()) & 1
+
+
 def test_single_launch_decode_small_batch_workload_and_its_choice():
     """B=8, H=32, D=128, ctx ~ U[128,1024]: the heuristic picks the single-launch form by itself; bad
     slots are flagged and skipped; cases it does not cover are refused when forced."""
