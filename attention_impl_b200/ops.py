@@ -336,7 +336,7 @@ class PagedDecodeGraph:
                                      device=dev)
         # tables_ready: the slot table and the offsets are written into the arena before the graph is launched
         kw = dict(scale=scale, return_sp=False, chunk=self.chunk, k_scale=k_scale, v_scale=v_scale,
-                  workspace=self.workspace, out=self.out, tables_ready=True)
+                  workspace=self.workspace, out=self.out, tables_ready=True, single_launch=False)
         self._pools = (K_cache, V_cache)
         self.graph = capture_graph(dev, lambda: paged_kv_attention_forward(
             self.q, self.k, self.v, K_cache, V_cache, self.cache_indices, self.offsets, H, **kw))
@@ -407,7 +407,8 @@ class DecodeStepGraph:
             paged_kv_attention_forward(d["q"], d["k"], d["v"], K_cache, V_cache, d["cache_indices"], d["offsets"], H,
                                        scale=scale, return_sp=False, chunk=self.chunk, k_scale=k_scale,
                                        v_scale=v_scale, workspace=self.workspace, out=self.out,
-                                       err_flag=self.err_flag, tables_ready=True)   # tables: uploaded, not made by the RoPE kernel
+                                       err_flag=self.err_flag, single_launch=False,
+                                       tables_ready=True)   # tables: uploaded, not made by the RoPE kernel
 
         # the warm-up run inside capture_graph executes a real step on whatever the arena holds (zeros:
         # position 0, slot 0, no cached tokens): the caller's first upload overwrites all of it, but

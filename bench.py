@@ -425,6 +425,7 @@ class SmallDecode(LargeDecode):
                 Kc, Vc = self.pools[i % self.POOLS]
                 A.paged_kv_attention_forward(self.Q, self.K, self.V, Kc, Vc, self.ci, self.off, self.H,
                                              return_sp=False, chunk=self.chunk, workspace=self.ws, out=self.O,
+                                             single_launch=False,   # (the warm-up run is eager: same kernels as the capture)
                                              tables_ready=True)     # the slot table and offsets are static
         self.many_graph = A.ops.capture_graph(dev, many)
         torch.cuda.synchronize()
