@@ -183,7 +183,12 @@ paged_decode_mha_kernel(const DecodeParams p) {
     const int sub = lane % LPR, grp = lane / LPR;
     const int h_raw = ((blockIdx.x % p.head_groups) * warps + warp) * HPW + grp;
     Unit un;
-    if (!resolve_unit(u, p.B, p.chunk, sb, un) || h_raw - grp >= p.H) return;
+    if (!resolve_unit(u, p.B, p.chunk, sb, un) || h_raw - grp >= p.H) {
+        // (a CTA without work still takes part in the grid dependency: if every CTA left without waiting,
+        // this grid would count as complete, and release its dependent, before its predecessor is)
+        if constexpr (EARLY) asm volatile("griddepcontrol.wait;" ::: "memory");
+        return;
+    }
     int early_slot = -1;
     if constexpr (EARLY) {
         const int64_t t = un.tbeg + lane;

@@ -76,6 +76,7 @@ def test_tables_ready_steps_chained_in_one_graph(dtype):
     assert torch.equal(O, out)
     ci = a[5].clone()
     ci[40] = -7
+    torch.cuda.synchronize()      # the flag's contract: the tables are not written by the kernel just before the call
     A.paged_kv_attention_forward(*a[:5], ci, a[6], H, return_sp=False, chunk=chunk, single_launch=False,
                                  tables_ready=True, err_flag=flag)
     assert int(flag.item()) & 1
