@@ -861,8 +861,11 @@ lse_combine_kernel(const CombineParams p) {
     __shared__ float s_acc[4][256];
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     // A kernel launched behind this one as a programmatic dependent (the partial kernel of the next
-    // decode step) may be scheduled from here on; it reads nothing before its own wait.
-    asm volatile("griddepcontrol.launch_dependents;");
+    // decode step) may be scheduled from here on; it reads nothing before its own wait.  Not in the
+    // exchange instantiation: what follows a pushing combine is the waiting combine, whose CTAs would
+    // sit on the SMs polling their counters while the partial kernel still runs (measured at 8 GPUs
+    // from a CUDA graph: 0.994 against 0.941 ms per step).
+    if constexpr (!XCHG) asm volatile("griddepcontrol.launch_dependents;");
     if constexpr (XCHG) {
         if (p.wait_flags) {
             if (threadIdx.x < p.n_parts) {
