@@ -15,7 +15,7 @@ LIB_PATH = os.path.join(_HERE, "lib", "libattn_b200.so")
 F16, BF16, F32, E4M3 = 0, 1, 2, 3
 FLAG_BAD_SLOT, FLAG_BAD_POSITION, FLAG_BAD_OFFSETS, FLAG_TIMEOUT = 1, 2, 4, 8
 DECODE_TABLES_READY = 0x100      # or-ed into `stages` of attn_b200_paged_decode
-ABI_VERSION = 3
+ABI_VERSION = 4
 STATIC_SCRATCH_BYTES = 16 << 20
 
 _vp, _i32, _i64, _f32, _sz = C.c_void_p, C.c_int, C.c_int64, C.c_float, C.c_size_t

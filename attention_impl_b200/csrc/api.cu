@@ -17,4 +17,4 @@ extern "C" const char* attn_b200_strerror(int status) {
     return "unknown status";
 }
 
-extern "C" int attn_b200_abi_version(void) { return 3; }
+extern "C" int attn_b200_abi_version(void) { return 4; }

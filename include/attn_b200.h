@@ -61,7 +61,7 @@ enum {
 };
 
 ATTN_B200_API const char* attn_b200_strerror(int status);
-/* ABI version of this header; bumped on any signature change. */
+/* ABI version of this header (4); bumped on any change of a signature or of an argument's meaning. */
 ATTN_B200_API int attn_b200_abi_version(void);
 
 /* ------------------------------------------------------------------------------------------
