@@ -343,6 +343,7 @@ static __device__ LaunchState g_launch[kLaunchSlots];
 
 struct Item2p {
     int tp, h, b, L, q0, n0, n1, nmax;
+    int t0;            // index of the lower query tile (the upper one, if any, is t0 + 1)
     int64_t seq_beg;
     bool valid;
 };
@@ -371,6 +372,14 @@ struct SmemLayout2p {
 // group come first while the CTAs running at any moment share the K/V of a few dozen (sequence,
 // head) combinations, which stay in L2 (with the pair index slowest over ALL combinations every CTA
 // would stream its own K/V from DRAM: measured 814 against 960 TFLOP/s).
+//
+// Pairing.  A sequence of nq query tiles is cut into pairs from its END: with nq odd, pair 0 is tile 0
+// alone and pair tp >= 1 holds tiles 2 tp - 1 and 2 tp; with nq even pair tp holds tiles 2 tp and
+// 2 tp + 1.  The tile without a partner keeps one warpgroup idle for as many rounds as it has key
+// tiles: one round for tile 0, but nq rounds for the last tile, which is where pairing from the start
+// would leave it (3.4 % of the workload's rounds).  A sequence longer than the caller's max_seqlen is
+// paired from the start, so that the rows covered are the first n_qtiles pairs' as the zero-fill of
+// the rest assumes.
 constexpr int ITEM_GROUP = 16;
 __device__ __forceinline__ Item2p decode_item(const Params& p, int64_t id) {
     Item2p it;
@@ -380,7 +389,7 @@ __device__ __forceinline__ Item2p decode_item(const Params& p, int64_t id) {
     it.tp = p.n_qtiles - 1 - x;
     it.valid = true;
     if (hb >= p.H * p.B) {          // padding of the last group: an empty item
-        it.L = 0; it.q0 = 1; it.b = it.h = 0; it.n0 = it.n1 = it.nmax = 0; it.seq_beg = 0;
+        it.L = 0; it.q0 = 1; it.b = it.h = 0; it.n0 = it.n1 = it.nmax = 0; it.seq_beg = 0; it.t0 = 0;
         return it;
     }
     it.b = hb / p.H;
@@ -389,9 +398,13 @@ __device__ __forceinline__ Item2p decode_item(const Params& p, int64_t id) {
     const int64_t seq_end = p.offsets[it.b];
     it.valid = !(it.seq_beg < 0 || seq_end < it.seq_beg || seq_end > p.n_tokens);
     it.L = it.valid ? (int)(seq_end - it.seq_beg) : 0;
-    it.q0 = it.tp * 2 * BM;
-    it.n0 = 2 * it.tp + 1;                                   // key tiles of the lower query tile
-    it.n1 = (it.q0 + BM < it.L) ? 2 * it.tp + 2 : 0;         // of the upper one (0: past the end)
+    const int nq = (it.L + BM - 1) / BM;                     // query (and key) tiles of the sequence
+    const int odd = it.L <= p.n_qtiles * 2 * BM ? (nq & 1) : 0;
+    it.t0 = it.tp == 0 ? 0 : 2 * it.tp - odd;
+    const int t1 = 2 * it.tp + 1 - odd;                      // upper tile (tp = 0 of an odd count: none)
+    it.q0 = it.t0 * BM;
+    it.n0 = it.t0 < nq ? it.t0 + 1 : 0;                      // key tiles of the lower query tile (0: no such tile)
+    it.n1 = (t1 > it.t0 && t1 < nq) ? t1 + 1 : 0;            // of the upper one (0: none)
     it.nmax = it.n1 > it.n0 ? it.n1 : it.n0;
     return it;
 }
@@ -460,7 +473,7 @@ prefill_tc2p_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                     if (id >= n_items) { id = -1; break; }
                     it = decode_item(p, id);
                     if (!it.valid && p.err_flag) atomicOr(p.err_flag, ATTN_B200_FLAG_BAD_OFFSETS);
-                } while (!it.valid || it.q0 >= it.L);
+                } while (!it.valid || it.n0 == 0);
                 if (id < 0) it.tp = -1;
                 sm.item[n_it & 3] = it;
                 mbar_arrive(&sm.item_full[n_it & 3]);
@@ -636,7 +649,7 @@ prefill_tc2p_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             const int u = upper_of(w, n_it);
             const int nk = u ? it.n1 : it.n0;
             if (nk == 0) continue;
-            const int tq = 2 * it.tp + u;
+            const int tq = it.t0 + u;
             // staged read-out when the tile lies wholly inside the sequence and the output is 16-bit
             const bool whole = it.q0 + u * BM + BM <= it.L && !p.out_f32;
             const OutStage stage{whole ? sm.o_stage[w] : nullptr, &map_o, (int)(it.seq_beg + it.q0 + u * BM)};
