@@ -40,7 +40,14 @@ def _int32(x: torch.Tensor, name: str) -> None:
         raise RuntimeError(f"{name} must be int32 (expected scalar type Int but found {x.dtype})")
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream() -> int:
+    # the raw handle of the current stream of the current device (the short way when torch has it:
+    # torch.cuda.current_stream() costs several microseconds of Python per call)
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
 
 
@@ -48,8 +55,44 @@ def _ptr(x: Optional[torch.Tensor]) -> Optional[int]:
     return None if x is None else x.data_ptr()
 
 
+_SM_COUNT: dict = {}
+
+
 def sm_count(device) -> int:
-    return torch.cuda.get_device_properties(device).multi_processor_count
+    key = device.index if isinstance(device, torch.device) and device.index is not None else device
+    n = _SM_COUNT.get(key)
+    if n is None:
+        n = _SM_COUNT[key] = torch.cuda.get_device_properties(device).multi_processor_count
+    return n
+
+
+class _on_device:
+    """`with torch.cuda.device(dev)` that does nothing when dev is already current (the usual case;
+    the context manager costs a few microseconds each way)."""
+    __slots__ = ("ctx",)
+
+    def __init__(self, dev: torch.device):
+        self.ctx = None if dev.index is None or dev.index == torch.cuda.current_device() else torch.cuda.device(dev)
+
+    def __enter__(self):
+        if self.ctx is not None:
+            self.ctx.__enter__()
+
+    def __exit__(self, *exc):
+        if self.ctx is not None:
+            return self.ctx.__exit__(*exc)
+        return False
+
+
+_EMPTY_F64: dict = {}
+
+
+def _empty_f64(dev: torch.device) -> torch.Tensor:
+    """The placeholder returned for S and P when they are not requested (one per device)."""
+    t = _EMPTY_F64.get(dev)
+    if t is None:
+        t = _EMPTY_F64[dev] = torch.empty(0, dtype=torch.float64, device=dev)
+    return t
 
 
 # ----------------------------------------------------------------------------------------------
@@ -74,7 +117,7 @@ def rotary_embedding_inplace(Q, K, positions, cos, sin, head_dim: int, *, check_
     if Q.size(1) % head_dim or K.size(1) % head_dim:
         raise RuntimeError("Q.size(1) and K.size(1) must be multiples of head_dim")
     flag = torch.zeros(1, dtype=torch.int32, device=Q.device) if check_positions else None
-    with torch.cuda.device(Q.device):
+    with _on_device(Q.device):
         check(lib.attn_b200_rope_inplace(Q.data_ptr(), K.data_ptr(), positions.data_ptr(), cos.data_ptr(),
                                          sin.data_ptr(), n_tokens, Q.size(1) // head_dim, K.size(1) // head_dim,
                                          head_dim, rot_half, cos.size(0), dt, _ptr(flag), _stream()),
@@ -101,7 +144,7 @@ def rope_and_cache_write(Q, K, V, positions, cos, sin, slots, K_cache, V_cache, 
     hk = K.size(1) // head_dim
     if V.shape != K.shape or K_cache.size(1) != K.size(1) or V_cache.shape != K_cache.shape:
         raise RuntimeError("V must match K, and the pools must be [slots, Hk*head_dim]")
-    with torch.cuda.device(Q.device):
+    with _on_device(Q.device):
         check(lib.attn_b200_rope_write_kv(Q.data_ptr(), K.data_ptr(), V.data_ptr(), positions.data_ptr(),
                                           cos.data_ptr(), sin.data_ptr(), slots.data_ptr(), K_cache.data_ptr(),
                                           V_cache.data_ptr(), n, Q.size(1) // head_dim, hk, head_dim, cos.size(1),
@@ -161,8 +204,8 @@ def paged_kv_attention_forward(Q, K, V, K_cache, V_cache, cache_indices, offsets
     memory (multi-head attention over 16-bit pools, per-token table, head_dim 64/128/256, no S/P).
     ``None`` (default) takes it for an EAGER call when S and P are not requested and the library's
     heuristic covers the case: the (sequence, head) pairs alone fill the machine in one wave and
-    sequences are short (a batch of 8 with 32 heads).  There the host bounds the call (32 us against
-    42 us per call for the two launches and their scratch allocation).  While the stream is being
+    sequences are short (a batch of 8 with 32 heads).  There the host bounds the call (23 us against
+    27 us per call for the two launches and their scratch allocation).  While the stream is being
     captured into a CUDA graph the default is the two-kernel form, whose step is shorter on the GPU
     (18 against 21 us at that shape).  ``True`` forces the single launch (RuntimeError if the case is
     not covered), ``False`` the two kernels.
@@ -207,9 +250,7 @@ def paged_kv_attention_forward(Q, K, V, K_cache, V_cache, cache_indices, offsets
             if t.dtype != torch.float32 or t.numel() != Hkv:
                 raise RuntimeError(f"{n} must be float32 [Hkv]")
     dev = Q.device
-    with torch.cuda.device(dev):
-        if chunk is None:
-            chunk = pick_chunk(B, Hkv, D, T, dev, group=H // Hkv, kv_dtype=kvd)
+    with _on_device(dev):
         if single_launch is None:
             single_launch = (not return_sp and stages == 3 and not torch.cuda.is_current_stream_capturing()
                              and bool(lib.attn_b200_paged_decode_single_launch_ok(
@@ -218,6 +259,10 @@ def paged_kv_attention_forward(Q, K, V, K_cache, V_cache, cache_indices, offsets
             raise RuntimeError("single_launch=True does not produce S and P: pass return_sp=False")
         if single_launch:
             stages = 4
+            if chunk is None:
+                chunk = 32                       # unused by the single launch, only range-checked
+        if chunk is None:
+            chunk = pick_chunk(B, Hkv, D, T, dev, group=H // Hkv, kv_dtype=kvd)
         need = 0 if single_launch else decode_workspace_bytes(B, H, D, T, chunk)
         if single_launch:
             workspace = None
@@ -234,8 +279,7 @@ def paged_kv_attention_forward(Q, K, V, K_cache, V_cache, cache_indices, offsets
             P = torch.zeros_like(S)
             stride = max_context_len + 1
         else:
-            S = torch.empty(0, dtype=torch.float64, device=dev)
-            P = torch.empty(0, dtype=torch.float64, device=dev)
+            S = P = _empty_f64(dev)
             stride = 0
         check(lib.attn_b200_paged_decode(
             Q.data_ptr(), K.data_ptr(), V.data_ptr(), K_cache.data_ptr(), V_cache.data_ptr(),
@@ -466,7 +510,7 @@ class HostStagedDecoder:
         self.max_batch, self.dim_kv = max_batch, dim_kv
         self.cur = 0                 # table buffer of the running step
         self._staged = None          # (cache_indices.data_ptr(), offsets.data_ptr(), T) resident in buffer 1 - cur
-        with torch.cuda.device(dev):
+        with _on_device(dev):
             self.copy_stream = torch.cuda.Stream()
             self.events = [torch.cuda.Event() for _ in range(n_groups)]
             self.table_event = torch.cuda.Event()
@@ -563,7 +607,7 @@ def paged_decode_partial(Q, K_cache, V_cache, cache_indices, offsets, num_heads:
     if scale is None:
         scale = 1.0 / math.sqrt(D)
     dev = Q.device
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         if chunk is None:
             chunk = pick_chunk(B, Hkv, D, T, dev, group=H // Hkv, kv_dtype=kvd)
         need = decode_workspace_bytes(B, H, D, T, chunk)
@@ -591,7 +635,7 @@ def lse_combine(parts, Q, K=None, V=None, *, num_heads: int, scale: Optional[flo
         scale = 1.0 / math.sqrt(D)
     O = torch.empty_like(Q)
     Hkv = K.size(1) // D if K is not None else H
-    with torch.cuda.device(Q.device):
+    with _on_device(Q.device):
         check(lib.attn_b200_lse_combine(parts.data_ptr(), n_parts, Q.data_ptr(), _ptr(K), _ptr(V), O.data_ptr(),
                                         B, H, Hkv, D, float(scale), _dtype_code(Q, "Q"), _stream()), "lse_combine")
     return O
@@ -617,7 +661,7 @@ def kv_attention_forward(Q, K, V, K_cache, V_cache, num_heads: int, *, scale: fl
     ctx = K_cache.size(1)
     T = B * ctx
     dev = Q.device
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         chunk = pick_chunk(B, H, D, T, dev)
         need = decode_workspace_bytes(B, H, D, T, chunk)
         ws = torch.empty(need, dtype=torch.uint8, device=dev)
@@ -668,7 +712,7 @@ def paged_attention_forward(Q, K, V, offsets, num_heads: int, *, scale: Optional
     if scale is None:
         scale = 1.0 / math.sqrt(D)
     dev = Q.device
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         if max_seqlen is None:
             lens = torch.diff(offsets, prepend=offsets.new_zeros(1))
             max_seqlen = int(lens.max().item()) if B > 0 else 0
@@ -724,7 +768,7 @@ def paged_prefill_attention(Q, K_cache, V_cache, cache_indices, kv_offsets, q_of
     if scale is None:
         scale = 1.0 / math.sqrt(D)
     dev = Q.device
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         if max_q_len is None:
             max_q_len = int(torch.diff(q_offsets, prepend=q_offsets.new_zeros(1)).max().item()) if B else 0
         if max_kv_len is None:
@@ -755,7 +799,7 @@ def naive_attention_forward(Q, K, V, mask, num_heads: int, *, scale: Optional[fl
     if scale is None:
         scale = 1.0 / math.sqrt(D)
     dev = Q.device
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         O = torch.empty_like(Q)
         if return_sp:
             S = torch.zeros(B, H, L, L, dtype=Q.dtype, device=dev)
