@@ -72,6 +72,12 @@ struct Params {
 // Params::split_rows = 256 is that default; a caller who wants 2e-3 everywhere asks for two terms
 // on every row (split_rows = INT_MAX: half as many P.V MMAs again and a second pass over P).
 constexpr int THREADS2 = 384;   // 3 warpgroups: softmax 0, softmax 1, {TMA, MMA, 2 idle warps}
+// Registers per thread after setmaxnreg.  The CTA's pool is what it was launched with: 65536 / threads
+// rounded down to a multiple of 8, times the thread count.  A setmaxnreg.inc that asks for more than
+// the pool holds never returns (the kernel hangs), so the identity is checked here and not by trying.
+constexpr int kRegsSoftmax2 = 216, kRegsOther2 = 72;     // 224 / 56 before: +1.6 %, the MMA thread spills less
+static_assert(8 * 32 * kRegsSoftmax2 + 4 * 32 * kRegsOther2 <= THREADS2 * ((65536 / THREADS2) / 8 * 8),
+              "setmaxnreg targets exceed the CTA's register pool");
 
 // Staged read-out of an output tile (16-bit output, all 128 rows of the tile inside the sequence):
 // the warpgroup packs its rows into a private 16 KB shared-memory buffer in the 128-byte-swizzled
@@ -457,7 +463,7 @@ prefill_tc2p_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     // producer bookkeeping for the drain on abort: K/V tiles and Q tiles issued in total
     int g_issued_k = 0, g_issued_v = 0, q_issued[2] = {0, 0};
     if (warp >= 8) {
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsOther2));
     if (warp == 8) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
@@ -635,7 +641,7 @@ prefill_tc2p_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     }
     } else {
         // ------------------------------------------------------------------ softmax warpgroups
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsSoftmax2));
         const int w = warp >> 2;
         const int r = threadIdx.x & 127;
         const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
@@ -698,6 +704,10 @@ prefill_tc2p_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 // stream's 64 threads) once it has landed.  Grouped-query heads: query head h reads KV head h / (H / Hkv).
 // =============================================================================================
 constexpr int THREADS_PG = 512;
+constexpr int kRegsSoftmaxPg = 208, kRegsOtherPg = 56, kRegsGatherPg = 40;     // 200 / 56 / 56 before: +1.1 %
+static_assert(8 * 32 * kRegsSoftmaxPg + 4 * 32 * kRegsOtherPg + 4 * 32 * kRegsGatherPg <=
+                  THREADS_PG * ((65536 / THREADS_PG) / 8 * 8),
+              "setmaxnreg targets exceed the CTA's register pool");
 constexpr int KSTAGES_PG = 2;    // K tiles in flight (3 fit in shared memory and were measured: 854 against 935 TFLOP/s)
 
 struct PagedTcParams {
@@ -790,10 +800,11 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const Params 
     tc_fence_after();
     const uint32_t tmem = sm.tmem_base;
 
-    // Registers: launched with 128 per thread (16 warps); 8 * 200 + 8 * 56 = 16 * 128.
+    // Registers: launched with 128 per thread (16 warps); 8 * 208 (softmax) + 4 * 56 (TMA, MMA) + 4 * 40
+    // (gather) = 16 * 128.  (200 / 56 / 56 before: +1.1 %, the softmax row spills less.)
     if (warp >= 12) {
         // ------------------------------------------------------------------ gather producers
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsGatherPg));
         // Two independent streams: warps 12-13 copy the K tiles, warps 14-15 the V tiles.  Each
         // stream loops  wait for its stage -> issue the tile's copies -> wait for them -> publish
         // (fence.proxy.async + arrive by its 64 threads), so K_j is on its way as soon as
@@ -854,7 +865,7 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const Params 
         }
         asm volatile("cp.async.wait_group 0;" ::: "memory");
     } else if (warp >= 8) {
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsOtherPg));
         if (warp == 8) {
             // -------------------------------------------------------------- TMA: the two Q tiles
             if (lane == 0) {
@@ -936,7 +947,7 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const Params 
         }
     } else {
         // ------------------------------------------------------------------ softmax warpgroups
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 200;");
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsSoftmaxPg));
         const int w = warp >> 2;
         const int r = threadIdx.x & 127;
         const int nk = w ? n1 : n0;
