@@ -1,6 +1,8 @@
 """Fetch the reference project's own test files, unchanged, for the acceptance run against the drop-in.
 
-    python tests/reference_suite/fetch.py [path to the reference checkout]     (default /root/reference)
+    python tests/reference_suite/fetch.py [path to the reference checkout]
+
+(default: the directory ``reference`` beside this repository, or ``$ATTENTION_IMPL_REFERENCE``)
 
 Copies ``<reference>/tests/*.py`` byte for byte into ``tests/reference_suite/_ref/`` and writes a
 MANIFEST with their SHA-256 sums.  ``_ref/`` is listed in .gitignore: the files are fetched, not
@@ -17,8 +19,16 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 DEST = os.path.join(HERE, "_ref")
 
 
-def fetch(reference_root: str = "/root/reference") -> int:
-    src = os.path.join(reference_root, "tests")
+def default_reference_root() -> str:
+    env = os.environ.get("ATTENTION_IMPL_REFERENCE")
+    if env:
+        return env
+    repo = os.path.dirname(os.path.dirname(HERE))
+    return os.path.join(os.path.dirname(repo), "reference")
+
+
+def fetch(reference_root: str = "") -> int:
+    src = os.path.join(reference_root or default_reference_root(), "tests")
     if not os.path.isdir(src):
         return 0
     os.makedirs(DEST, exist_ok=True)
